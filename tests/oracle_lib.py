@@ -1,0 +1,177 @@
+"""ctypes bindings of the CPU checkers (test infrastructure only).
+
+`oracle()` loads oracle/liboracle.so, our C restatement of picograd's CPU GEMM
+path.  `reference()` loads oracle/_ref/libpicograd_ref.so, the unmodified
+picograd library compiled from its own sources, when that build exists
+(it is git-ignored and built by `make -C oracle ref`).
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+F32, F16, BF16 = 0, 1, 2
+_sz = C.c_size_t
+_vp = C.c_void_p
+
+
+def _ptr(a):
+    return a.ctypes.data_as(_vp)
+
+
+class Oracle:
+    def __init__(self, path):
+        L = C.CDLL(path)
+        self.L = L
+        L.pgo_gemm_ex.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]
+        L.pgo_gemm_ex_panel.argtypes = L.pgo_gemm_ex.argtypes + [_sz] * 4
+        L.pgo_bmm.argtypes = [C.c_int, _sz, _sz, _sz, _sz, _vp, _vp, _vp]
+        L.pgo_matmul_backward.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp]
+        L.pgo_softmax_rows.argtypes = [_vp, _vp, _sz, _sz]
+        L.pgo_gelu.argtypes = [_vp, _vp, _sz]
+        L.pgo_gelu_grad.argtypes = [_vp, _vp, _vp, _sz]
+        for n in ("pgo_f32_to_bf16_n", "pgo_f32_to_f16_n", "pgo_bf16_to_f32_n", "pgo_f16_to_f32_n"):
+            getattr(L, n).argtypes = [_vp, _vp, _sz]
+        L.pgo_num_threads.restype = C.c_int
+
+    def threads(self):
+        return int(self.L.pgo_num_threads())
+
+    def gemm_ex(self, dtype, a, b, m=None, n=None, k=None, lda=None, ldb=None, ldc=None, c=None):
+        """a: [m,lda-ish] array (f32 or uint16), b likewise; returns f32 C [m,ldc]."""
+        m = a.shape[0] if m is None else m
+        k = a.shape[1] if k is None else k
+        n = b.shape[1] if n is None else n
+        lda = a.strides[0] // a.itemsize if lda is None else lda
+        ldb = b.strides[0] // b.itemsize if ldb is None else ldb
+        if c is None:
+            ldc = n if ldc is None else ldc
+            c = np.zeros((m, ldc), np.float32)
+        else:
+            ldc = c.strides[0] // 4
+        self.L.pgo_gemm_ex(dtype, m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), ldc)
+        return c
+
+    def gemm_ex_panel(self, dtype, a, b, r0, r1, c0, c1):
+        m, k = a.shape
+        n = b.shape[1]
+        c = np.zeros((m, n), np.float32) if m * n <= (1 << 24) else None
+        if c is None:
+            # compute into a compact panel buffer by offsetting the C pointer
+            pan = np.zeros((r1 - r0, c1 - c0), np.float32)
+            ldc = c1 - c0
+            base = pan.ctypes.data - (r0 * ldc + c0) * 4
+            self.L.pgo_gemm_ex_panel(dtype, m, n, k, _ptr(a), a.strides[0] // a.itemsize,
+                                     _ptr(b), b.strides[0] // b.itemsize,
+                                     _vp(base), ldc, r0, r1, c0, c1)
+            return pan
+        self.L.pgo_gemm_ex_panel(dtype, m, n, k, _ptr(a), a.strides[0] // a.itemsize,
+                                 _ptr(b), b.strides[0] // b.itemsize, _ptr(c), n, r0, r1, c0, c1)
+        return c[r0:r1, c0:c1].copy()
+
+    def bmm(self, dtype, a, b):
+        bt, m, k = a.shape
+        n = b.shape[2]
+        c = np.zeros((bt, m, n), np.float32)
+        self.L.pgo_bmm(dtype, bt, m, n, k, _ptr(a), _ptr(b), _ptr(c))
+        return c
+
+    def matmul_backward(self, dtype, a, b, g, want_a=True, want_b=True):
+        m, k = a.shape
+        n = b.shape[1]
+        ga = np.zeros((m, k), np.float32) if want_a else None
+        gb = np.zeros((k, n), np.float32) if want_b else None
+        self.L.pgo_matmul_backward(dtype, m, n, k, _ptr(a), _ptr(b), _ptr(g),
+                                   _ptr(ga) if want_a else None, _ptr(gb) if want_b else None)
+        return ga, gb
+
+    def softmax_rows(self, x):
+        out = np.empty_like(x)
+        self.L.pgo_softmax_rows(_ptr(out), _ptr(x), x.size // x.shape[-1], x.shape[-1])
+        return out
+
+    def gelu(self, x):
+        out = np.empty_like(x)
+        self.L.pgo_gelu(_ptr(out), _ptr(x), x.size)
+        return out
+
+    def gelu_grad(self, x, gy):
+        out = np.empty_like(x)
+        self.L.pgo_gelu_grad(_ptr(out), _ptr(x), _ptr(gy), x.size)
+        return out
+
+    def to_bf16(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape, np.uint16)
+        self.L.pgo_f32_to_bf16_n(_ptr(out), _ptr(x), x.size)
+        return out
+
+    def to_f16(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape, np.uint16)
+        self.L.pgo_f32_to_f16_n(_ptr(out), _ptr(x), x.size)
+        return out
+
+    def from_bf16(self, x):
+        out = np.empty(x.shape, np.float32)
+        self.L.pgo_bf16_to_f32_n(_ptr(out), _ptr(x), x.size)
+        return out
+
+    def from_f16(self, x):
+        out = np.empty(x.shape, np.float32)
+        self.L.pgo_f16_to_f32_n(_ptr(out), _ptr(x), x.size)
+        return out
+
+
+class Reference:
+    """The unmodified picograd CPU library (backend/backend.h:103-136)."""
+
+    def __init__(self, path):
+        L = C.CDLL(path)
+        self.L = L
+        L.pg_gemm.argtypes = [_sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]
+        L.pg_gemm_ex.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]
+        L.pg_thread_pool_size.restype = C.c_int
+
+    def threads(self):
+        return int(self.L.pg_thread_pool_size())
+
+    def gemm_ex(self, dtype, a, b, c=None):
+        m, k = a.shape
+        n = b.shape[1]
+        if c is None:
+            c = np.zeros((m, n), np.float32)
+        lda, ldb, ldc = a.strides[0] // a.itemsize, b.strides[0] // b.itemsize, c.strides[0] // 4
+        if dtype == F32:
+            self.L.pg_gemm(m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), ldc)
+        else:
+            self.L.pg_gemm_ex(dtype, m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), ldc)
+        return c
+
+
+_ORACLE = None
+_REF = None
+
+
+def oracle_path():
+    return os.path.join(ROOT, "oracle", "liboracle.so")
+
+
+def reference_path():
+    return os.path.join(ROOT, "oracle", "_ref", "libpicograd_ref.so")
+
+
+def oracle():
+    global _ORACLE
+    if _ORACLE is None:
+        _ORACLE = Oracle(oracle_path())
+    return _ORACLE
+
+
+def reference():
+    """None when oracle/_ref has not been built on this machine."""
+    global _REF
+    if _REF is None and os.path.exists(reference_path()):
+        _REF = Reference(reference_path())
+    return _REF
