@@ -1,0 +1,130 @@
+/* pg_b200.h — C-ABI of libpg_b200.so, the B200 (sm_100a) device side of
+ * picograd's dense matrix-multiply path.
+ *
+ * The library is what picograd's CUDA seat (src/backend/cuda/cuda.c) would bind
+ * instead of its embedded sm_75 PTX: every entry below names the picograd
+ * interface it stands behind.  Plain C types only; pointers called "device"
+ * come from pg_b200_malloc (or any CUDA allocation of the current device).
+ * Matrices are row-major, leading dimensions are in ELEMENTS, C is always f32
+ * and is overwritten (no alpha/beta), exactly as in backend/backend.h:103-136.
+ *
+ * Status codes are picograd's pg_status (backend/backend.h:25-32):
+ *   0 OK, -1 UNSUPPORTED, -2 ALLOC, -3 COPY, -4 SYNC, -5 GEMM.
+ * Kernel launches are asynchronous on the library's stream; asynchronous
+ * failures (a kernel wait that gave up) surface at pg_b200_sync().
+ * The library is not thread-safe, like the backend it replaces
+ * (backend/backend.c:50, backend/cuda/cuda.c:32-33).
+ */
+#ifndef PG_B200_H
+#define PG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PG_B200_API __attribute__((visibility("default")))
+#else
+#define PG_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* pg_dtype (core/dtype.h:11-16) */
+#define PG_B200_F32 0
+#define PG_B200_F16 1
+#define PG_B200_BF16 2
+
+/* ---- vtable entries of pg_backend_ops (backend/backend_i.h:8-34) ---------- */
+
+/* .init — cuda.c:30-105.  Binds the calling thread to a B200 (ordinal from
+ * pg_b200_set_device, default 0), creates the library's state.  Returns
+ * UNSUPPORTED when no sm_100 device or driver is present. */
+PG_B200_API int pg_b200_init(void);
+/* .malloc / .free — cuda.c:107-121 */
+PG_B200_API void *pg_b200_malloc(size_t nbytes);
+PG_B200_API void pg_b200_free(void *p);
+/* .copy_h2d / .copy_d2h — cuda.c:123-141 (synchronous, like cuMemcpyHtoD) */
+PG_B200_API int pg_b200_copy_h2d(void *dst, const void *src, size_t nbytes);
+PG_B200_API int pg_b200_copy_d2h(void *dst, const void *src, size_t nbytes);
+/* .sync — cuda.c:143-148; also reports kernel-side wait failures as GEMM */
+PG_B200_API int pg_b200_sync(void);
+/* .gemm — cuda.c:150-174: f32 C = A*B, device pointers, any lda/ldb/ldc
+ * (picograd's kernel silently returns unless lda==k, ldb==n, ldc==n). */
+PG_B200_API void pg_b200_gemm(size_t m, size_t n, size_t k, const float *a, size_t lda,
+                  const float *b, size_t ldb, float *c, size_t ldc);
+/* .hgemm / .bgemm — NULL in picograd's CUDA seat (cuda.c:282-291) */
+PG_B200_API void pg_b200_hgemm(size_t m, size_t n, size_t k, const uint16_t *a, size_t lda,
+                   const uint16_t *b, size_t ldb, float *c, size_t ldc);
+PG_B200_API void pg_b200_bgemm(size_t m, size_t n, size_t k, const uint16_t *a, size_t lda,
+                   const uint16_t *b, size_t ldb, float *c, size_t ldc);
+/* .gemm_ex — backend.c:150-177.  Accepts device pointers, or host pointers
+ * (what ops/matmul.c:264-271 passes for f16/bf16), which are staged through
+ * device memory inside the call: H2D, GEMM, D2H, synchronous.  All three
+ * pointers must be of the same kind. */
+PG_B200_API int pg_b200_gemm_ex(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda,
+                    const void *b, size_t ldb, float *c, size_t ldc);
+
+/* ---- the callers' shapes: ops/matmul.c and autograd/autograd.c ------------- */
+
+/* General strided-batched product behind pg_matmul / pg_bmm / pg_tensordot
+ * (ops/matmul.c:186-284, :340-369, :407-490) and the two products of
+ * bwd_matmul (autograd/autograd.c:659-691).  Device pointers.
+ *   C[b] (f32, m x n) = op(A[b]) * op(B[b]),  b = 0..batch-1
+ *   trans_a = 0: A[b] is m x k with leading dimension lda; 1: A[b] is stored k x m
+ *   trans_b = 0: B[b] is k x n with leading dimension ldb; 1: B[b] is stored n x k
+ *   dtype_a / dtype_b: a 16-bit operand may be paired with an f32 one (the f32
+ *   gradient of the backward pass); the f32 side is then split exactly into
+ *   bf16 pieces on the device, never rounded to one.
+ *   stride_* are element offsets between consecutive batch elements (0 =
+ *   operand shared by the whole batch).  accumulate != 0: C += (used for grads). */
+PG_B200_API int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int trans_b,
+                         size_t batch, size_t m, size_t n, size_t k,
+                         const void *a, size_t lda, size_t stride_a,
+                         const void *b, size_t ldb, size_t stride_b,
+                         float *c, size_t ldc, size_t stride_c, int accumulate);
+
+/* bwd_matmul (autograd/autograd.c:561-706) for a [batch,m,k] x [batch,k,n]
+ * (or shared [k,n] when b_batched == 0) product: ga += g * B^T, gb += A^T * g.
+ * a, b in `dtype`; g, ga, gb f32; ga / gb may be NULL. Device pointers. */
+PG_B200_API int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t k,
+                            const void *a, const void *b, int b_batched,
+                            const float *g, float *ga, float *gb);
+
+/* Harness steps between the GEMMs of the attention-shaped and MLP workloads
+ * (ops/activations.c:22-45 softmax rows, :114 GELU, autograd.c:794-801 GELU
+ * gradient), so that those workloads stay on the device.  out16 (optional)
+ * receives the result rounded to dtype16 (f16/bf16, round-to-nearest-even). */
+PG_B200_API int pg_b200_softmax_rows(const float *src, float *out_f32, uint16_t *out16, int dtype16,
+                         size_t rows, size_t len);
+PG_B200_API int pg_b200_gelu(const float *src, float *out_f32, uint16_t *out16, int dtype16, size_t n);
+PG_B200_API int pg_b200_gelu_grad(const float *x, const float *gy, float *out, size_t n);
+PG_B200_API int pg_b200_cast_f32(const float *src, uint16_t *dst, int dtype16, size_t n);
+PG_B200_API int pg_b200_fill_f32(float *dst, float value, size_t n);
+
+/* ---- control ---------------------------------------------------------------- */
+
+/* Device ordinal used by pg_b200_init (picograd uses device 0, cuda.c:49). */
+PG_B200_API int pg_b200_set_device(int ordinal);
+/* Run the library's kernels and copies on this CUDA stream (a cudaStream_t /
+ * CUstream handle; NULL = the default stream). */
+PG_B200_API int pg_b200_set_stream(void *stream);
+/* Text of the last error recorded by this library ("" if none). */
+PG_B200_API const char *pg_b200_last_error(void);
+/* Tuning / test hooks: kernel path 0 = choose, 1 = tensor-core kernel only
+ * (UNSUPPORTED if it cannot take the shape), 2 = FFMA kernel only;
+ * tile configuration index (-1 = choose) and its name; epilogue -1 = choose,
+ * 0 = direct stores, 1 = TMA stores; K splits 0 = choose. */
+PG_B200_API int pg_b200_set_option(const char *name, int value);
+PG_B200_API int pg_b200_num_tile_configs(void);
+PG_B200_API const char *pg_b200_tile_config_name(int index);
+/* Number of kernels this library has launched since it was loaded. */
+PG_B200_API uint64_t pg_b200_launch_count(void);
+/* Name of the path the last GEMM call took ("tc:2cta_256x256", "simt", ...). */
+PG_B200_API const char *pg_b200_last_path(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,257 @@
+"""Python mirror of picograd's operator interface for the matrix-multiply path.
+
+Same names, argument meaning and error behaviour as picograd's C API
+(backend/backend.h:103-136, ops/matmul.h:6-11); device memory is held in torch
+CUDA tensors, whose pointers go straight into the C-ABI of libpg_b200.so.
+16-bit operands are torch.float16 / torch.bfloat16 tensors (or uint16 bit
+patterns with an explicit dtype code); results are always float32.
+"""
+import ctypes as C
+
+import torch
+
+from ._lib import lib
+
+PG_DTYPE_F32, PG_DTYPE_F16, PG_DTYPE_BF16 = 0, 1, 2          # core/dtype.h:11-16
+PG_OK, PG_ERR_UNSUPPORTED, PG_ERR_ALLOC, PG_ERR_COPY, PG_ERR_SYNC, PG_ERR_GEMM = 0, -1, -2, -3, -4, -5
+
+_TORCH2PG = {torch.float32: PG_DTYPE_F32, torch.float16: PG_DTYPE_F16, torch.bfloat16: PG_DTYPE_BF16}
+
+
+class PgError(RuntimeError):
+    def __init__(self, status, what):
+        self.status = status
+        msg = lib.pg_b200_last_error().decode(errors="replace")
+        super().__init__(f"{what}: pg_status {status}: {msg}")
+
+
+def _check(st, what):
+    if st != PG_OK:
+        raise PgError(st, what)
+
+
+_initialised = False
+
+
+def pg_set_device(ordinal=None):
+    """pg_set_device(PG_DEV_CUDA) (backend/backend.c:76-90): init the device seat.
+    The ordinal defaults to torch's current CUDA device."""
+    global _initialised
+    if ordinal is None:
+        ordinal = torch.cuda.current_device()
+    _check(lib.pg_b200_set_device(int(ordinal)), "pg_b200_set_device")
+    _check(lib.pg_b200_init(), "pg_b200_init")
+    _initialised = True
+
+
+def _ready():
+    if not _initialised:
+        pg_set_device()
+    # kernels are queued on torch's current stream so that torch events time them
+    lib.pg_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
+def pg_dev_sync():
+    """pg_dev_sync (backend/backend.c:125-132); raises if a kernel reported a failed wait."""
+    _ready()
+    _check(lib.pg_b200_sync(), "pg_dev_sync")
+
+
+def set_option(name, value):
+    _check(lib.pg_b200_set_option(name.encode(), int(value)), f"set_option({name})")
+
+
+def last_path():
+    return lib.pg_b200_last_path().decode()
+
+
+def launch_count():
+    return int(lib.pg_b200_launch_count())
+
+
+def _code(t, dtype):
+    if dtype is not None:
+        return dtype
+    if t.dtype not in _TORCH2PG:
+        raise TypeError(f"unsupported tensor dtype {t.dtype}")
+    return _TORCH2PG[t.dtype]
+
+
+def pg_gemm_ex(dtype, m, n, k, a, lda, b, ldb, c, ldc):
+    """pg_gemm_ex (backend/backend.c:150-177) on device tensors: C[m,n] f32 = A[m,k] * B[k,n],
+    row-major, ld* in elements, C overwritten.  a/b/c are CUDA tensors (any shape; only their
+    pointers are used)."""
+    _ready()
+    if not (a.is_cuda and b.is_cuda and c.is_cuda):
+        raise ValueError("pg_gemm_ex takes device tensors; use pg_gemm_ex_host for host buffers")
+    if c.dtype != torch.float32:
+        raise TypeError("C must be float32")
+    _check(lib.pg_b200_gemm_ex(dtype, m, n, k, a.data_ptr(), lda, b.data_ptr(), ldb, c.data_ptr(), ldc),
+           "pg_gemm_ex")
+
+
+def pg_gemm(m, n, k, a, lda, b, ldb, c, ldc):
+    """pg_gemm (backend/backend.c:134-148): f32."""
+    pg_gemm_ex(PG_DTYPE_F32, m, n, k, a, lda, b, ldb, c, ldc)
+
+
+def pg_hgemm(m, n, k, a, lda, b, ldb, c, ldc):
+    """pg_hgemm (backend/backend.c:179-185)."""
+    pg_gemm_ex(PG_DTYPE_F16, m, n, k, a, lda, b, ldb, c, ldc)
+
+
+def pg_bgemm(m, n, k, a, lda, b, ldb, c, ldc):
+    """pg_bgemm (backend/backend.c:186-192)."""
+    pg_gemm_ex(PG_DTYPE_BF16, m, n, k, a, lda, b, ldb, c, ldc)
+
+
+def pg_gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc):
+    """pg_gemm_ex with HOST buffers, the way ops/matmul.c:264-271 calls it: a, b, c are CPU
+    tensors (pinned or pageable) or numpy arrays; staging copies happen inside the call."""
+    _ready()
+
+    def ptr(x):
+        return x.data_ptr() if isinstance(x, torch.Tensor) else x.ctypes.data
+
+    _check(lib.pg_b200_gemm_ex(dtype, m, n, k, ptr(a), lda, ptr(b), ldb, ptr(c), ldc), "pg_gemm_ex(host)")
+
+
+def _gemm_batched(dta, dtb, ta, tb, batch, m, n, k, a, lda, sa, b, ldb, sb, c, ldc, sc, accumulate=False):
+    _ready()
+    _check(lib.pg_b200_gemm_batched(dta, dtb, int(ta), int(tb), batch, m, n, k, a.data_ptr(), lda, sa,
+                                    b.data_ptr(), ldb, sb, c.data_ptr(), ldc, sc, int(accumulate)),
+           "pg_b200_gemm_batched")
+
+
+def pg_matmul(a, b, dtype=None):
+    """pg_matmul (ops/matmul.c:186-284): NumPy-style matmul with 1-D promotion; batch dims must be
+    equal or one side unbatched; dtypes must match; last-dim stride must be 1; output float32.
+    Returns None where picograd returns NULL."""
+    if a is None or b is None or a.dim() < 1 or b.dim() < 1:
+        return None
+    if a.dtype != b.dtype:
+        return None
+    dt = _code(a, dtype)
+    av, bv = a.dim() == 1, b.dim() == 1
+    if not bv and a.shape[-1] != b.shape[-2]:
+        return None
+    if bv and a.shape[-1] != b.shape[0]:
+        return None
+    if a.stride(-1) != 1 or (not bv and b.stride(-1) != 1):
+        return None
+    am = 1 if av else a.shape[-2]
+    ak = a.shape[-1]
+    bn = 1 if bv else b.shape[-1]
+    abat = list(a.shape[:-2]) if not av else []
+    bbat = list(b.shape[:-2]) if not bv else []
+    if abat and bbat and abat != bbat:
+        return None
+    bshape = abat or bbat
+    nbatch = 1
+    for d in bshape:
+        if d == 0:
+            return None
+        nbatch *= d
+    rshape = list(bshape) + ([] if av else [am]) + ([] if bv else [bn])
+    if not rshape:
+        rshape = [1]
+    out = torch.empty(rshape, dtype=torch.float32, device=a.device)
+    lda = ak if av else a.stride(-2)
+    ldb = 1 if bv else b.stride(-2)
+    # batch strides: contiguous batches (as every picograd constructor makes them) or shared
+    if abat:
+        ac = a if a.is_contiguous() or _uniform_batch(a) else a.contiguous()
+        sa = _batch_stride(ac)
+    else:
+        ac, sa = a, 0
+    if bbat:
+        bc = b if b.is_contiguous() or _uniform_batch(b) else b.contiguous()
+        sb = _batch_stride(bc)
+    else:
+        bc, sb = b, 0
+    if bv:
+        # [k] vector as a k x 1 matrix
+        ldb = 1
+    _gemm_batched(dt, dt, 0, 0, nbatch, am, bn, ak, ac, lda, sa, bc, ldb, sb, out, bn, am * bn)
+    return out
+
+
+def _uniform_batch(t):
+    """True when all leading (batch) dims collapse to one stride."""
+    if t.dim() <= 3:
+        return True
+    exp = t.stride(-3)
+    for d in range(t.dim() - 3, -1, -1):
+        if t.stride(d) != exp:
+            return False
+        exp *= t.shape[d]
+    return True
+
+
+def _batch_stride(t):
+    return t.stride(-3) if t.dim() >= 3 else 0
+
+
+def pg_bmm(a, b, dtype=None):
+    """pg_bmm (ops/matmul.c:340-369): strict [B,M,K] x [B,K,N] -> float32 [B,M,N]."""
+    if a is None or b is None or a.dim() != 3 or b.dim() != 3:
+        return None
+    if a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1] or a.dtype != b.dtype:
+        return None
+    dt = _code(a, dtype)
+    a, b = a.contiguous(), b.contiguous()
+    bt, m, k = a.shape
+    n = b.shape[2]
+    out = torch.empty((bt, m, n), dtype=torch.float32, device=a.device)
+    _gemm_batched(dt, dt, 0, 0, bt, m, n, k, a, k, m * k, b, n, k * n, out, n, m * n)
+    return out
+
+
+def pg_tensordot(a, b, axes_a, axes_b, dtype=None):
+    """pg_tensordot (ops/matmul.c:407-490): contract axes_a of a with axes_b of b — permute to
+    (free, contracted) x (contracted, free), reshape to 2-D, matmul, reshape back."""
+    if a is None or b is None or a.dtype != b.dtype:
+        return None
+    nd = len(axes_a)
+    if nd < 1 or nd != len(axes_b) or nd > a.dim() or nd > b.dim():
+        return None
+    for i in range(nd):
+        if axes_a[i] >= a.dim() or axes_b[i] >= b.dim() or a.shape[axes_a[i]] != b.shape[axes_b[i]]:
+            return None
+    pa = [d for d in range(a.dim()) if d not in axes_a] + list(axes_a)
+    pb = list(axes_b) + [d for d in range(b.dim()) if d not in axes_b]
+    free_a = [a.shape[d] for d in pa[:a.dim() - nd]]
+    free_b = [b.shape[d] for d in pb[nd:]]
+    kdim = 1
+    for d in axes_a:
+        kdim *= a.shape[d]
+    ra = a.permute(pa).contiguous().reshape(-1, kdim)
+    rb = b.permute(pb).contiguous().reshape(kdim, -1)
+    rc = pg_matmul(ra, rb, dtype=dtype)
+    if rc is None:
+        return None
+    fshape = free_a + free_b
+    return rc.reshape(fshape if fshape else [1])
+
+
+def pg_matmul_backward(a, b, g, need_a=True, need_b=True, ga=None, gb=None, dtype=None):
+    """bwd_matmul (autograd/autograd.c:561-706): ga += g * B^T, gb += A^T * g with float32 g and
+    float32 gradients; a: [..., m, k], b: [..., k, n] or [k, n]; a, b of one dtype.  Gradient
+    tensors are created zeroed when not passed in (pg_backward zeroes them, :2490-2492)."""
+    _ready()
+    dt = _code(a, dtype)
+    a, b, g = a.contiguous(), b.contiguous(), g.contiguous()
+    m, k = a.shape[-2], a.shape[-1]
+    n = b.shape[-1]
+    batch = 1
+    for d in a.shape[:-2]:
+        batch *= d
+    b_batched = b.dim() > 2
+    if need_a and ga is None:
+        ga = torch.zeros(a.shape, dtype=torch.float32, device=a.device)
+    if need_b and gb is None:
+        gb = torch.zeros(b.shape, dtype=torch.float32, device=a.device)
+    _check(lib.pg_b200_matmul_backward(dt, batch, m, n, k, a.data_ptr(), b.data_ptr(), int(b_batched),
+                                       g.data_ptr(), ga.data_ptr() if need_a else None,
+                                       gb.data_ptr() if need_b else None), "pg_b200_matmul_backward")
+    return ga, gb

@@ -1,0 +1,542 @@
+// C-ABI of libpg_b200.so (declared in include/pg_b200.h) and the dispatch between
+// the tensor-core kernel (gemm_tc.cu) and the FFMA kernel (gemm_simt.cu).
+// There is no CPU fallback in here: when no B200 is present every entry fails.
+
+#include "../../include/pg_b200.h"
+#include "pg_internal.h"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+namespace pgb {
+
+struct DeviceBuf {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+
+struct State {
+    bool tried = false;
+    int init_status = ST_UNSUPPORTED;
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    uint32_t *dev_status = nullptr;
+    uint32_t *host_status = nullptr;   // pinned mirror
+    DeviceBuf ws;                      // scratch: operand pieces, split-K slices
+    DeviceBuf stage_a, stage_b, stage_c;  // device staging for host-pointer calls
+    // options
+    int opt_path = 0;        // 0 choose, 1 tensor-core only, 2 FFMA only
+    int opt_cfg = -1;
+    int opt_epilogue = -1;
+    int opt_splits = 0;
+    int opt_f32_parts = 2;   // bf16 pieces an f32 operand is split into when paired with a 16-bit one
+    int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
+    char err[512] = "";
+    char last_path[96] = "";
+    unsigned long long launches = 0;
+    EncodeTiledFn encode = nullptr;
+};
+static State g;
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g.err, sizeof g.err, fmt, ap);
+    va_end(ap);
+    if (getenv("PG_B200_DEBUG")) fprintf(stderr, "pg_b200: %s\n", g.err);
+}
+void set_last_path(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g.last_path, sizeof g.last_path, fmt, ap);
+    va_end(ap);
+}
+void note_launch(int n) { g.launches += (unsigned long long)n; }
+int device_sm_count() { return g.sm_count > 0 ? g.sm_count : 148; }
+EncodeTiledFn get_encode_tiled() { return g.encode; }
+
+static int do_init() {
+    if (g.tried) return g.init_status;
+    g.tried = true;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        set_error("no CUDA device: %s", e != cudaSuccess ? cudaGetErrorString(e) : "count is 0");
+        cudaGetLastError();
+        return g.init_status = ST_UNSUPPORTED;
+    }
+    if (g.device >= n) {
+        set_error("device ordinal %d out of range (%d devices)", g.device, n);
+        return g.init_status = ST_UNSUPPORTED;
+    }
+    if (cudaSetDevice(g.device) != cudaSuccess) {
+        set_error("cudaSetDevice(%d) failed", g.device);
+        cudaGetLastError();
+        return g.init_status = ST_UNSUPPORTED;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, g.device) != cudaSuccess) {
+        set_error("cudaGetDeviceProperties failed");
+        cudaGetLastError();
+        return g.init_status = ST_UNSUPPORTED;
+    }
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; this library holds sm_100a code only", g.device, prop.major, prop.minor);
+        return g.init_status = ST_UNSUPPORTED;
+    }
+    g.sm_count = prop.multiProcessorCount;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr);
+    if (e != cudaSuccess || !fn || qr != cudaDriverEntryPointSuccess) {
+        set_error("cuTensorMapEncodeTiled not available from the driver");
+        cudaGetLastError();
+        return g.init_status = ST_UNSUPPORTED;
+    }
+    g.encode = (EncodeTiledFn)fn;
+    if (cudaMalloc((void **)&g.dev_status, 256) != cudaSuccess ||
+        cudaMemset(g.dev_status, 0, 256) != cudaSuccess ||
+        cudaMallocHost((void **)&g.host_status, 256) != cudaSuccess) {
+        set_error("could not allocate the status word");
+        cudaGetLastError();
+        return g.init_status = ST_ALLOC;
+    }
+    *g.host_status = 0;
+    return g.init_status = ST_OK;
+}
+
+static bool ready() { return do_init() == ST_OK; }
+
+static int grow(DeviceBuf &b, size_t bytes) {
+    if (bytes <= b.bytes) return ST_OK;
+    if (b.ptr) {
+        cudaStreamSynchronize(g.stream);   // nothing in flight may still use the old buffer
+        cudaFree(b.ptr);
+        b.ptr = nullptr;
+        b.bytes = 0;
+    }
+    size_t want = bytes + (bytes >> 3);
+    want = (want + 0xFFFFF) & ~(size_t)0xFFFFF;
+    if (cudaMalloc(&b.ptr, want) != cudaSuccess) {
+        cudaGetLastError();
+        if (cudaMalloc(&b.ptr, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            set_error("out of device memory for %zu bytes of scratch", bytes);
+            return ST_ALLOC;
+        }
+        want = bytes;
+    }
+    b.bytes = want;
+    return ST_OK;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static size_t esize(int dt) { return dt == DT_F32 ? 4 : 2; }
+static bool is16(int dt) { return dt == DT_F16 || dt == DT_BF16; }
+
+// One GEMM, device pointers.
+struct Problem {
+    int dtype_a, dtype_b, trans_a, trans_b;
+    size_t batch, m, n, k;
+    const void *a; size_t lda, stride_a;
+    const void *b; size_t ldb, stride_b;
+    float *c; size_t ldc, stride_c;
+    int accumulate;
+};
+
+static int run_simt(const Problem &p) {
+    SimtGemm s;
+    s.dtype_a = p.dtype_a; s.dtype_b = p.dtype_b;
+    s.M = (uint32_t)p.m; s.N = (uint32_t)p.n; s.K = (uint32_t)p.k; s.batch = (uint32_t)p.batch;
+    s.A = p.a; s.B = p.b;
+    if (!p.trans_a) { s.a_rs = (int64_t)p.lda; s.a_cs = 1; } else { s.a_rs = 1; s.a_cs = (int64_t)p.lda; }
+    if (!p.trans_b) { s.b_rs = (int64_t)p.ldb; s.b_cs = 1; } else { s.b_rs = 1; s.b_cs = (int64_t)p.ldb; }
+    s.a_bs = (int64_t)p.stride_a; s.b_bs = (int64_t)p.stride_b;
+    s.C = p.c; s.ldc = (int64_t)p.ldc; s.c_bs = (int64_t)p.stride_c;
+    s.accumulate = p.accumulate;
+    s.stream = g.stream;
+    int st = simt_gemm_launch(s);
+    if (st == ST_OK) set_last_path("simt");
+    return st;
+}
+
+// Pieces an operand is cut into for the tensor cores, or 1 when it goes as it is.
+static uint32_t parts_for(int dt, int other_dt) {
+    if (dt == DT_F32) return other_dt == DT_F32 ? 3u : (uint32_t)g.opt_f32_parts;
+    if (dt == DT_F16 && other_dt != DT_F16) return 2u;   // f16 = bf16 + bf16 exactly
+    return 1u;
+}
+
+// Tensor-core route.  Returns ST_UNSUPPORTED when the operands break a TMA rule.
+static int run_tc(const Problem &p) {
+    const bool mixed = p.dtype_a != p.dtype_b || p.dtype_a == DT_F32;
+    const uint32_t npa = mixed ? parts_for(p.dtype_a, p.dtype_b) : 1u;
+    const uint32_t npb = mixed ? parts_for(p.dtype_b, p.dtype_a) : 1u;
+    if (p.m > 0x7FFFFFFFull || p.n > 0x7FFFFFFFull || p.k > 0x7FFFFFFFull || p.batch > 0x7FFFFFFull) return ST_UNSUPPORTED;
+
+    TcGemm t = {};
+    t.dtype = mixed ? DT_BF16 : p.dtype_a;
+    t.M = (uint32_t)p.m; t.N = (uint32_t)p.n; t.K = (uint32_t)p.k; t.batch = (uint32_t)p.batch;
+    t.A.ptr = p.a; t.A.ld = p.lda; t.A.z_stride = p.stride_a; t.A.nparts = 1; t.A.mn_major = p.trans_a ? 1u : 0u;
+    t.B.ptr = p.b; t.B.ld = p.ldb; t.B.z_stride = p.stride_b; t.B.nparts = 1; t.B.mn_major = p.trans_b ? 0u : 1u;
+    t.npass = 1; t.a_sel = 0; t.b_sel = 0;
+    t.C = p.c; t.ldc = p.ldc; t.c_stride = p.stride_c;
+    t.accumulate = p.accumulate;
+    t.splits = 1;
+    t.force_cfg = g.opt_cfg; t.force_epilogue = g.opt_epilogue;
+    t.stream = g.stream; t.dev_status = g.dev_status;
+
+    // a batch-shared operand (stride 0) with batch > 1 cannot be a TMA dimension of stride 0
+    if (p.batch > 1 && (p.stride_a == 0 || p.stride_b == 0)) {
+        // fold: run the batch elements as separate launches
+        int st = ST_OK;
+        for (size_t s = 0; s < p.batch && st == ST_OK; ++s) {
+            Problem q = p;
+            q.batch = 1;
+            q.a = (const char *)p.a + s * p.stride_a * esize(p.dtype_a);
+            q.b = (const char *)p.b + s * p.stride_b * esize(p.dtype_b);
+            q.c = p.c + s * p.stride_c;
+            st = run_tc(q);
+        }
+        return st;
+    }
+
+    // ---- scratch layout -------------------------------------------------------
+    const size_t a_rows = p.trans_a ? p.k : p.m, a_cols = p.trans_a ? p.m : p.k;
+    const size_t b_rows = p.trans_b ? p.n : p.k, b_cols = p.trans_b ? p.k : p.n;
+    const size_t a_ld2 = align_up(a_cols, 8), b_ld2 = align_up(b_cols, 8);
+    size_t off = 0, off_a = 0, off_b = 0, off_k = 0;
+    if (npa > 1) { off_a = off; off = align_up(off + p.batch * npa * a_rows * a_ld2 * 2, 256); }
+    if (npb > 1) { off_b = off; off = align_up(off + p.batch * npb * b_rows * b_ld2 * 2, 256); }
+
+    // split-K for shapes that would leave most SMs idle
+    uint32_t splits = 1;
+    const uint32_t k_blocks = (uint32_t)((p.k + 63) / 64);
+    if (p.batch == 1 && npa == 1 && npb == 1) {
+        if (g.opt_splits > 0) {
+            splits = (uint32_t)g.opt_splits;
+        } else {
+            const uint64_t tiles = ((p.m + 127) / 128) * ((p.n + 127) / 128);
+            const uint32_t sms = (uint32_t)device_sm_count();
+            if (tiles * 2 <= sms && k_blocks >= 8) {
+                uint32_t want = (uint32_t)(sms / tiles);
+                uint32_t maxs = k_blocks / 4;
+                splits = want < maxs ? want : maxs;
+                if (splits < 1) splits = 1;
+            }
+        }
+        if (splits > k_blocks) splits = k_blocks;
+        if (splits > 1) {
+            uint32_t per = (k_blocks + splits - 1) / splits;
+            splits = (k_blocks + per - 1) / per;
+        }
+    }
+    const size_t ws_ld = align_up(p.n, 4);
+    if (splits > 1) { off_k = off; off = align_up(off + (size_t)splits * p.m * ws_ld * 4, 256); }
+    if (off) {
+        int st = grow(g.ws, off);
+        if (st != ST_OK) return st;
+    }
+    char *ws = (char *)g.ws.ptr;
+
+    // ---- operand pieces -----------------------------------------------------------
+    if (npa > 1) {
+        uint16_t *dst = (uint16_t *)(ws + off_a);
+        int st;
+        if (p.dtype_a == DT_F32)
+            st = split_f32_to_bf16_launch((const float *)p.a, p.lda, p.stride_a, dst, a_ld2, (uint32_t)a_rows,
+                                          (uint32_t)a_cols, (uint32_t)p.batch, npa, g.stream);
+        else
+            st = split_f16_to_bf16_launch((const uint16_t *)p.a, p.lda, p.stride_a, dst, a_ld2, (uint32_t)a_rows,
+                                          (uint32_t)a_cols, (uint32_t)p.batch, g.stream);
+        if (st != ST_OK) return st;
+        t.A.ptr = dst; t.A.ld = a_ld2; t.A.z_stride = a_rows * a_ld2; t.A.nparts = npa;
+    } else if (mixed && p.dtype_a == DT_F16) {
+        return ST_UNSUPPORTED;
+    }
+    if (npb > 1) {
+        uint16_t *dst = (uint16_t *)(ws + off_b);
+        int st;
+        if (p.dtype_b == DT_F32)
+            st = split_f32_to_bf16_launch((const float *)p.b, p.ldb, p.stride_b, dst, b_ld2, (uint32_t)b_rows,
+                                          (uint32_t)b_cols, (uint32_t)p.batch, npb, g.stream);
+        else
+            st = split_f16_to_bf16_launch((const uint16_t *)p.b, p.ldb, p.stride_b, dst, b_ld2, (uint32_t)b_rows,
+                                          (uint32_t)b_cols, (uint32_t)p.batch, g.stream);
+        if (st != ST_OK) return st;
+        t.B.ptr = dst; t.B.ld = b_ld2; t.B.z_stride = b_rows * b_ld2; t.B.nparts = npb;
+    } else if (mixed && p.dtype_b == DT_F16) {
+        return ST_UNSUPPORTED;
+    }
+    if (npa > 1 || npb > 1) {
+        // keep products whose combined order is below the larger piece count; smallest terms first
+        const uint32_t maxo = (npa > npb ? npa : npb) - 1;
+        uint32_t np = 0, asel = 0, bsel = 0;
+        for (int order = (int)maxo; order >= 0; --order)
+            for (uint32_t i = 0; i < npa; ++i) {
+                int j = order - (int)i;
+                if (j < 0 || j >= (int)npb) continue;
+                asel |= i << (4 * np);
+                bsel |= (uint32_t)j << (4 * np);
+                ++np;
+            }
+        t.npass = np; t.a_sel = asel; t.b_sel = bsel;
+    }
+
+    if (splits > 1) {
+        t.splits = splits;
+        t.C = (float *)(ws + off_k);
+        t.ldc = ws_ld;
+        t.c_stride = p.m * ws_ld;
+        t.accumulate = 0;
+    }
+    if (g.opt_path != 1 && !tc_gemm_supported(t)) return ST_UNSUPPORTED;
+    int st = tc_gemm_launch(t);
+    if (st != ST_OK) return st;
+    if (splits > 1) {
+        st = reduce_splits_launch((const float *)(ws + off_k), p.m * ws_ld, splits, p.c, p.ldc, (uint32_t)p.m,
+                                  (uint32_t)p.n, ws_ld, p.accumulate, g.stream);
+        if (st != ST_OK) return st;
+    }
+    return ST_OK;
+}
+
+static int run_problem(const Problem &p) {
+    if (!ready()) return g.init_status;
+    if (p.m == 0 || p.n == 0 || p.batch == 0) return ST_OK;
+    if (!p.a || !p.b || !p.c) { set_error("null operand"); return ST_GEMM; }
+    const bool f32f32 = p.dtype_a == DT_F32 && p.dtype_b == DT_F32;
+    bool want_tc = g.opt_path != 2 && p.k > 0;
+    if (f32f32 && !g.opt_f32_tc && g.opt_path != 1) want_tc = false;
+    // tiny problems: one FFMA CTA beats building three tensor maps
+    if (g.opt_path == 0 && (uint64_t)p.m * p.n * p.k * p.batch <= (uint64_t)64 * 64 * 64) want_tc = false;
+    if (want_tc) {
+        int st = run_tc(p);
+        if (st == ST_OK) return ST_OK;
+        if (st != ST_UNSUPPORTED || g.opt_path == 1) return st;
+    }
+    return run_simt(p);
+}
+
+static bool is_device_ptr(const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+// Host-pointer pg_gemm_ex: stage compact copies through device memory.
+static int gemm_ex_host(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+                        float *c, size_t ldc) {
+    const size_t es = esize(dtype);
+    const size_t k8 = align_up(k, 8), n8 = align_up(n, 8), n4 = align_up(n, 4);
+    int st;
+    if ((st = grow(g.stage_a, m * k8 * es + 256)) != ST_OK) return st;
+    if ((st = grow(g.stage_b, k * n8 * es + 256)) != ST_OK) return st;
+    if ((st = grow(g.stage_c, m * n4 * 4 + 256)) != ST_OK) return st;
+    cudaError_t e;
+    if (k) {
+        e = cudaMemcpy2DAsync(g.stage_a.ptr, k8 * es, a, lda * es, k * es, m, cudaMemcpyHostToDevice, g.stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(g.stage_b.ptr, n8 * es, b, ldb * es, n * es, k, cudaMemcpyHostToDevice, g.stream);
+        if (e != cudaSuccess) { set_error("H2D staging failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_COPY; }
+    }
+    Problem p = {dtype, dtype, 0, 0, 1, m, n, k, g.stage_a.ptr, k8, 0, g.stage_b.ptr, n8, 0,
+                 (float *)g.stage_c.ptr, n4, 0, 0};
+    st = run_problem(p);
+    if (st != ST_OK) return st;
+    e = cudaMemcpy2DAsync(c, ldc * 4, g.stage_c.ptr, n4 * 4, n * 4, m, cudaMemcpyDeviceToHost, g.stream);
+    if (e != cudaSuccess) { set_error("D2H staging failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_COPY; }
+    if (cudaStreamSynchronize(g.stream) != cudaSuccess) { set_error("sync after staged GEMM failed"); cudaGetLastError(); return ST_SYNC; }
+    return ST_OK;
+}
+
+static int gemm_ex_any(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+                       float *c, size_t ldc) {
+    if (!ready()) return g.init_status;
+    if (dtype != DT_F32 && dtype != DT_F16 && dtype != DT_BF16) { set_error("bad dtype %d", dtype); return ST_UNSUPPORTED; }
+    if (m == 0 || n == 0) return ST_OK;
+    const bool da = is_device_ptr(a), db = is_device_ptr(b), dc = is_device_ptr(c);
+    if (da && db && dc) {
+        Problem p = {dtype, dtype, 0, 0, 1, m, n, k, a, lda, 0, b, ldb, 0, c, ldc, 0, 0};
+        return run_problem(p);
+    }
+    if (!da && !db && !dc) return gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc);
+    set_error("pg_gemm_ex: A, B and C must all be device pointers or all host pointers");
+    return ST_UNSUPPORTED;
+}
+
+}  // namespace pgb
+
+using namespace pgb;
+
+extern "C" {
+
+int pg_b200_init(void) { return do_init(); }
+
+int pg_b200_set_device(int ordinal) {
+    if (g.tried && g.init_status == ST_OK && ordinal != g.device) {
+        set_error("pg_b200_set_device after init: the library is bound to device %d", g.device);
+        return ST_UNSUPPORTED;
+    }
+    if (ordinal < 0) return ST_UNSUPPORTED;
+    g.device = ordinal;
+    return ST_OK;
+}
+
+int pg_b200_set_stream(void *stream) {
+    g.stream = (cudaStream_t)stream;
+    return ST_OK;
+}
+
+void *pg_b200_malloc(size_t nbytes) {
+    if (!ready()) return nullptr;
+    void *p = nullptr;
+    if (cudaMalloc(&p, nbytes ? nbytes : 1) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("cudaMalloc(%zu) failed", nbytes);
+        return nullptr;
+    }
+    return p;
+}
+
+void pg_b200_free(void *p) {
+    if (p && ready()) cudaFree(p);
+}
+
+int pg_b200_copy_h2d(void *dst, const void *src, size_t nbytes) {
+    if (!ready()) return ST_COPY;
+    if (!nbytes) return ST_OK;
+    cudaError_t e = cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyHostToDevice, g.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
+    if (e != cudaSuccess) { set_error("copy_h2d: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_COPY; }
+    return ST_OK;
+}
+
+int pg_b200_copy_d2h(void *dst, const void *src, size_t nbytes) {
+    if (!ready()) return ST_COPY;
+    if (!nbytes) return ST_OK;
+    cudaError_t e = cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, g.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
+    if (e != cudaSuccess) { set_error("copy_d2h: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_COPY; }
+    return ST_OK;
+}
+
+int pg_b200_sync(void) {
+    if (!ready()) return ST_SYNC;
+    cudaError_t e = cudaMemcpyAsync(g.host_status, g.dev_status, 4, cudaMemcpyDeviceToHost, g.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
+    if (e != cudaSuccess) { set_error("sync: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_SYNC; }
+    if (*g.host_status) {
+        set_error("a GEMM kernel gave up waiting (status bits 0x%x)", *g.host_status);
+        *g.host_status = 0;
+        cudaMemsetAsync(g.dev_status, 0, 4, g.stream);
+        cudaStreamSynchronize(g.stream);
+        return ST_GEMM;
+    }
+    return ST_OK;
+}
+
+void pg_b200_gemm(size_t m, size_t n, size_t k, const float *a, size_t lda, const float *b, size_t ldb, float *c,
+                  size_t ldc) {
+    int st = gemm_ex_any(DT_F32, m, n, k, a, lda, b, ldb, c, ldc);
+    if (st != ST_OK && getenv("PG_B200_DEBUG")) fprintf(stderr, "pg_b200_gemm failed: %d %s\n", st, g.err);
+}
+void pg_b200_hgemm(size_t m, size_t n, size_t k, const uint16_t *a, size_t lda, const uint16_t *b, size_t ldb,
+                   float *c, size_t ldc) {
+    int st = gemm_ex_any(DT_F16, m, n, k, a, lda, b, ldb, c, ldc);
+    if (st != ST_OK && getenv("PG_B200_DEBUG")) fprintf(stderr, "pg_b200_hgemm failed: %d %s\n", st, g.err);
+}
+void pg_b200_bgemm(size_t m, size_t n, size_t k, const uint16_t *a, size_t lda, const uint16_t *b, size_t ldb,
+                   float *c, size_t ldc) {
+    int st = gemm_ex_any(DT_BF16, m, n, k, a, lda, b, ldb, c, ldc);
+    if (st != ST_OK && getenv("PG_B200_DEBUG")) fprintf(stderr, "pg_b200_bgemm failed: %d %s\n", st, g.err);
+}
+int pg_b200_gemm_ex(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+                    float *c, size_t ldc) {
+    return gemm_ex_any(dtype, m, n, k, a, lda, b, ldb, c, ldc);
+}
+
+int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int trans_b, size_t batch, size_t m, size_t n,
+                         size_t k, const void *a, size_t lda, size_t stride_a, const void *b, size_t ldb,
+                         size_t stride_b, float *c, size_t ldc, size_t stride_c, int accumulate) {
+    for (int dt : {dtype_a, dtype_b})
+        if (dt != DT_F32 && dt != DT_F16 && dt != DT_BF16) { set_error("bad dtype %d", dt); return ST_UNSUPPORTED; }
+    Problem p = {dtype_a, dtype_b, trans_a ? 1 : 0, trans_b ? 1 : 0, batch, m, n, k, a, lda, stride_a,
+                 b, ldb, stride_b, c, ldc, stride_c, accumulate ? 1 : 0};
+    return run_problem(p);
+}
+
+int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t k, const void *a, const void *b,
+                            int b_batched, const float *gr, float *ga, float *gb) {
+    if (!ready()) return g.init_status;
+    int st = ST_OK;
+    if (ga) {
+        // ga[batch][m][k] += g[batch][m][n] * B^T : the product's "A" is g (m x n), its "B" is B (stored
+        // k x n) read transposed.  A B shared by the batch folds the batch into the rows of g and ga.
+        Problem p = {DT_F32, dtype, 0, 1, batch, m, k, n, gr, n, m * n, b, n, k * n, ga, k, m * k, 1};
+        if (!b_batched) { p.batch = 1; p.m = batch * m; p.stride_a = p.stride_b = p.stride_c = 0; }
+        st = run_problem(p);
+        if (st != ST_OK) return st;
+    }
+    if (gb) {
+        if (b_batched || batch == 1) {
+            // gb[batch][k][n] += A^T[batch][k][m] * g[batch][m][n]
+            Problem p = {dtype, DT_F32, 1, 0, batch, k, n, m, a, k, m * k, gr, n, m * n, gb, n, k * n, 1};
+            st = run_problem(p);
+        } else {
+            // B shared by the batch: gb[k][n] += sum_b A[b]^T g[b]  ==  one product with the batch folded into the
+            // contraction: A as [(batch*m)][k], g as [(batch*m)][n]
+            Problem p = {dtype, DT_F32, 1, 0, 1, k, n, batch * m, a, k, 0, gr, n, 0, gb, n, 0, 1};
+            st = run_problem(p);
+        }
+    }
+    return st;
+}
+
+int pg_b200_softmax_rows(const float *src, float *out_f32, uint16_t *out16, int dtype16, size_t rows, size_t len) {
+    if (!ready()) return g.init_status;
+    if (len > 0xFFFFFFFFull) return ST_UNSUPPORTED;
+    return softmax_rows_launch(src, out_f32, out16, dtype16, rows, (uint32_t)len, g.stream);
+}
+int pg_b200_gelu(const float *src, float *out_f32, uint16_t *out16, int dtype16, size_t n) {
+    if (!ready()) return g.init_status;
+    return gelu_launch(src, out_f32, out16, dtype16, n, g.stream);
+}
+int pg_b200_gelu_grad(const float *x, const float *gy, float *out, size_t n) {
+    if (!ready()) return g.init_status;
+    return gelu_grad_launch(x, gy, out, n, g.stream);
+}
+int pg_b200_cast_f32(const float *src, uint16_t *dst, int dtype16, size_t n) {
+    if (!ready()) return g.init_status;
+    return cast_f32_launch(src, dst, n, dtype16, g.stream);
+}
+int pg_b200_fill_f32(float *dst, float value, size_t n) {
+    if (!ready()) return g.init_status;
+    return fill_f32_launch(dst, value, n, g.stream);
+}
+
+const char *pg_b200_last_error(void) { return g.err; }
+const char *pg_b200_last_path(void) { return g.last_path; }
+uint64_t pg_b200_launch_count(void) { return g.launches; }
+int pg_b200_num_tile_configs(void) { return tc_num_configs(); }
+const char *pg_b200_tile_config_name(int index) { return tc_config_name(index); }
+
+int pg_b200_set_option(const char *name, int value) {
+    if (!name) return ST_UNSUPPORTED;
+    if (!strcmp(name, "path")) { g.opt_path = value; return ST_OK; }
+    if (!strcmp(name, "tile_config")) { g.opt_cfg = value; return ST_OK; }
+    if (!strcmp(name, "epilogue")) { g.opt_epilogue = value; return ST_OK; }
+    if (!strcmp(name, "k_splits")) { g.opt_splits = value; return ST_OK; }
+    if (!strcmp(name, "f32_parts")) { if (value != 2 && value != 3) return ST_UNSUPPORTED; g.opt_f32_parts = value; return ST_OK; }
+    if (!strcmp(name, "f32_tensor_cores")) { g.opt_f32_tc = value ? 1 : 0; return ST_OK; }
+    set_error("unknown option %s", name);
+    return ST_UNSUPPORTED;
+}
+
+}  // extern "C"

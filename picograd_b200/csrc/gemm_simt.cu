@@ -1,0 +1,157 @@
+// FFMA GEMM for everything the tensor-core kernel does not take: f32 operands
+// (picograd's pg_gemm, backend/backend.c:134-148, whose CUDA kernel is
+// backend/cuda/kernels/kernel_sgemm.c:50-111), leading dimensions or pointers
+// that break the TMA alignment rules, and tiny shapes.
+//
+// Every C element is one fused-multiply-add chain over k ascending on exactly
+// upcast operands — the same arithmetic as picograd's CPU micro-kernels
+// (backend/cpu/asm/sgemm_avx512.S:126-154), so results agree with them bit for
+// bit, not merely within tolerance.  No TF32, no reordering.
+//
+// Tiling: 256 threads, a TILE x TILE block of C per CTA, (TILE/16)^2 outputs per
+// thread, K in slabs of 16 staged through shared memory.  Operands are read
+// through generic (row, column, batch) element strides, so transposed views and
+// mixed dtypes need no separate kernel.
+
+#include "pg_internal.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace pgb {
+
+struct SimtParams {
+    uint32_t M, N, K, batch;
+    const void *A; long long a_rs, a_cs, a_bs;
+    const void *B; long long b_rs, b_cs, b_bs;
+    float *C; long long ldc, c_bs;
+    int dtype_a, dtype_b, accumulate;
+};
+
+__device__ __forceinline__ float load_as_f32(const void *base, long long idx, int dtype) {
+    if (dtype == DT_F32) return reinterpret_cast<const float *>(base)[idx];
+    const unsigned short raw = reinterpret_cast<const unsigned short *>(base)[idx];
+    if (dtype == DT_BF16) return __uint_as_float((unsigned)raw << 16);
+    return __half2float(__ushort_as_half(raw));
+}
+
+constexpr int SK = 16;
+
+template <int TILE>
+__global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
+    constexpr int T = TILE / 16;              // outputs per thread per dimension
+    __shared__ float As[SK][TILE + 1];
+    __shared__ float Bs[SK][TILE + 1];
+
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const uint32_t bz = blockIdx.z;
+    const long long m0 = (long long)blockIdx.y * TILE, n0 = (long long)blockIdx.x * TILE;
+    const char *Ab = reinterpret_cast<const char *>(p.A);
+    const char *Bb = reinterpret_cast<const char *>(p.B);
+    const long long a_off = (long long)bz * p.a_bs, b_off = (long long)bz * p.b_bs;
+    (void)Ab; (void)Bb;
+
+    float acc[T][T];
+#pragma unroll
+    for (int i = 0; i < T; ++i)
+#pragma unroll
+        for (int j = 0; j < T; ++j) acc[i][j] = 0.0f;
+
+    // walk the contiguous dimension with consecutive threads
+    const bool a_k_contig = (p.a_cs == 1);
+    const bool b_n_contig = (p.b_cs == 1);
+
+    for (uint32_t k0 = 0; k0 < p.K; k0 += SK) {
+        for (int idx = tid; idx < TILE * SK; idx += 256) {
+            int kk, mm;
+            if (a_k_contig) { kk = idx % SK; mm = idx / SK; } else { mm = idx % TILE; kk = idx / TILE; }
+            const long long gm = m0 + mm, gk = (long long)k0 + kk;
+            float v = 0.0f;
+            if (gm < p.M && gk < p.K) v = load_as_f32(p.A, a_off + gm * p.a_rs + gk * p.a_cs, p.dtype_a);
+            As[kk][mm] = v;
+        }
+        for (int idx = tid; idx < TILE * SK; idx += 256) {
+            int kk, nn;
+            if (b_n_contig) { nn = idx % TILE; kk = idx / TILE; } else { kk = idx % SK; nn = idx / SK; }
+            const long long gn = n0 + nn, gk = (long long)k0 + kk;
+            float v = 0.0f;
+            if (gn < p.N && gk < p.K) v = load_as_f32(p.B, b_off + gk * p.b_rs + gn * p.b_cs, p.dtype_b);
+            Bs[kk][nn] = v;
+        }
+        __syncthreads();
+        const int kmax = (p.K - k0) < (uint32_t)SK ? (int)(p.K - k0) : SK;
+        if (kmax == SK) {
+#pragma unroll
+            for (int kk = 0; kk < SK; ++kk) {
+                float a[T], b[T];
+#pragma unroll
+                for (int i = 0; i < T; ++i) a[i] = As[kk][ty + 16 * i];
+#pragma unroll
+                for (int j = 0; j < T; ++j) b[j] = Bs[kk][tx + 16 * j];
+#pragma unroll
+                for (int i = 0; i < T; ++i)
+#pragma unroll
+                    for (int j = 0; j < T; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+            }
+        } else {
+            // K tail: stop at the true K so that no "+ 0*0" step is added to the chain
+            for (int kk = 0; kk < kmax; ++kk) {
+#pragma unroll
+                for (int i = 0; i < T; ++i)
+#pragma unroll
+                    for (int j = 0; j < T; ++j)
+                        acc[i][j] = __fmaf_rn(As[kk][ty + 16 * i], Bs[kk][tx + 16 * j], acc[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+
+    float *Cb = p.C + (long long)bz * p.c_bs;
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+        const long long gm = m0 + ty + 16 * i;
+        if (gm >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+            const long long gn = n0 + tx + 16 * j;
+            if (gn >= p.N) continue;
+            float *dst = Cb + gm * p.ldc + gn;
+            *dst = p.accumulate ? (*dst + acc[i][j]) : acc[i][j];
+        }
+    }
+}
+
+int simt_gemm_launch(const SimtGemm &g) {
+    if (g.M == 0 || g.N == 0 || g.batch == 0) return ST_OK;
+    SimtParams p;
+    p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.batch;
+    p.A = g.A; p.a_rs = g.a_rs; p.a_cs = g.a_cs; p.a_bs = g.a_bs;
+    p.B = g.B; p.b_rs = g.b_rs; p.b_cs = g.b_cs; p.b_bs = g.b_bs;
+    p.C = g.C; p.ldc = g.ldc; p.c_bs = g.c_bs;
+    p.dtype_a = g.dtype_a; p.dtype_b = g.dtype_b; p.accumulate = g.accumulate;
+    // grid.z is limited to 65535: launch the batch in slices
+    const bool big = (uint64_t)g.M * g.N >= (uint64_t)512 * 512 * 4;
+    const int tile = big ? 128 : 64;
+    uint32_t done = 0;
+    while (done < g.batch) {
+        uint32_t nb = g.batch - done < 65535u ? g.batch - done : 65535u;
+        SimtParams q = p;
+        q.batch = nb;
+        const size_t esa = g.dtype_a == DT_F32 ? 4 : 2, esb = g.dtype_b == DT_F32 ? 4 : 2;
+        q.A = (const char *)g.A + (long long)done * g.a_bs * (long long)esa;
+        q.B = (const char *)g.B + (long long)done * g.b_bs * (long long)esb;
+        q.C = g.C + (long long)done * g.c_bs;
+        dim3 grid((g.N + tile - 1) / tile, (g.M + tile - 1) / tile, nb);
+        if (grid.y > 65535u) { set_error("simt gemm: M too large for one launch"); return ST_UNSUPPORTED; }
+        if (big) simt_gemm_kernel<128><<<grid, 256, 0, g.stream>>>(q);
+        else simt_gemm_kernel<64><<<grid, 256, 0, g.stream>>>(q);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { set_error("simt gemm launch: %s", cudaGetErrorString(e)); return ST_GEMM; }
+        note_launch();
+        done += nb;
+    }
+    return ST_OK;
+}
+
+}  // namespace pgb

@@ -1,0 +1,762 @@
+// Dense GEMM on the Blackwell tensor cores (sm_100a): C[f32] = A * B with 16-bit
+// (f16 / bf16) operands and f32 accumulation in tensor memory.
+//
+//   * tcgen05.mma (kind::f16) issued by one thread per CTA (or per CTA pair with
+//     cta_group::2), accumulators in TMEM, double-buffered so that the epilogue of
+//     one tile overlaps the main loop of the next.
+//   * Operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, no
+//     cluster multicast) into a ring of shared-memory stages guarded by mbarriers.
+//   * Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+//     warps 2..5 = epilogue (tcgen05.ld -> swizzled smem -> TMA store, or direct
+//     predicated stores when C does not satisfy the TMA alignment rules).
+//   * Persistent: each CTA (pair) walks a strided list of work units
+//     (batch x M-tile x N-tile x K-split) in an L2-friendly grouped order.
+//   * Either operand may be K-major or MN-major in memory (that is how the
+//     row-major NN product and the two transposed products of the backward pass
+//     are served without materialising a transpose), and the K loop may run
+//     several "passes" over different bf16 pieces of an operand that was split
+//     from f32 (used by the backward pass and by the f32 GEMM).
+//   * Every mbarrier wait is bounded: after ~2 s it records a bit in the device
+//     status word, raises a CTA-wide abort flag and the CTA drains and exits.
+//
+// This implements the device side of pg_gemm_ex for f16/bf16
+// (picograd backend/backend.c:150-177; the CUDA seat backend/cuda/cuda.c:282-291
+// leaves hgemm/bgemm/gemm_ex NULL — this kernel is what fills them).
+
+#include "pg_internal.h"
+
+#include <stdio.h>
+
+namespace pgb {
+
+// ---------------------------------------------------------------------------------------------
+// Tile constants
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t BM_CTA = 128;                 // C rows per CTA == TMEM lanes
+constexpr uint32_t BK = 64;                      // 64 x 16-bit = one 128-byte swizzle row
+constexpr uint32_t UMMA_K = 16;                  // K of one tcgen05.mma for 16-bit inputs
+constexpr uint32_t A_TILE_BYTES = BM_CTA * BK * 2;
+constexpr uint32_t EPI_WARPS = 4;
+constexpr uint32_t EPI_COLS = 32;                // columns per tcgen05.ld / per TMA-store box
+constexpr uint32_t EPI_BUF_BYTES = 32 * EPI_COLS * 4;
+constexpr uint32_t EPI_BUFS = 2;
+constexpr uint32_t NUM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr uint32_t SMEM_LIMIT = 232448;          // 227 KB opt-in maximum per CTA
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+template <int CG, int BN>
+struct Cfg {
+    static constexpr uint32_t BN_CTA = BN / CG;                      // B columns loaded by one CTA
+    static constexpr uint32_t B_TILE_BYTES = BN_CTA * BK * 2;
+    static constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    static constexpr uint32_t EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
+    static constexpr uint32_t BAR_BYTES = 512;
+    static constexpr uint32_t STAGES_RAW = (SMEM_LIMIT - 1024 - EPI_BYTES - BAR_BYTES) / STAGE_BYTES;
+    static constexpr uint32_t STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
+    static constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;                    // two accumulators
+    static_assert(STAGES >= 3, "pipeline too shallow");
+    static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
+    static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+};
+
+struct TcParams {
+    uint32_t M, N, K;
+    uint32_t batch, splits;
+    uint32_t m_tiles, n_tiles;
+    uint32_t k_blocks, kb_per_split;
+    uint32_t npass, a_sel, b_sel, a_nparts, b_nparts;
+    uint32_t a_mn, b_mn;          // operand is MN-major in memory
+    uint32_t idesc;               // tcgen05 instruction descriptor
+    uint32_t group_m;             // M tiles per rasterisation group
+    uint32_t epilogue_tma;        // 1: TMA-store epilogue, 0: direct stores
+    uint32_t accumulate;          // C += instead of C = (TMA reduce-add / read-modify-write)
+    uint32_t c_vec4;              // direct stores may use 16-byte vectors
+    float *C;
+    uint64_t ldc, c_stride;
+    uint32_t *status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bar is a shared::cluster address (possibly of the peer CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this or another wait ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t *status, uint32_t err_bit) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 0xFFu) == 0) {
+            if (*abort_flag) return false;
+            uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicOr(status, err_bit);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int CG>
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    else
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tmem_relinquish() {
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    else
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    else
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+template <int CG>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (CG == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on `bar` (same offset in every CTA of the pair) once all MMAs issued so far have completed.
+template <int CG>
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    if constexpr (CG == 1) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    } else {
+        const uint16_t mask = 3;  // both CTAs of the pair
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(bar), "h"(mask) : "memory");
+    }
+}
+
+// TMA tile load global -> shared, completion counted on `bar` (for CG == 2 the barrier of the
+// leader CTA, a shared::cluster address).
+template <int CG>
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int32_t c0, int32_t c1, int32_t c2) {
+    if constexpr (CG == 1)
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// C tile += smem tile, performed by the TMA unit in L2
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile (version 1 = Blackwell).
+//   K-major : rows of 64 elements (128 B), 8-row groups 1024 B apart (SBO), LBO unused.
+//   MN-major: [MN/64 chunks][BK k-rows][64 elements]; k-rows 128 B apart, 8-k groups 1024 B apart
+//             (SBO), chunks BK*128 B apart (LBO).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+struct WorkUnit {
+    uint32_t m_blk, n_blk, batch, split;
+    uint32_t kb_begin, kb_count;
+};
+
+__device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
+    WorkUnit w;
+    uint32_t t = u / p.splits;
+    w.split = u - t * p.splits;
+    uint32_t per_batch = p.m_tiles * p.n_tiles;
+    w.batch = t / per_batch;
+    uint32_t r = t - w.batch * per_batch;
+    uint32_t gsz = p.group_m * p.n_tiles;
+    uint32_t g = r / gsz;
+    uint32_t first_m = g * p.group_m;
+    uint32_t gm = p.m_tiles - first_m < p.group_m ? p.m_tiles - first_m : p.group_m;
+    uint32_t in_g = r - g * gsz;
+    w.m_blk = first_m + in_g % gm;
+    w.n_blk = in_g / gm;
+    w.kb_begin = w.split * p.kb_per_split;
+    uint32_t kb_end = w.kb_begin + p.kb_per_split;
+    if (kb_end > p.k_blocks) kb_end = p.k_blocks;
+    w.kb_count = kb_end - w.kb_begin;
+    return w;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+template <int CG, int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, const TcParams p) {
+    using C_ = Cfg<CG, BN>;
+    constexpr uint32_t STAGES = C_::STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t stage_base = smem_base;
+    const uint32_t epi_base = smem_base + STAGES * C_::STAGE_BYTES;
+    const uint32_t bar_base = epi_base + C_::EPI_BYTES;
+    auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+    auto tmem_full_bar = [&](uint32_t s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto tmem_empty_bar = [&](uint32_t s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+    const uint32_t abort_off = (bar_base - smem_base) + 8u * (2 * STAGES + 4) + 8u;
+    volatile uint32_t *tmem_slot_gen = (volatile uint32_t *)(smem_gen + (tmem_slot - smem_base));
+    volatile uint32_t *abort_flag = (volatile uint32_t *)(smem_gen + abort_off);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0;
+    const uint32_t cluster_id = blockIdx.x / CG;
+    const uint32_t num_clusters = gridDim.x / CG;
+    const uint32_t total_units = p.batch * p.m_tiles * p.n_tiles * p.splits;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        prefetch_tmap(&map_a);
+        prefetch_tmap(&map_b);
+        if (p.epilogue_tma) prefetch_tmap(&map_c);
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(tmem_full_bar(s), 1);
+            mbar_init(tmem_empty_bar(s), EPI_WARPS * CG);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<CG>(tmem_slot, C_::TMEM_COLS);
+        tmem_relinquish<CG>();
+    }
+    tc_fence_before();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        uint32_t stage = 0, phase = 0;
+        // barrier that counts the bytes of this stage: the leader CTA's when paired
+        bool ok = true;
+        for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
+            const WorkUnit w = decode_unit(p, u);
+            const int32_t m0 = (int32_t)(w.m_blk * BM_CTA * CG + cta_rank * BM_CTA);
+            const int32_t n0 = (int32_t)(w.n_blk * BN + cta_rank * C_::BN_CTA);
+            for (uint32_t pass = 0; pass < p.npass && ok; ++pass) {
+                const int32_t za = (int32_t)(w.batch * p.a_nparts + ((p.a_sel >> (4 * pass)) & 0xF));
+                const int32_t zb = (int32_t)(w.batch * p.b_nparts + ((p.b_sel >> (4 * pass)) & 0xF));
+                for (uint32_t kb = 0; kb < w.kb_count; ++kb) {
+                    ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const int32_t k0 = (int32_t)((w.kb_begin + kb) * BK);
+                        const uint32_t sa = stage_base + stage * C_::STAGE_BYTES;
+                        const uint32_t sb = sa + A_TILE_BYTES;
+                        uint32_t bar = full_bar(stage);
+                        if constexpr (CG == 2) bar = mapa(bar, 0);
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C_::STAGE_BYTES * CG);
+                        if (!p.a_mn) {
+                            tma_load_3d<CG>(sa, &map_a, bar, k0, m0, za);
+                        } else {
+#pragma unroll
+                            for (uint32_t c = 0; c < BM_CTA / 64; ++c)
+                                tma_load_3d<CG>(sa + c * (BK * 128), &map_a, bar, m0 + (int32_t)(c * 64), k0, za);
+                        }
+                        if (!p.b_mn) {
+                            tma_load_3d<CG>(sb, &map_b, bar, k0, n0, zb);
+                        } else {
+#pragma unroll
+                            for (uint32_t c = 0; c < C_::BN_CTA / 64; ++c)
+                                tma_load_3d<CG>(sb + c * (BK * 128), &map_b, bar, n0 + (int32_t)(c * 64), k0, zb);
+                        }
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (cta_rank == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            const uint32_t a_lbo = p.a_mn ? BK * 128 : 0;
+            const uint32_t b_lbo = p.b_mn ? BK * 128 : 0;
+            const uint32_t a_kstep = p.a_mn ? UMMA_K * 128 : UMMA_K * 2;
+            const uint32_t b_kstep = p.b_mn ? UMMA_K * 128 : UMMA_K * 2;
+            bool ok = true;
+            for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
+                const WorkUnit w = decode_unit(p, u);
+                ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t iters = p.npass * w.kb_count;
+                for (uint32_t it = 0; it < iters; ++it) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, DEV_ERR_WAIT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t sa = stage_base + stage * C_::STAGE_BYTES;
+                        const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+                        for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
+                            const uint64_t da = make_desc(sa + kk * a_kstep, a_lbo);
+                            const uint64_t db = make_desc(sb + kk * b_kstep, b_lbo);
+                            umma<CG>(d_tmem, da, db, p.idesc, (it | kk) ? 1u : 0u);
+                        }
+                        umma_commit<CG>(empty_bar(stage));          // frees the smem stage
+                        if (it + 1 == iters) umma_commit<CG>(tmem_full_bar(acc));  // accumulator complete
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const uint32_t q = warp & 3;                    // TMEM lane quadrant this warp may read
+        const uint32_t ew = warp - 2;                   // staging buffer owner index
+        const uint32_t my_epi = epi_base + ew * EPI_BUFS * EPI_BUF_BYTES;
+        uint8_t *my_epi_gen = smem_gen + (my_epi - smem_base);
+        uint32_t acc = 0, acc_phase = 0;
+        uint32_t buf = 0;
+        bool ok = true;
+        for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
+            const WorkUnit w = decode_unit(p, u);
+            ok = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t row0 = w.m_blk * BM_CTA * CG + cta_rank * BM_CTA + q * 32;  // first row of this warp
+            const uint32_t col0 = w.n_blk * BN;
+            const uint32_t zc = p.splits > 1 ? w.split : w.batch;
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN / EPI_COLS; ++c) {
+                const uint32_t col = col0 + c * EPI_COLS;
+                if (col >= p.N || row0 >= p.M) break;   // nothing of this warp's slab is inside C
+                uint32_t v[32];
+                tmem_ld32(taddr + c * EPI_COLS, v);
+                tmem_ld_wait();
+                if (p.epilogue_tma) {
+                    // the store issued two chunks ago must have finished reading this buffer
+                    if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
+                    __syncwarp();
+                    uint8_t *dst = my_epi_gen + buf * EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        uint4 val = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        *reinterpret_cast<uint4 *>(dst + ((j ^ (lane & 7)) << 4)) = val;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (p.accumulate)
+                            tma_reduce_add_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc);
+                        else
+                            tma_store_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc);
+                        tma_store_commit();
+                    }
+                    buf ^= 1;
+                } else {
+                    const uint32_t row = row0 + lane;
+                    if (row < p.M) {
+                        float *crow = p.C + (uint64_t)zc * p.c_stride + (uint64_t)row * p.ldc + col;
+                        if (p.accumulate) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 32; ++j)
+                                if (col + j < p.N) crow[j] += __uint_as_float(v[j]);
+                        } else if (p.c_vec4 && col + EPI_COLS <= p.N) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 8; ++j)
+                                *reinterpret_cast<uint4 *>(crow + 4 * j) =
+                                    make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (uint32_t j = 0; j < 32; ++j)
+                                if (col + j < p.N) crow[j] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+            // all TMEM reads of this accumulator are done: hand it back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t bar = tmem_empty_bar(acc);
+                if constexpr (CG == 2) {
+                    mbar_arrive_cluster(mapa(bar, 0));
+                } else {
+                    mbar_arrive(bar);
+                }
+            }
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+        if (lane == 0) tma_store_wait_all();
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CG>(tmem_base, C_::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+struct TcConfig {
+    const char *name;
+    int cg, bn;
+    uint32_t smem;
+    const void *fn;
+};
+
+static const TcConfig g_cfgs[] = {
+    {"1cta_128x256", 1, 256, Cfg<1, 256>::SMEM_BYTES, (const void *)tc_gemm_kernel<1, 256>},
+    {"1cta_128x128", 1, 128, Cfg<1, 128>::SMEM_BYTES, (const void *)tc_gemm_kernel<1, 128>},
+    {"1cta_128x64", 1, 64, Cfg<1, 64>::SMEM_BYTES, (const void *)tc_gemm_kernel<1, 64>},
+    {"2cta_256x256", 2, 256, Cfg<2, 256>::SMEM_BYTES, (const void *)tc_gemm_kernel<2, 256>},
+    {"2cta_256x128", 2, 128, Cfg<2, 128>::SMEM_BYTES, (const void *)tc_gemm_kernel<2, 128>},
+};
+constexpr int NUM_CFGS = sizeof(g_cfgs) / sizeof(g_cfgs[0]);
+
+int tc_num_configs() { return NUM_CFGS; }
+const char *tc_config_name(int cfg) { return (cfg >= 0 && cfg < NUM_CFGS) ? g_cfgs[cfg].name : "?"; }
+
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+bool tc_gemm_supported(const TcGemm &g) {
+    if (g.dtype != DT_F16 && g.dtype != DT_BF16) return false;
+    if (g.M == 0 || g.N == 0 || g.K == 0 || g.batch == 0) return false;
+    const TcOperand *ops[2] = {&g.A, &g.B};
+    for (const TcOperand *o : ops) {
+        if (!aligned16(o->ptr)) return false;
+        if (o->ld % 8) return false;
+        if ((uint64_t)g.batch * o->nparts > 1 && (o->z_stride % 8)) return false;
+        if (o->ld * 2 >= (1ull << 40)) return false;
+    }
+    if ((uint64_t)g.batch * g.A.nparts > 0x7FFFFFFFull || (uint64_t)g.batch * g.B.nparts > 0x7FFFFFFFull) return false;
+    if (g.splits > 1 && g.batch != 1) return false;
+    if (g.npass < 1 || g.npass > 8) return false;
+    return true;
+}
+
+static int encode_operand(CUtensorMap *map, const TcOperand &o, int dtype, uint32_t mn_extent, uint32_t K,
+                          uint32_t z, uint32_t mn_box_rows) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return ST_UNSUPPORTED;
+    CUtensorMapDataType dt = dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    cuuint64_t dims[3], strides[2];
+    cuuint32_t box[3], estr[3] = {1, 1, 1};
+    if (!o.mn_major) {
+        dims[0] = K; dims[1] = mn_extent; dims[2] = z;
+        box[0] = BK; box[1] = mn_box_rows; box[2] = 1;
+    } else {
+        dims[0] = mn_extent; dims[1] = K; dims[2] = z;
+        box[0] = 64; box[1] = BK; box[2] = 1;
+    }
+    strides[0] = o.ld * 2;
+    strides[1] = (z > 1 ? o.z_stride : o.ld * dims[1]) * 2;   // a single slice gets a harmless stride
+    CUresult r = enc(map, dt, 3, const_cast<void *>(o.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled(operand) failed: %d", (int)r);
+        return ST_GEMM;
+    }
+    return ST_OK;
+}
+
+static int encode_c(CUtensorMap *map, const TcGemm &g, uint32_t z) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return ST_UNSUPPORTED;
+    cuuint64_t dims[3] = {g.N, g.M, z};
+    uint64_t zs = z > 1 ? g.c_stride : g.ldc * g.M;
+    cuuint64_t strides[2] = {g.ldc * 4, zs * 4};
+    cuuint32_t box[3] = {EPI_COLS, 32, 1}, estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, g.C, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled(C) failed: %d", (int)r);
+        return ST_GEMM;
+    }
+    return ST_OK;
+}
+
+struct CfgRuntime {
+    bool ready = false;
+    bool usable = false;
+    int max_clusters = 0;   // co-resident clusters (CG == 2) or CTAs (CG == 1)
+};
+static CfgRuntime g_rt[8][NUM_CFGS];   // per device
+
+static const CfgRuntime &prepare_cfg(int cfg) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 8) dev = 0;
+    CfgRuntime &rt = g_rt[dev][cfg];
+    if (rt.ready) return rt;
+    rt.ready = true;
+    const TcConfig &c = g_cfgs[cfg];
+    cudaError_t e = cudaFuncSetAttribute(c.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
+    if (e != cudaSuccess) {
+        set_error("cudaFuncSetAttribute(%s, smem=%u): %s", c.name, c.smem, cudaGetErrorString(e));
+        cudaGetLastError();
+        return rt;
+    }
+    int sms = device_sm_count();
+    if (c.cg == 1) {
+        rt.max_clusters = sms;
+    } else {
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3((unsigned)(sms / 2 * 2), 1, 1);
+        lc.blockDim = dim3(NUM_THREADS, 1, 1);
+        lc.dynamicSmemBytes = c.smem;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        lc.attrs = at;
+        lc.numAttrs = 1;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, c.fn, &lc);
+        if (e != cudaSuccess || n <= 0) {
+            set_error("cudaOccupancyMaxActiveClusters(%s): %s", c.name, cudaGetErrorString(e));
+            cudaGetLastError();
+            return rt;
+        }
+        rt.max_clusters = n < sms / 2 ? n : sms / 2;
+    }
+    rt.usable = rt.max_clusters > 0;
+    return rt;
+}
+
+static uint32_t cdiv(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+// Pick a tile configuration: the 256x256 CTA-pair tile for large problems, narrower
+// tiles when that would leave SMs idle.
+static int choose_cfg(const TcGemm &g) {
+    if (g.force_cfg >= 0 && g.force_cfg < NUM_CFGS) return g.force_cfg;
+    const int sms = device_sm_count();
+    int best = 0;
+    double best_cost = 1e300;
+    for (int i = 0; i < NUM_CFGS; ++i) {
+        const TcConfig &c = g_cfgs[i];
+        const CfgRuntime &rt = prepare_cfg(i);
+        if (!rt.usable) continue;
+        uint64_t tiles = (uint64_t)g.batch * cdiv(g.M, BM_CTA * c.cg) * cdiv(g.N, c.bn) * (g.splits ? g.splits : 1);
+        uint64_t slots = (uint64_t)rt.max_clusters;
+        uint64_t waves = (tiles + slots - 1) / slots;
+        // time ~ waves * (MMA work per SM of one tile, padded) ; wider tiles stream less per flop
+        double per_tile = (double)BM_CTA * c.bn;                       // MMA columns*rows per SM
+        double eff = c.bn >= 256 ? 1.0 : (c.bn == 128 ? 0.92 : 0.80);  // narrower N wastes smem bandwidth
+        if (c.cg == 2) eff *= 1.04;                                   // pair halves B traffic per SM
+        double cost = (double)waves * per_tile / eff;
+        (void)sms;
+        if (cost < best_cost) { best_cost = cost; best = i; }
+    }
+    return best;
+}
+
+int tc_gemm_launch(const TcGemm &g) {
+    if (!tc_gemm_supported(g)) return ST_UNSUPPORTED;
+    const int cfg = choose_cfg(g);
+    const TcConfig &c = g_cfgs[cfg];
+    const CfgRuntime &rt = prepare_cfg(cfg);
+    if (!rt.usable) return ST_GEMM;
+
+    const uint32_t splits = g.splits ? g.splits : 1;
+    TcParams p = {};
+    p.M = g.M; p.N = g.N; p.K = g.K;
+    p.batch = g.batch;
+    p.m_tiles = cdiv(g.M, BM_CTA * c.cg);
+    p.n_tiles = cdiv(g.N, c.bn);
+    p.k_blocks = cdiv(g.K, BK);
+    p.kb_per_split = cdiv(p.k_blocks, splits);
+    p.splits = cdiv(p.k_blocks, p.kb_per_split);     // no empty slice
+    if (p.splits != splits) {
+        set_error("tc_gemm: %u K-splits leave an empty slice (k_blocks=%u)", splits, p.k_blocks);
+        return ST_GEMM;
+    }
+    p.npass = g.npass; p.a_sel = g.a_sel; p.b_sel = g.b_sel;
+    p.a_nparts = g.A.nparts; p.b_nparts = g.B.nparts;
+    p.a_mn = g.A.mn_major; p.b_mn = g.B.mn_major;
+    const uint32_t fmt = g.dtype == DT_BF16 ? 1u : 0u;
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+              ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(c.bn >> 3) << 17) |
+              ((uint32_t)((BM_CTA * c.cg) >> 4) << 24);
+    p.group_m = 8;
+    {
+        // keep one wave's footprint roughly square in elements: group_m * BM ~ slots/group_m * BN
+        uint32_t slots = (uint32_t)rt.max_clusters;
+        uint32_t bm = BM_CTA * c.cg;
+        uint32_t best = 1;
+        double best_cost = 1e300;
+        for (uint32_t gm = 1; gm <= 32 && gm <= p.m_tiles; ++gm) {
+            double cols = (double)slots / gm;
+            double cost = gm * (double)bm + cols * (double)c.bn;
+            if (cost < best_cost) { best_cost = cost; best = gm; }
+        }
+        p.group_m = best;
+    }
+    p.C = g.C; p.ldc = g.ldc; p.c_stride = g.c_stride;
+    p.accumulate = g.accumulate ? 1u : 0u;
+    p.status = g.dev_status;
+    const uint32_t zc = splits > 1 ? splits : g.batch;
+    bool c_tma_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (zc == 1 || g.c_stride % 4 == 0);
+    p.epilogue_tma = (g.force_epilogue >= 0) ? (uint32_t)(g.force_epilogue && c_tma_ok) : (c_tma_ok ? 1u : 0u);
+    p.c_vec4 = c_tma_ok ? 1u : 0u;
+
+    CUtensorMap ma, mb, mc;
+    int st = encode_operand(&ma, g.A, g.dtype, g.M, g.K, g.batch * g.A.nparts, BM_CTA);
+    if (st != ST_OK) return st;
+    st = encode_operand(&mb, g.B, g.dtype, g.N, g.K, g.batch * g.B.nparts, (uint32_t)(c.bn / c.cg));
+    if (st != ST_OK) return st;
+    if (p.epilogue_tma) {
+        st = encode_c(&mc, g, zc);
+        if (st != ST_OK) return st;
+    } else {
+        mc = ma;  // unused by the kernel
+    }
+
+    const uint64_t units = (uint64_t)g.batch * p.m_tiles * p.n_tiles * p.splits;
+    if (units > 0xFFFFFFFFull) return ST_UNSUPPORTED;
+    uint32_t clusters = (uint32_t)(units < (uint64_t)rt.max_clusters ? units : (uint64_t)rt.max_clusters);
+
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(clusters * c.cg, 1, 1);
+    lc.blockDim = dim3(NUM_THREADS, 1, 1);
+    lc.dynamicSmemBytes = c.smem;
+    lc.stream = g.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)c.cg;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    void *args[4] = {(void *)&ma, (void *)&mb, (void *)&mc, (void *)&p};
+    cudaError_t e = cudaLaunchKernelExC(&lc, c.fn, args);
+    if (e != cudaSuccess) {
+        set_error("launch %s failed: %s", c.name, cudaGetErrorString(e));
+        cudaGetLastError();
+        return ST_GEMM;
+    }
+    note_launch();
+    set_last_path("tc:%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "");
+    return ST_OK;
+}
+
+}  // namespace pgb

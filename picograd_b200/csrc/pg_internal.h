@@ -1,0 +1,107 @@
+// Internal declarations shared by the .cu files of libpg_b200.so.
+// Nothing here is part of the C-ABI (that is include/pg_b200.h).
+#pragma once
+
+#include <cuda.h>          // CUtensorMap and its enums only; no libcuda symbol is linked
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace pgb {
+
+// pg_status values of picograd (backend/backend.h:25-32)
+enum : int { ST_OK = 0, ST_UNSUPPORTED = -1, ST_ALLOC = -2, ST_COPY = -3, ST_SYNC = -4, ST_GEMM = -5 };
+// pg_dtype values of picograd (core/dtype.h:11-16)
+enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
+
+// Bits of the device status word a kernel ORs in when one of its bounded waits
+// gives up.  The host reads the word at pg_b200_sync() and maps any bit to
+// PG_ERR_GEMM.
+enum : uint32_t {
+    DEV_ERR_WAIT_EMPTY = 1u << 0,      // TMA producer: smem stage never freed
+    DEV_ERR_WAIT_FULL = 1u << 1,       // MMA issuer: TMA bytes never landed
+    DEV_ERR_WAIT_TMEM_EMPTY = 1u << 2, // MMA issuer: epilogue never drained TMEM
+    DEV_ERR_WAIT_TMEM_FULL = 1u << 3,  // epilogue: accumulator never completed
+};
+
+// One operand of the tensor-core GEMM as it lies in HBM.
+//   K-major  (mn_major = 0): element (r, k) at ptr[z*z_stride + r*ld + k]   (r = row of A / column of B)
+//   MN-major (mn_major = 1): element (r, k) at ptr[z*z_stride + k*ld + r]
+// z runs over batch * nparts (+ part); parts are the bf16 pieces an f32 operand
+// was split into, laid out one after the other.
+struct TcOperand {
+    const void *ptr;
+    uint64_t ld;        // elements
+    uint64_t z_stride;  // elements between consecutive z slices
+    uint32_t nparts;    // pieces per batch element (1 for a native 16-bit operand)
+    uint32_t mn_major;
+};
+
+struct TcGemm {
+    int dtype;                 // DT_F16 or DT_BF16 (both operands)
+    uint32_t M, N, K, batch;
+    TcOperand A, B;            // A: MN extent = M, B: MN extent = N
+    uint32_t npass;            // K passes; pass p multiplies part a_sel[p] of A with part b_sel[p] of B
+    uint32_t a_sel, b_sel;     // 4 bits per pass
+    float *C;
+    uint64_t ldc, c_stride;    // elements; c_stride between batch elements (or split-K slices)
+    int accumulate;            // C += A*B instead of C = A*B
+    uint32_t splits;           // >1: split-K, slice s goes to C + s*c_stride (batch must be 1)
+    int force_cfg;             // -1 = choose; else index into the config table
+    int force_epilogue;        // -1 = choose; 0 = direct stores; 1 = TMA stores
+    cudaStream_t stream;
+    uint32_t *dev_status;      // device status word
+};
+
+// Returns ST_OK if launched, ST_UNSUPPORTED if the shape/alignment cannot go
+// through TMA (caller then uses the SIMT kernel), ST_GEMM on a launch error.
+int tc_gemm_launch(const TcGemm &g);
+// true if operands satisfy the TMA rules (16-byte aligned bases and strides)
+bool tc_gemm_supported(const TcGemm &g);
+int tc_num_configs();
+const char *tc_config_name(int cfg);
+
+// Generic FFMA fallback: any dtype (per operand), any strides.
+struct SimtGemm {
+    int dtype_a, dtype_b;      // DT_*
+    uint32_t M, N, K, batch;
+    const void *A; int64_t a_rs, a_cs, a_bs;   // element strides: row (m), column (k), batch
+    const void *B; int64_t b_rs, b_cs, b_bs;   // row (k), column (n), batch
+    float *C; int64_t ldc, c_bs;
+    int accumulate;            // C += instead of C =
+    cudaStream_t stream;
+};
+int simt_gemm_launch(const SimtGemm &g);
+
+// Helper kernels (aux_kernels.cu)
+int split_f32_to_bf16_launch(const float *src, uint64_t ld_src, uint64_t src_bs,
+                             uint16_t *dst, uint64_t ld_dst, uint32_t rows, uint32_t cols,
+                             uint32_t batch, uint32_t nparts, cudaStream_t s);
+int split_f16_to_bf16_launch(const uint16_t *src, uint64_t ld_src, uint64_t src_bs,
+                             uint16_t *dst, uint64_t ld_dst, uint32_t rows, uint32_t cols,
+                             uint32_t batch, cudaStream_t s);
+int reduce_splits_launch(const float *ws, uint64_t slice_stride, uint32_t splits,
+                         float *c, uint64_t ldc, uint32_t M, uint32_t N, uint64_t ws_ld,
+                         int accumulate, cudaStream_t s);
+int add_inplace_launch(float *dst, const float *src, uint64_t n, cudaStream_t s);
+int cast_f32_launch(const float *src, uint16_t *dst, uint64_t n, int dtype, cudaStream_t s);
+int gelu_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16, uint64_t n, cudaStream_t s);
+int gelu_grad_launch(const float *x, const float *gy, float *out, uint64_t n, cudaStream_t s);
+int softmax_rows_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
+                        uint64_t rows, uint32_t len, cudaStream_t s);
+int fill_f32_launch(float *dst, float v, uint64_t n, cudaStream_t s);
+
+void set_error(const char *fmt, ...);
+void set_last_path(const char *fmt, ...);
+void note_launch(int n = 1);   // counts kernels launched by this library
+
+// cuTensorMapEncodeTiled, fetched through the runtime (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_tiled();
+
+int device_sm_count();
+
+}  // namespace pgb
