@@ -1,0 +1,308 @@
+#!/usr/bin/env python
+"""Headline benchmark: bf16 -> f32 pg_gemm_ex at M = N = K = 8192 on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one pass of the hot path over the whole 8192^3 product.  With N > 1 the product
+is partitioned by N-column shards of B and C (rank r owns columns [r*8192/N, (r+1)*8192/N)),
+A is replicated, and there is no collective in the timed path: total work is fixed, so the
+scaling is "strong".  Rank 0 prints ONE JSON line.
+
+Inputs are synthetic (seeded N(0,1) rounded to bf16, as the configuration specifies); A, B and
+C together are 512 MiB, larger than the 126 MB L2, so consecutive timed launches cannot be
+served from cache.
+
+`--impl reference` times picograd's own CPU implementation of the same call (the unmodified
+library compiled into oracle/_ref when that build travelled with the repository, else the C
+restatement in oracle/) on the host cores, each step a bounded row-slab of the same product.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+M = N = K = 8192
+FLOPS = 2.0 * M * N * K
+NOMINAL_BF16_TFLOPS = 2250.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+        except Exception:
+            pass
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        rows = [ln for (t, ln) in self.lines if t0 - 0.05 <= t <= t1 + 0.1] or [ln for (_, ln) in self.lines]
+        for ln in rows:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm (reference implementation on the host cores)
+# ------------------------------------------------------------------------------------------
+def cpu_gemm_fn():
+    """(callable(a_bits, b_bits) -> C, kind, threads)."""
+    import oracle_lib
+    ref = oracle_lib.reference()
+    if ref is not None:
+        return (lambda a, b: ref.gemm_ex(oracle_lib.BF16, a, b)), "reference", ref.threads()
+    if not os.path.exists(oracle_lib.oracle_path()):
+        subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "oracle"], stdout=subprocess.DEVNULL)
+    o = oracle_lib.oracle()
+    return (lambda a, b: o.gemm_ex(oracle_lib.BF16, a, b)), "port", o.threads()
+
+
+def cpu_time_rows(fn, a, b, rows):
+    t = time.perf_counter()
+    fn(a[:rows], b)
+    return time.perf_counter() - t
+
+
+def cpu_baseline(a, b, budget_s=15.0):
+    """Times the CPU implementation on a row-slab of the same product sized for ~budget_s."""
+    fn, kind, threads = cpu_gemm_fn()
+    probe = 64
+    t = cpu_time_rows(fn, a, b, probe)
+    rows = int(min(M, max(probe, probe * budget_s / max(t, 1e-3))))
+    rows = max(8, rows // 8 * 8)
+    t = cpu_time_rows(fn, a, b, rows)
+    tf = 2.0 * rows * N * K / t / 1e12
+    return {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+            "sample": f"rows [0,{rows}) of the 8192^3 bf16 product ({rows}x8192x8192), one run, {t:.2f} s"}
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    import workloads as wl
+    a, b = wl.config2(M, N, K)
+    fn, kind, threads = cpu_gemm_fn()
+    t = cpu_time_rows(fn, a, b, 64)
+    rows = int(min(M, max(8, 64 * 2.0 / max(t, 1e-3))))     # ~2 s per step
+    rows = max(8, rows // 8 * 8)
+    for _ in range(args.warmup):
+        cpu_time_rows(fn, a, b, rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn(a[:rows], b)
+    dt = (time.perf_counter() - t0) / args.steps
+    tf = 2.0 * rows * N * K / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "bf16->f32 GEMM TFLOP/s at M=N=K=8192", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "pg_gemm_ex(PG_DTYPE_BF16) M=N=K=8192, A,B~N(0,1) rounded to bf16, seed 1, C f32",
+                   "step": f"row-slab [0,{rows}) of the product per step on the host cores"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+                         "sample": f"{rows}x8192x8192 per step, {args.steps} steps"},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def run_ours(args, rank, world):
+    import torch
+    import workloads as wl
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import picograd_b200 as pg
+    pg.pg_set_device(local)
+
+    if N % world:
+        raise SystemExit(f"--gpus {world} does not divide N={N}")
+    n_loc = N // world
+    c0 = rank * n_loc
+    # every rank draws the same seeded matrices and keeps its column shard of B
+    a_bits, b_bits = wl.config2(M, N, K)
+    b_loc = np.ascontiguousarray(b_bits[:, c0:c0 + n_loc])
+    a_host = torch.from_numpy(a_bits.view(np.int16)).pin_memory()
+    b_host = torch.from_numpy(b_loc.view(np.int16)).pin_memory()
+    c_host = torch.empty((M, n_loc), dtype=torch.float32).pin_memory()
+    a_dev = a_host.cuda().view(torch.bfloat16)
+    b_dev = b_host.cuda().view(torch.bfloat16)
+    c_dev = torch.empty((M, n_loc), dtype=torch.float32, device="cuda")
+
+    def step():
+        pg.pg_gemm_ex(pg.PG_DTYPE_BF16, M, n_loc, K, a_dev, K, b_dev, n_loc, c_dev, n_loc)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    pg.pg_dev_sync()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    barrier()
+    launches0 = pg.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    launches = pg.launch_count() - launches0
+    ms = e0.elapsed_time(e1)
+    pg.pg_dev_sync()                                   # surfaces a kernel-side failure, if any
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    ms_per_step = ms / args.steps
+    tflops = FLOPS / (ms_per_step * 1e-3) / 1e12
+
+    # end to end through the reference-facing call with HOST buffers: H2D of A and the B shard,
+    # the GEMM, D2H of the C shard, every step
+    e2e_steps = max(2, min(args.steps, 5))
+    pg.pg_gemm_ex_host(pg.PG_DTYPE_BF16, M, n_loc, K, a_host, K, b_host, n_loc, c_host, n_loc)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        pg.pg_gemm_ex_host(pg.PG_DTYPE_BF16, M, n_loc, K, a_host, K, b_host, n_loc, c_host, n_loc)
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_tflops = FLOPS / e2e_s / 1e12
+
+    # spot-check the timed result against the device result of the staged call (same bytes)
+    same = bool(torch.equal(c_dev[:64].cpu(), c_host[:64]))
+
+    if rank == 0:
+        burst, sustained, src = measured_peaks()
+        line = {
+            "metric": "bf16->f32 GEMM TFLOP/s at M=N=K=8192", "value": tflops, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "pg_gemm_ex(PG_DTYPE_BF16) M=N=K=8192, A,B~N(0,1) rounded to bf16, seed 1, C f32",
+                       "partition": f"N-column shards of B and C, {n_loc} columns per GPU, A replicated, no collective",
+                       "l2": "A+B+C = 512 MiB per step > 126 MB L2 (inputs larger than L2, no flush needed)",
+                       "kernel": pg.last_path()},
+            "pct_of_nominal_peak": 100.0 * tflops / (NOMINAL_BF16_TFLOPS * world),
+            "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": burst, "unit": "TFLOP/s",
+                         "frac": tflops / world / burst, "traffic": None,
+                         "peak_source": f"{src} burst bf16 (kernel timed alone, back to back)",
+                         "frac_of_sustained": tflops / world / sustained},
+            "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": int((M * K + K * n_loc) * 2),
+                    "d2h_bytes_per_step": int(M * n_loc * 4), "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "staged_equals_resident": same,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(a_bits, b_bits)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world == 1 and args.gpus > 1:
+        # launched without torchrun: re-launch ourselves with one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 1000), os.path.abspath(__file__),
+               "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup), "--impl", args.impl]
+        if args.no_cpu_baseline:
+            cmd.append("--no-cpu-baseline")
+        sys.exit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

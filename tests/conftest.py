@@ -1,0 +1,49 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    import oracle_lib
+    if not os.path.exists(oracle_lib.oracle_path()):
+        import subprocess
+        subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "oracle"])
+    return oracle_lib.oracle()
+
+
+@pytest.fixture(scope="session")
+def reference():
+    """The compiled unmodified picograd library, or None when oracle/_ref was not built here."""
+    import oracle_lib
+    return oracle_lib.reference()
+
+
+@pytest.fixture(scope="session")
+def pg():
+    """The product's Python mirror, bound to cuda:0; fails loudly if the CUDA library is missing."""
+    import torch
+    assert torch.cuda.is_available(), "a -m gpu test needs a GPU"
+    import picograd_b200 as pg
+    pg.pg_set_device(0)
+    return pg
+
+
+@pytest.fixture(autouse=True)
+def _reset_options(request):
+    yield
+    if "gpu" in request.keywords:
+        import picograd_b200 as pg
+        for name, val in (("path", 0), ("tile_config", -1), ("epilogue", -1), ("k_splits", 0),
+                          ("f32_parts", 2), ("f32_tensor_cores", 0)):
+            pg.set_option(name, val)

@@ -1,0 +1,77 @@
+"""Generates tests/golden/reference_outputs.npz from the UNMODIFIED picograd CPU library.
+
+Run in a container that holds picograd's sources: `make -C oracle ref` compiles them into
+oracle/_ref/libpicograd_ref.so, then `python tests/golden/make_golden.py` calls its
+pg_gemm / pg_gemm_ex on small seeded inputs and stores inputs' seeds + outputs.  The committed
+.npz is what travels; the tests re-create the inputs from the seeds and compare our oracle
+(and, on a GPU, the CUDA path) with these reference outputs.
+
+The host CPU matters for one case: on AVX512-FP16 hosts picograd's f16 micro-kernel
+(backend/cpu/hgemm_avx512fp16.c:31-41) resets the accumulators of columns 0..15 of every
+32-column block at each 256-deep K block, so for K > 256 only columns 16..31 (mod 32) of its
+f16 output are an f32 accumulation over all of K.  `f16_valid_cols` records which columns of
+each f16 case are usable as golden values on the host that generated the file.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+import oracle_lib  # noqa: E402
+import workloads as wl  # noqa: E402
+
+CASES = [
+    # (name, dtype, m, n, k, seed)
+    ("f32_13x9x7", wl.F32, 13, 9, 7, 10),
+    ("f32_16x16x300", wl.F32, 16, 16, 300, 11),       # crosses the 256-deep K block (tests/test_ops.c:78-102)
+    ("f32_37x53x129", wl.F32, 37, 53, 129, 12),
+    ("f32_96x80x520", wl.F32, 96, 80, 520, 13),
+    ("bf16_13x9x7", wl.BF16, 13, 9, 7, 20),
+    ("bf16_40x72x256", wl.BF16, 40, 72, 256, 21),
+    ("bf16_64x96x600", wl.BF16, 64, 96, 600, 22),
+    ("f16_13x9x7", wl.F16, 13, 9, 7, 30),
+    ("f16_40x72x256", wl.F16, 40, 72, 256, 31),
+    ("f16_64x96x600", wl.F16, 64, 96, 600, 32),
+]
+
+
+def make_inputs(dtype, m, n, k, seed):
+    rng = np.random.default_rng(seed)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    if dtype == wl.BF16:
+        return wl.to_bf16_bits(a), wl.to_bf16_bits(b)
+    if dtype == wl.F16:
+        return wl.to_f16_bits(a), wl.to_f16_bits(b)
+    return a, b
+
+
+def main():
+    ref = oracle_lib.reference()
+    if ref is None:
+        raise SystemExit("oracle/_ref/libpicograd_ref.so not built: run `make -C oracle ref` first")
+    out = {}
+    for name, dt, m, n, k, seed in CASES:
+        a, b = make_inputs(dt, m, n, k, seed)
+        c = ref.gemm_ex(dt, a, b)
+        out[name] = c
+        if dt == wl.F16:
+            # detect the accumulator-reset columns by comparing with an f64 product
+            exact = wl.f16_bits_to_f32(a).astype(np.float64) @ wl.f16_bits_to_f32(b).astype(np.float64)
+            good = np.abs(c - exact).max(axis=0) < 1e-3
+            out[name + "_valid_cols"] = good
+    # picograd's own dyadic correctness data (benchmarks/bench_gemm_cuda.c:16-65), exact in f32
+    s = 64
+    d = wl.dyadic(s * s).reshape(s, s)
+    out["f32_dyadic64"] = ref.gemm_ex(wl.F32, d, d)
+    np.savez_compressed(os.path.join(HERE, "reference_outputs.npz"), **out)
+    print("wrote", len(out), "arrays; threads", ref.threads())
+    for kname in out:
+        if kname.endswith("_valid_cols"):
+            print(kname, int(out[kname].sum()), "of", out[kname].size)
+
+
+if __name__ == "__main__":
+    main()

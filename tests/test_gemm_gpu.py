@@ -1,0 +1,286 @@
+"""Parity of the CUDA path with the CPU oracle, through the C-ABI, on the same seeded bytes.
+
+Tolerances are the ones the path is specified with: normwise relative error <= 1e-6 for f32
+and <= 1e-5 * sqrt(K) for f16/bf16 inputs.  The FFMA kernel is additionally bit-exact.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import workloads as wl
+from golden.make_golden import CASES, make_inputs
+from gpu_util import bits_to_host, gemm_dev, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_outputs.npz")
+
+
+def test_library_is_the_cuda_one(pg):
+    from picograd_b200 import _lib
+    assert os.path.basename(_lib.LIB_PATH) == "libpg_b200.so"
+    n0 = pg.launch_count()
+    a = torch.ones(64, 64, device="cuda").bfloat16()
+    pg.pg_matmul(a, a); pg.pg_dev_sync()
+    assert pg.launch_count() > n0, "no kernel of ours was launched"
+
+
+def test_exact_case_from_test_backend(pg):
+    # tests/test_backend.c:91-95
+    v = torch.tensor([[1., 2.], [3., 4.]], device="cuda")
+    w = torch.tensor([[5.], [6.]], device="cuda")
+    r = pg.pg_matmul(v, w); pg.pg_dev_sync()
+    assert r.flatten().tolist() == [17.0, 39.0]
+
+
+def test_config1_f32_512_bit_exact(pg, oracle):
+    a, b = wl.config1(512)
+    want = oracle.gemm_ex(wl.F32, a, b)
+    got = to_host(pg.pg_matmul(to_dev(a, wl.F32), to_dev(b, wl.F32)))
+    pg.pg_dev_sync()
+    assert pg.last_path() == "simt"
+    assert wl.relerr(got, want) <= 1e-6
+    assert np.array_equal(got, want), "FFMA path: same fused chain over k as the CPU kernels"
+
+
+def test_f32_dyadic_exact_like_bench_gemm_cuda(pg):
+    # benchmarks/bench_gemm_cuda.c:16-65: max abs err 0 on dyadic data
+    s = 512
+    d = wl.dyadic(s * s).reshape(s, s)
+    got = gemm_dev(pg, wl.F32, d, d)
+    assert np.array_equal(got.astype(np.float64), d.astype(np.float64) @ d.astype(np.float64))
+
+
+def test_f32_on_tensor_cores_within_1e6(pg, oracle):
+    """f32 x f32 as three exact bf16 pieces per operand, six tensor-core passes."""
+    a, b = wl.config1(512)
+    want = oracle.gemm_ex(wl.F32, a, b)
+    pg.set_option("f32_tensor_cores", 1)
+    got = to_host(pg.pg_matmul(to_dev(a, wl.F32), to_dev(b, wl.F32)))
+    pg.pg_dev_sync()
+    assert pg.last_path().startswith("tc:")
+    assert wl.relerr(got, want) <= 1e-6
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_against_reference_outputs(pg, case):
+    """The committed outputs of the unmodified picograd CPU library."""
+    name, dt, m, n, k, seed = case
+    gold = np.load(GOLDEN)
+    a, b = make_inputs(dt, m, n, k, seed)
+    got = gemm_dev(pg, dt, a, b)
+    ref = gold[name]
+    cols = gold[name + "_valid_cols"] if dt == wl.F16 else np.ones(n, bool)
+    assert wl.relerr(got[:, cols], ref[:, cols]) <= wl.tolerance(dt, k)
+    if pg.last_path() == "simt" and dt != wl.BF16:
+        assert np.array_equal(got[:, cols], ref[:, cols])
+
+
+@pytest.mark.parametrize("dt", [wl.BF16, wl.F16])
+@pytest.mark.parametrize("shape", [(1024, 768, 512), (384, 1000, 1096), (130, 70, 4096)])
+@pytest.mark.parametrize("path", [1, 2], ids=["tensor", "ffma"])
+def test_gemm_ex_vs_oracle(pg, oracle, dt, shape, path):
+    m, n, k = shape
+    a, b = (wl.config2(m, n, k) if dt == wl.BF16 else wl.config3(m, n, k))
+    pad = lambda v: (v + 7) // 8 * 8
+    pg.set_option("path", path)
+    got = gemm_dev(pg, dt, a, b, lda=pad(k), ldb=pad(n), ldc=pad(n) + 4)
+    want = oracle.gemm_ex(dt, a, b)
+    assert pg.last_path().startswith("tc:" if path == 1 else "simt")
+    assert wl.relerr(got, want) <= wl.tolerance(dt, k)
+    if path == 2:
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("cfg", range(5))
+@pytest.mark.parametrize("epi", [0, 1])
+def test_every_tile_config(pg, oracle, cfg, epi):
+    a, b = wl.config2(520, 776, 328)
+    pg.set_option("path", 1); pg.set_option("tile_config", cfg); pg.set_option("epilogue", epi)
+    got = gemm_dev(pg, wl.BF16, a, b)
+    assert pg.last_path().startswith("tc:")
+    assert wl.relerr(got, oracle.gemm_ex(wl.BF16, a, b)) <= wl.tolerance(wl.BF16, 328)
+
+
+def test_config3b_skinny_split_k(pg, oracle):
+    """M = 16 decode-like shape at full size: one M tile, K split across CTAs, slices reduced."""
+    a, b = wl.config3(16, 4096, 4096)
+    got = gemm_dev(pg, wl.F16, a, b)
+    assert "splitk" in pg.last_path()
+    assert wl.relerr(got, oracle.gemm_ex(wl.F16, a, b)) <= wl.tolerance(wl.F16, 4096)
+
+
+SIZES = [1, 2, 3, 7, 8, 9, 16, 17, 127, 128, 129, 255, 256, 257]
+
+
+@pytest.mark.parametrize("path", [1, 2], ids=["tensor", "ffma"])
+def test_edge_shape_sweep(pg, oracle, path):
+    """Tile-edge sizes in each of M, N, K (the others held at an awkward size)."""
+    pg.set_option("path", path)
+    rng = np.random.default_rng(11)
+    pad = lambda v: (v + 7) // 8 * 8
+    for axis in range(3):
+        for s in SIZES:
+            shp = [72, 40, 136]
+            shp[axis] = s
+            m, n, k = shp
+            a = wl.to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32))
+            b = wl.to_bf16_bits(rng.standard_normal((k, n), dtype=np.float32))
+            if path == 1:
+                got = gemm_dev(pg, wl.BF16, a, b, lda=pad(k), ldb=pad(n), ldc=pad(n))
+                assert pg.last_path().startswith("tc:"), (shp, pg.last_path())
+            else:
+                got = gemm_dev(pg, wl.BF16, a, b, lda=k + 1, ldb=n + 3, ldc=n + 1)
+            want = oracle.gemm_ex(wl.BF16, a, b)
+            assert wl.relerr(got, want) <= wl.tolerance(wl.BF16, k), shp
+
+
+def test_unaligned_operands_fall_to_ffma_not_to_garbage(pg, oracle):
+    a, b = wl.config2(100, 90, 77)
+    got = gemm_dev(pg, wl.BF16, a, b)          # ld = 77 / 90: breaks the 16-byte stride rule of TMA
+    assert pg.last_path() == "simt"
+    assert np.array_equal(got, oracle.gemm_ex(wl.BF16, a, b))
+    pg.set_option("path", 1)
+    with pytest.raises(pg.PgError) as e:
+        gemm_dev(pg, wl.BF16, a, b)
+    assert e.value.status == -1                # PG_ERR_UNSUPPORTED: the dispatcher may then go elsewhere
+
+
+def test_empty_and_k0(pg):
+    c = torch.full((4, 4), 3.0, device="cuda")
+    a = torch.zeros(4, 8, device="cuda").bfloat16()
+    pg.pg_gemm_ex(wl.BF16, 0, 4, 8, a, 8, a, 4, c, 4)
+    pg.pg_gemm_ex(wl.BF16, 4, 0, 8, a, 8, a, 4, c, 4)
+    pg.pg_dev_sync()
+    assert torch.all(c == 3.0)
+    pg.pg_gemm_ex(wl.BF16, 4, 4, 0, a, 8, a, 4, c, 4)      # k = 0: C rows are zeroed (gemm.c:539)
+    pg.pg_dev_sync()
+    assert torch.all(c == 0.0)
+
+
+def test_host_pointer_gemm_ex(pg, oracle):
+    """pg_gemm_ex as ops/matmul.c:264-271 calls it: host buffers in, host buffer out."""
+    a, b = wl.config2(300, 200, 264)
+    c = np.full((300, 204), 0xAB, np.float32)
+    pg.pg_gemm_ex_host(wl.BF16, 300, 200, 264, a, 264, b, 200, c, 204)
+    assert np.all(c[:, 200:] == np.float32(0xAB))
+    assert wl.relerr(c[:, :200], oracle.gemm_ex(wl.BF16, a, b)) <= wl.tolerance(wl.BF16, 264)
+
+
+def test_matmul_shape_modes(pg):
+    """tests/test_ops.c:368-492: 2-D, vec.vec, vec.mat, mat.vec, bmm, batched.unbatched; 1e-4*(1+|y|)."""
+    rng = np.random.default_rng(12)
+    f = lambda *s: rng.uniform(-1, 1, s).astype(np.float32)
+    cases = [(f(5, 7), f(7, 3)), (f(7), f(7)), (f(7), f(7, 4)), (f(6, 7), f(7)), (f(3, 5, 7), f(3, 7, 2)),
+             (f(2, 3, 5, 7), f(7, 4)), (f(5, 7), f(4, 7, 6)), (f(2, 3, 4, 5), f(2, 3, 5, 6))]
+    for a, b in cases:
+        y = pg.pg_matmul(to_dev(a, wl.F32), to_dev(b, wl.F32)); pg.pg_dev_sync()
+        ref = np.matmul(a.astype(np.float64), b.astype(np.float64))
+        ref = ref.reshape(y.shape)
+        assert np.all(np.abs(to_host(y) - ref) <= 1e-4 * (1 + np.abs(ref))), (a.shape, b.shape)
+    # rejected like picograd does (ops/matmul.c:191-200)
+    assert pg.pg_matmul(to_dev(f(4, 5), wl.F32), to_dev(f(6, 4), wl.F32)) is None
+    assert pg.pg_matmul(to_dev(f(4, 5), wl.F32), to_dev(f(5, 4), wl.F32).bfloat16()) is None
+    assert pg.pg_bmm(to_dev(f(2, 4, 5), wl.F32), to_dev(f(3, 5, 4), wl.F32)) is None
+
+
+def test_tensordot(pg):
+    """tests/test_ops.c:451-484 shapes: contraction over one and over two axes."""
+    rng = np.random.default_rng(13)
+    a = rng.uniform(-1, 1, (3, 4, 5)).astype(np.float32)
+    b = rng.uniform(-1, 1, (5, 4, 6)).astype(np.float32)
+    y = pg.pg_tensordot(to_dev(a, wl.F32), to_dev(b, wl.F32), [2], [0]); pg.pg_dev_sync()
+    ref = np.tensordot(a.astype(np.float64), b.astype(np.float64), axes=([2], [0]))
+    assert np.all(np.abs(to_host(y) - ref) <= 1e-4 * (1 + np.abs(ref)))
+    y = pg.pg_tensordot(to_dev(a, wl.F32), to_dev(b, wl.F32), [1, 2], [1, 0]); pg.pg_dev_sync()
+    ref = np.tensordot(a.astype(np.float64), b.astype(np.float64), axes=([1, 2], [1, 0]))
+    assert np.all(np.abs(to_host(y) - ref) <= 1e-4 * (1 + np.abs(ref)))
+    ab = to_dev(wl.to_bf16_bits(a), wl.BF16); bb = to_dev(wl.to_bf16_bits(b), wl.BF16)
+    y = pg.pg_tensordot(ab, bb, [2], [0]); pg.pg_dev_sync()
+    ref = np.tensordot(ab.double().cpu().numpy(), bb.double().cpu().numpy(), axes=([2], [0]))
+    assert np.all(np.abs(to_host(y) - ref) <= 1e-4 * (1 + np.abs(ref)))
+
+
+def test_config4_attention_shaped_bmm(pg, oracle):
+    """Reduced config 4 (batch 4, seq 256, d 128).  Each GEMM is checked on identical input bytes:
+    P = bf16(softmax(S)) is produced once (on the device) and fed to both sides."""
+    q, kt, v = wl.config4(4, 256, 128)
+    qd, ktd, vd = (to_dev(x, wl.BF16) for x in (q, kt, v))
+    s = pg.pg_bmm(qd, ktd); pg.pg_dev_sync()
+    assert pg.last_path().startswith("tc:")
+    s_ref = oracle.bmm(wl.BF16, q, kt)
+    assert wl.relerr(to_host(s), s_ref) <= wl.tolerance(wl.BF16, 128)
+    from picograd_b200 import ops
+    p32, p16 = ops.softmax_rows(s, out16=torch.bfloat16); pg.pg_dev_sync()
+    assert np.abs(to_host(p32) - oracle.softmax_rows(to_host(s))).max() < 1e-6
+    p_bits = bits_to_host(p16)
+    assert np.array_equal(p_bits, wl.to_bf16_bits(to_host(p32)))
+    o = pg.pg_bmm(p16, vd); pg.pg_dev_sync()
+    o_ref = oracle.bmm(wl.BF16, p_bits, v)
+    assert wl.relerr(to_host(o), o_ref) <= wl.tolerance(wl.BF16, 256)
+
+
+@pytest.mark.parametrize("parts", [2, 3])
+def test_config5_mlp_forward_backward(pg, oracle, parts):
+    """Reduced config 5 (rows 256, 128 -> 512 -> 128), loss = sum.  gelu(h) is rounded to bf16 once
+    and the same bytes feed layer 2 on both sides; every GEMM is compared in isolation."""
+    from picograd_b200 import ops
+    pg.set_option("f32_parts", parts)
+    x, w1, w2 = wl.config5(256, 128, 512)
+    xd, w1d, w2d = (to_dev(t, wl.BF16) for t in (x, w1, w2))
+    # forward
+    h = pg.pg_matmul(xd, w1d); pg.pg_dev_sync()
+    h_ref = oracle.gemm_ex(wl.BF16, x, w1)
+    assert wl.relerr(to_host(h), h_ref) <= wl.tolerance(wl.BF16, 128)
+    a32, a16 = ops.gelu(h, out16=torch.bfloat16); pg.pg_dev_sync()
+    assert np.abs(to_host(a32) - oracle.gelu(to_host(h))).max() < 1e-5
+    a_bits = bits_to_host(a16)
+    y = pg.pg_matmul(a16, w2d); pg.pg_dev_sync()
+    assert wl.relerr(to_host(y), oracle.gemm_ex(wl.BF16, a_bits, w2)) <= wl.tolerance(wl.BF16, 512)
+    # backward of loss = sum(y): dY = 1
+    dy = torch.ones_like(y)
+    da, dw2 = pg.pg_matmul_backward(a16, w2d, dy); pg.pg_dev_sync()
+    da_ref, dw2_ref = oracle.matmul_backward(wl.BF16, a_bits, w2, np.ones(y.shape, np.float32))
+    assert wl.relerr(to_host(da), da_ref) <= wl.tolerance(wl.BF16, 128)      # contraction over n = 128
+    assert wl.relerr(to_host(dw2), dw2_ref) <= wl.tolerance(wl.BF16, 256)    # contraction over rows = 256
+    dh = ops.gelu_grad(h, da); pg.pg_dev_sync()
+    dh_host = to_host(dh)
+    assert np.abs(dh_host - oracle.gelu_grad(to_host(h), to_host(da))).max() < 1e-4
+    dx, dw1 = pg.pg_matmul_backward(xd, w1d, dh); pg.pg_dev_sync()
+    dx_ref, dw1_ref = oracle.matmul_backward(wl.BF16, x, w1, dh_host)
+    assert wl.relerr(to_host(dx), dx_ref) <= wl.tolerance(wl.BF16, 512)
+    assert wl.relerr(to_host(dw1), dw1_ref) <= wl.tolerance(wl.BF16, 256)
+
+
+def test_backward_accumulates_into_existing_grads(pg, oracle):
+    """autograd/autograd.c:669-670, :690-691: grad += product."""
+    rng = np.random.default_rng(14)
+    m, n, k = 136, 264, 200
+    a = wl.to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32))
+    b = wl.to_bf16_bits(rng.standard_normal((k, n), dtype=np.float32))
+    g = rng.standard_normal((m, n), dtype=np.float32)
+    ga0 = rng.standard_normal((m, k), dtype=np.float32)
+    gb0 = rng.standard_normal((k, n), dtype=np.float32)
+    ga, gb = pg.pg_matmul_backward(to_dev(a, wl.BF16), to_dev(b, wl.BF16), to_dev(g, wl.F32),
+                                   ga=to_dev(ga0, wl.F32), gb=to_dev(gb0, wl.F32))
+    pg.pg_dev_sync()
+    ga_ref, gb_ref = oracle.matmul_backward(wl.BF16, a, b, g)
+    assert wl.relerr(to_host(ga) - ga0, ga_ref) <= wl.tolerance(wl.BF16, n)
+    assert wl.relerr(to_host(gb) - gb0, gb_ref) <= wl.tolerance(wl.BF16, m)
+
+
+def test_backward_batched_and_shared_b(pg, oracle):
+    rng = np.random.default_rng(15)
+    bt, m, n, k = 3, 72, 136, 64
+    a = wl.to_bf16_bits(rng.standard_normal((bt, m, k), dtype=np.float32))
+    b = wl.to_bf16_bits(rng.standard_normal((k, n), dtype=np.float32))
+    g = rng.standard_normal((bt, m, n), dtype=np.float32)
+    ga, gb = pg.pg_matmul_backward(to_dev(a, wl.BF16), to_dev(b, wl.BF16), to_dev(g, wl.F32))
+    pg.pg_dev_sync()
+    ga_ref = np.zeros((bt, m, k), np.float32); gb_ref = np.zeros((k, n), np.float32)
+    for s in range(bt):
+        x, y = oracle.matmul_backward(wl.BF16, a[s], b, g[s])
+        ga_ref[s] = x; gb_ref += y
+    assert wl.relerr(to_host(ga), ga_ref) <= wl.tolerance(wl.BF16, n)
+    assert wl.relerr(to_host(gb), gb_ref) <= wl.tolerance(wl.BF16, bt * m)
