@@ -715,9 +715,12 @@ int tc_gemm_launch(const TcGemm &g) {
     p.accumulate = g.accumulate ? 1u : 0u;
     p.status = g.dev_status;
     const uint32_t zc = splits > 1 ? splits : g.batch;
-    bool c_tma_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (zc == 1 || g.c_stride % 4 == 0);
+    const bool c_vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (zc == 1 || g.c_stride % 4 == 0);
+    // A TMA store clips the innermost extent in 16-byte units (measured on B200: with N % 4 != 0
+    // it wrote up to the next multiple of four columns), so it is used only when N is one.
+    const bool c_tma_ok = c_vec_ok && (g.N % 4 == 0);
     p.epilogue_tma = (g.force_epilogue >= 0) ? (uint32_t)(g.force_epilogue && c_tma_ok) : (c_tma_ok ? 1u : 0u);
-    p.c_vec4 = c_tma_ok ? 1u : 0u;
+    p.c_vec4 = c_vec_ok ? 1u : 0u;
 
     CUtensorMap ma, mb, mc;
     int st = encode_operand(&ma, g.A, g.dtype, g.M, g.K, g.batch * g.A.nparts, BM_CTA);
