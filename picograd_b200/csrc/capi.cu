@@ -34,6 +34,8 @@ struct State {
     int opt_splits = 0;
     int opt_f32_parts = 2;   // bf16 pieces an f32 operand is split into when paired with a 16-bit one
     int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
+    int opt_stages = 0;      // 0: all smem stages of the tile configuration
+    int opt_debug = 0;       // timing experiments only (see TcGemm::debug)
     char err[512] = "";
     char last_path[96] = "";
     unsigned long long launches = 0;
@@ -187,6 +189,7 @@ static int run_tc(const Problem &p) {
     t.accumulate = p.accumulate;
     t.splits = 1;
     t.force_cfg = g.opt_cfg; t.force_epilogue = g.opt_epilogue;
+    t.stages = g.opt_stages; t.debug = g.opt_debug;
     t.stream = g.stream; t.dev_status = g.dev_status;
 
     // a batch-shared operand (stride 0) with batch > 1 cannot be a TMA dimension of stride 0
@@ -535,6 +538,8 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "k_splits")) { g.opt_splits = value; return ST_OK; }
     if (!strcmp(name, "f32_parts")) { if (value != 2 && value != 3) return ST_UNSUPPORTED; g.opt_f32_parts = value; return ST_OK; }
     if (!strcmp(name, "f32_tensor_cores")) { g.opt_f32_tc = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "stages")) { g.opt_stages = value; return ST_OK; }
+    if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);
     return ST_UNSUPPORTED;
 }

@@ -72,6 +72,8 @@ struct TcParams {
     uint32_t epilogue_tma;        // 1: TMA-store epilogue, 0: direct stores
     uint32_t accumulate;          // C += instead of C = (TMA reduce-add / read-modify-write)
     uint32_t c_vec4;              // direct stores may use 16-byte vectors
+    uint32_t stages;              // smem stages in use (<= the configuration's maximum)
+    uint32_t debug;               // timing experiments only: 1 = issue no TMA loads, 2 = issue no C stores
     float *C;
     uint64_t ldc, c_stride;
     uint32_t *status;
@@ -292,7 +294,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const TcParams p) {
     using C_ = Cfg<CG, BN>;
-    constexpr uint32_t STAGES = C_::STAGES;
+    constexpr uint32_t STAGES = C_::STAGES;     // allocated; p.stages of them are cycled through
+    const uint32_t nstages = p.stages;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -362,6 +365,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const uint32_t sb = sa + A_TILE_BYTES;
                         uint32_t bar = full_bar(stage);
                         if constexpr (CG == 2) bar = mapa(bar, 0);
+                        if (p.debug & 1u) {
+                            if (cta_rank == 0) mbar_arrive(full_bar(stage));
+                        } else {
                         if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C_::STAGE_BYTES * CG);
                         if (!p.a_mn) {
                             tma_load_3d<CG>(sa, &map_a, bar, k0, m0, za);
@@ -377,9 +383,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (uint32_t c = 0; c < C_::BN_CTA / 64; ++c)
                                 tma_load_3d<CG>(sb + c * (BK * 128), &map_b, bar, n0 + (int32_t)(c * 64), k0, zb);
                         }
+                        }
                     }
                     __syncwarp();
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == nstages) { stage = 0; phase ^= 1; }
                 }
             }
         }
@@ -416,7 +423,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (it + 1 == iters) umma_commit<CG>(tmem_full_bar(acc));  // accumulator complete
                     }
                     __syncwarp();
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == nstages) { stage = 0; phase ^= 1; }
                 }
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
@@ -446,6 +453,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t v[32];
                 tmem_ld32(taddr + c * EPI_COLS, v);
                 tmem_ld_wait();
+                if (p.debug & 2u) continue;
                 if (p.epilogue_tma) {
                     // the store issued two chunks ago must have finished reading this buffer
                     if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
@@ -518,16 +526,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 struct TcConfig {
     const char *name;
     int cg, bn;
-    uint32_t smem;
+    uint32_t smem, stages;
     const void *fn;
 };
 
 static const TcConfig g_cfgs[] = {
-    {"1cta_128x256", 1, 256, Cfg<1, 256>::SMEM_BYTES, (const void *)tc_gemm_kernel<1, 256>},
-    {"1cta_128x128", 1, 128, Cfg<1, 128>::SMEM_BYTES, (const void *)tc_gemm_kernel<1, 128>},
-    {"1cta_128x64", 1, 64, Cfg<1, 64>::SMEM_BYTES, (const void *)tc_gemm_kernel<1, 64>},
-    {"2cta_256x256", 2, 256, Cfg<2, 256>::SMEM_BYTES, (const void *)tc_gemm_kernel<2, 256>},
-    {"2cta_256x128", 2, 128, Cfg<2, 128>::SMEM_BYTES, (const void *)tc_gemm_kernel<2, 128>},
+    {"1cta_128x256", 1, 256, Cfg<1, 256>::SMEM_BYTES, Cfg<1, 256>::STAGES, (const void *)tc_gemm_kernel<1, 256>},
+    {"1cta_128x128", 1, 128, Cfg<1, 128>::SMEM_BYTES, Cfg<1, 128>::STAGES, (const void *)tc_gemm_kernel<1, 128>},
+    {"1cta_128x64", 1, 64, Cfg<1, 64>::SMEM_BYTES, Cfg<1, 64>::STAGES, (const void *)tc_gemm_kernel<1, 64>},
+    {"2cta_256x256", 2, 256, Cfg<2, 256>::SMEM_BYTES, Cfg<2, 256>::STAGES, (const void *)tc_gemm_kernel<2, 256>},
+    {"2cta_256x128", 2, 128, Cfg<2, 128>::SMEM_BYTES, Cfg<2, 128>::STAGES, (const void *)tc_gemm_kernel<2, 128>},
 };
 constexpr int NUM_CFGS = sizeof(g_cfgs) / sizeof(g_cfgs[0]);
 
@@ -713,6 +721,8 @@ int tc_gemm_launch(const TcGemm &g) {
     }
     p.C = g.C; p.ldc = g.ldc; p.c_stride = g.c_stride;
     p.accumulate = g.accumulate ? 1u : 0u;
+    p.stages = (g.stages >= 2 && (uint32_t)g.stages < c.stages) ? (uint32_t)g.stages : c.stages;
+    p.debug = (uint32_t)g.debug;
     p.status = g.dev_status;
     const uint32_t zc = splits > 1 ? splits : g.batch;
     const bool c_vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (zc == 1 || g.c_stride % 4 == 0);

@@ -49,6 +49,8 @@ struct TcGemm {
     uint32_t splits;           // >1: split-K, slice s goes to C + s*c_stride (batch must be 1)
     int force_cfg;             // -1 = choose; else index into the config table
     int force_epilogue;        // -1 = choose; 0 = direct stores; 1 = TMA stores
+    int stages;                // 0 = all the configuration has; else use this many smem stages
+    int debug;                 // timing experiments: 1 = no TMA loads, 2 = no C stores (results are garbage)
     cudaStream_t stream;
     uint32_t *dev_status;      // device status word
 };
