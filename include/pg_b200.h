@@ -119,6 +119,9 @@ PG_B200_API const char *pg_b200_last_error(void);
 PG_B200_API int pg_b200_set_option(const char *name, int value);
 PG_B200_API int pg_b200_num_tile_configs(void);
 PG_B200_API const char *pg_b200_tile_config_name(int index);
+/* Diagnostics of the timing experiments (option "debug" bit 32): copies per-CTA cycle counters
+ * of the last tensor-core launch, 16 per CTA, to `out`. */
+PG_B200_API int pg_b200_debug_counters(uint64_t *out, size_t count);
 /* Number of kernels this library has launched since it was loaded. */
 PG_B200_API uint64_t pg_b200_launch_count(void);
 /* Name of the path the last GEMM call took ("tc:2cta_256x256", "simt", ...). */

@@ -25,6 +25,7 @@ struct State {
     cudaStream_t stream = nullptr;
     uint32_t *dev_status = nullptr;
     uint32_t *host_status = nullptr;   // pinned mirror
+    unsigned long long *prof = nullptr;   // per-CTA cycle counters of the timing experiments
     DeviceBuf ws;                      // scratch: operand pieces, split-K slices
     DeviceBuf stage_a, stage_b, stage_c;  // device staging for host-pointer calls
     // options
@@ -107,6 +108,8 @@ static int do_init() {
         return g.init_status = ST_ALLOC;
     }
     *g.host_status = 0;
+    if (cudaMalloc((void **)&g.prof, 512 * 16 * 8) == cudaSuccess) cudaMemset(g.prof, 0, 512 * 16 * 8);
+    else { g.prof = nullptr; cudaGetLastError(); }
     return g.init_status = ST_OK;
 }
 
@@ -190,7 +193,7 @@ static int run_tc(const Problem &p) {
     t.splits = 1;
     t.force_cfg = g.opt_cfg; t.force_epilogue = g.opt_epilogue;
     t.stages = g.opt_stages; t.debug = g.opt_debug;
-    t.stream = g.stream; t.dev_status = g.dev_status;
+    t.stream = g.stream; t.dev_status = g.dev_status; t.prof = g.prof;
 
     // a batch-shared operand (stride 0) with batch > 1 cannot be a TMA dimension of stride 0
     if (p.batch > 1 && (p.stride_a == 0 || p.stride_b == 0)) {
@@ -522,6 +525,13 @@ int pg_b200_cast_f32(const float *src, uint16_t *dst, int dtype16, size_t n) {
 int pg_b200_fill_f32(float *dst, float value, size_t n) {
     if (!ready()) return g.init_status;
     return fill_f32_launch(dst, value, n, g.stream);
+}
+
+int pg_b200_debug_counters(uint64_t *out, size_t count) {
+    if (!ready() || !g.prof) return ST_UNSUPPORTED;
+    if (count > 512 * 16) count = 512 * 16;
+    cudaStreamSynchronize(g.stream);
+    return cudaMemcpy(out, g.prof, count * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? ST_OK : ST_COPY;
 }
 
 const char *pg_b200_last_error(void) { return g.err; }

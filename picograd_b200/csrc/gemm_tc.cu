@@ -44,20 +44,23 @@ constexpr uint32_t NUM_THREADS = 32 * (2 + EPI_WARPS);
 constexpr uint32_t SMEM_LIMIT = 232448;          // 227 KB opt-in maximum per CTA
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
-template <int CG, int BN>
+template <int CG, int BN, int SUB, bool STAGING>
 struct Cfg {
     static constexpr uint32_t BN_CTA = BN / CG;                      // B columns loaded by one CTA
     static constexpr uint32_t B_TILE_BYTES = BN_CTA * BK * 2;
-    static constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-    static constexpr uint32_t EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
+    static constexpr uint32_t SUB_BYTES = A_TILE_BYTES + B_TILE_BYTES;  // one 64-deep K block of A and B
+    static constexpr uint32_t STAGE_BYTES = SUB * SUB_BYTES;            // SUB K blocks share one barrier round
+    // staging buffers of the TMA-store epilogue; a configuration without them stores C straight
+    // from registers and spends the memory on one more pipeline stage
+    static constexpr uint32_t EPI_BYTES = STAGING ? EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES : 0;
     static constexpr uint32_t BAR_BYTES = 512;
     static constexpr uint32_t STAGES_RAW = (SMEM_LIMIT - 1024 - EPI_BYTES - BAR_BYTES) / STAGE_BYTES;
     static constexpr uint32_t STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
     static constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
     static constexpr uint32_t TMEM_COLS = 2 * BN;                    // two accumulators
-    static_assert(STAGES >= 3, "pipeline too shallow");
+    static_assert(STAGES >= 2, "pipeline too shallow");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
-    static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+    static_assert(SUB_BYTES % 1024 == 0, "tiles must keep the 1024-byte swizzle alignment");
 };
 
 struct TcParams {
@@ -73,10 +76,12 @@ struct TcParams {
     uint32_t accumulate;          // C += instead of C = (TMA reduce-add / read-modify-write)
     uint32_t c_vec4;              // direct stores may use 16-byte vectors
     uint32_t stages;              // smem stages in use (<= the configuration's maximum)
-    uint32_t debug;               // timing experiments only: 1 = issue no TMA loads, 2 = issue no C stores
+    uint32_t debug;               // timing experiments only (results are garbage): 1 = no TMA loads, 2 = no C
+                                  // stores, 4 = no TMEM reads, 8 = alternate accumulators, 16 = no MMAs
     float *C;
     uint64_t ldc, c_stride;
     uint32_t *status;
+    unsigned long long *prof;     // debug & 32: 16 cycle counters per CTA
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -119,35 +124,84 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
+// Spins on try_wait inside one asm block (so that the compiler sees straight-line, warp-uniform
+// code around it) for at most `tries` attempts; returns 1 if the phase completed.
+__device__ __forceinline__ uint32_t mbar_spin(uint32_t bar, uint32_t parity, uint32_t tries) {
+    uint32_t done;
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p;\n\t.reg .b32 n;\n\t"
+        "mov.b32 n, %3;\n"
+        "PG_WAIT_LOOP:\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra PG_WAIT_DONE;\n\t"
+        "sub.u32 n, n, 1;\n\t"
+        "setp.ne.u32 p, n, 0;\n\t"
+        "@p bra PG_WAIT_LOOP;\n\t"
+        "setp.ne.u32 p, n, 0;\n"          // n == 0 here: p = false
+        "PG_WAIT_DONE:\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(tries)
         : "memory");
-    return ok;
+    return done;
 }
-// Bounded wait.  Returns false when the CTA is aborting (this or another wait ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t err_bit) {
-    if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = 0;
-    for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 0xFFu) == 0) {
-            if (*abort_flag) return false;
-            uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            if (now - t0 > WAIT_LIMIT_NS) {
+// Bounded wait, executed by a whole (converged) warp; the result is the same in every lane.
+// Returns false when the CTA is aborting (this or another wait ran out of time).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                            uint32_t *status, uint32_t err_bit) {
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        const uint32_t done = mbar_spin(bar, parity, 1024);
+        if (__all_sync(0xffffffffu, done)) return true;
+        uint32_t give_up = *abort_flag;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) give_up = 1;
+        if (__any_sync(0xffffffffu, give_up)) {
+            if ((threadIdx.x & 31) == 0) {
                 *abort_flag = 1;
                 atomicOr(status, err_bit);
-                return false;
             }
+            return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t *status, uint32_t err_bit) {
+    const uint32_t done = mbar_spin(bar, parity, 1u << 14);
+    if (__all_sync(0xffffffffu, done)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, err_bit);
+}
+// For waits that normally last tens of microseconds (the epilogue waiting for a whole main loop):
+// sleep between polls so that the waiting warps do not burn issue slots and power.
+__device__ __forceinline__ bool mbar_wait_patient(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                  uint32_t *status, uint32_t err_bit) {
+    uint32_t done = mbar_spin(bar, parity, 4);
+    if (__all_sync(0xffffffffu, done)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        __nanosleep(256);
+        done = mbar_spin(bar, parity, 2);
+        if (__all_sync(0xffffffffu, done)) return true;
+        uint32_t give_up = *abort_flag;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) give_up = 1;
+        if (__any_sync(0xffffffffu, give_up)) {
+            if ((threadIdx.x & 31) == 0) {
+                *abort_flag = 1;
+                atomicOr(status, err_bit);
+            }
+            return false;
+        }
+    }
+}
+// One lane per warp, chosen by the hardware; unlike `lane == 0` the compiler knows the enclosing
+// code stays warp-uniform, which lets descriptors and loop state live in uniform registers.
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+        "elect.sync rx|px, 0xFFFFFFFF;\n\t"
+        "@px mov.s32 %0, 1;\n\t}"
+        : "+r"(pred));
+    return pred;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -188,6 +242,25 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
             ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Same, with each 64-bit descriptor passed as its two 32-bit halves (the high half is constant for
+// an operand; only the address field in the low half moves), which keeps the issuing thread's
+// arithmetic in 32 bits.
+template <int CG>
+__device__ __forceinline__ void umma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
+    if constexpr (CG == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\tsetp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\tsetp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Arrive on `bar` (same offset in every CTA of the pair) once all MMAs issued so far have completed.
 template <int CG>
@@ -289,11 +362,11 @@ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-template <int CG, int BN>
+template <int CG, int BN, int SUB, bool STAGING>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const TcParams p) {
-    using C_ = Cfg<CG, BN>;
+    using C_ = Cfg<CG, BN, SUB, STAGING>;
     constexpr uint32_t STAGES = C_::STAGES;     // allocated; p.stages of them are cycled through
     const uint32_t nstages = p.stages;
 
@@ -313,7 +386,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile uint32_t *tmem_slot_gen = (volatile uint32_t *)(smem_gen + (tmem_slot - smem_base));
     volatile uint32_t *abort_flag = (volatile uint32_t *)(smem_gen + abort_off);
 
-    const uint32_t warp = threadIdx.x >> 5;
+    // warp index through a shuffle, so that the compiler knows it is the same in all lanes
+    const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0;
     const uint32_t cluster_id = blockIdx.x / CG;
@@ -344,88 +418,171 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
+    // Each role loop below is executed by its whole warp with warp-uniform state; the instructions
+    // that must come from one thread (TMA, tcgen05.mma, tcgen05.commit, barrier arrives) sit under
+    // elect_one().
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         uint32_t stage = 0, phase = 0;
-        // barrier that counts the bytes of this stage: the leader CTA's when paired
         bool ok = true;
+        const bool prof = (p.debug & 32u) != 0;
+        long long tp_wait = 0, tp_issue = 0;
         for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
             const WorkUnit w = decode_unit(p, u);
             const int32_t m0 = (int32_t)(w.m_blk * BM_CTA * CG + cta_rank * BM_CTA);
             const int32_t n0 = (int32_t)(w.n_blk * BN + cta_rank * C_::BN_CTA);
+            const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
             for (uint32_t pass = 0; pass < p.npass && ok; ++pass) {
                 const int32_t za = (int32_t)(w.batch * p.a_nparts + ((p.a_sel >> (4 * pass)) & 0xF));
                 const int32_t zb = (int32_t)(w.batch * p.b_nparts + ((p.b_sel >> (4 * pass)) & 0xF));
-                for (uint32_t kb = 0; kb < w.kb_count; ++kb) {
+                for (uint32_t r = 0; r < rounds; ++r) {
+                    long long c0 = prof ? clock64() : 0;
                     ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
                     if (!ok) break;
-                    if (lane == 0) {
-                        const int32_t k0 = (int32_t)((w.kb_begin + kb) * BK);
-                        const uint32_t sa = stage_base + stage * C_::STAGE_BYTES;
-                        const uint32_t sb = sa + A_TILE_BYTES;
-                        uint32_t bar = full_bar(stage);
-                        if constexpr (CG == 2) bar = mapa(bar, 0);
+                    long long c1 = prof ? clock64() : 0;
+                    // the barrier that counts this stage's bytes: the leader CTA's when paired
+                    uint32_t bar = full_bar(stage);
+                    if constexpr (CG == 2) bar = mapa(bar, 0);
+                    const uint32_t sbase = stage_base + stage * C_::STAGE_BYTES;
+                    const int32_t kbase = (int32_t)((w.kb_begin + r * SUB) * BK);
+                    if (elect_one()) {
                         if (p.debug & 1u) {
                             if (cta_rank == 0) mbar_arrive(full_bar(stage));
                         } else {
-                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C_::STAGE_BYTES * CG);
-                        if (!p.a_mn) {
-                            tma_load_3d<CG>(sa, &map_a, bar, k0, m0, za);
-                        } else {
+                            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C_::STAGE_BYTES * CG);
 #pragma unroll
-                            for (uint32_t c = 0; c < BM_CTA / 64; ++c)
-                                tma_load_3d<CG>(sa + c * (BK * 128), &map_a, bar, m0 + (int32_t)(c * 64), k0, za);
-                        }
-                        if (!p.b_mn) {
-                            tma_load_3d<CG>(sb, &map_b, bar, k0, n0, zb);
-                        } else {
+                            for (uint32_t j = 0; j < (uint32_t)SUB; ++j) {
+                                // a K block past the end of K is all zero fill (and still counts its bytes)
+                                const int32_t k0 = kbase + (int32_t)(j * BK);
+                                const uint32_t sa = sbase + j * C_::SUB_BYTES;
+                                const uint32_t sb = sa + A_TILE_BYTES;
+                                if (!p.a_mn) {
+                                    tma_load_3d<CG>(sa, &map_a, bar, k0, m0, za);
+                                } else {
 #pragma unroll
-                            for (uint32_t c = 0; c < C_::BN_CTA / 64; ++c)
-                                tma_load_3d<CG>(sb + c * (BK * 128), &map_b, bar, n0 + (int32_t)(c * 64), k0, zb);
-                        }
+                                    for (uint32_t c = 0; c < BM_CTA / 64; ++c)
+                                        tma_load_3d<CG>(sa + c * (BK * 128), &map_a, bar, m0 + (int32_t)(c * 64), k0, za);
+                                }
+                                if (!p.b_mn) {
+                                    tma_load_3d<CG>(sb, &map_b, bar, k0, n0, zb);
+                                } else {
+#pragma unroll
+                                    for (uint32_t c = 0; c < C_::BN_CTA / 64; ++c)
+                                        tma_load_3d<CG>(sb + c * (BK * 128), &map_b, bar, n0 + (int32_t)(c * 64), k0, zb);
+                                }
+                            }
                         }
                     }
                     __syncwarp();
+                    if (prof) { tp_wait += c1 - c0; tp_issue += clock64() - c1; }
                     if (++stage == nstages) { stage = 0; phase ^= 1; }
                 }
             }
         }
+        if (prof && lane == 0) {
+            unsigned long long *o = p.prof + (size_t)blockIdx.x * 16;
+            o[8] = (unsigned long long)tp_wait; o[9] = (unsigned long long)tp_issue;
+        }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
+        // ------------------------------ MMA issuer (leader CTA) ------------------------------
+        // The tensor core queues only about two MMAs ahead of the one it executes (measured: the
+        // issue of a third blocks), so whatever happens between MMAs must fit in the time two of
+        // them take.  Hence the order inside a round: issue the first half of the round's MMAs,
+        // THEN wait for the next round's bytes, then issue the second half and release this
+        // round's stage (a tcgen05.commit costs ~100 cycles) while those are still executing.
         if (cta_rank == 0) {
+            constexpr uint32_t MMAS = SUB * (BK / UMMA_K);        // per round
+            constexpr uint32_t HALF = MMAS / 2;
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             const uint32_t a_lbo = p.a_mn ? BK * 128 : 0;
             const uint32_t b_lbo = p.b_mn ? BK * 128 : 0;
-            const uint32_t a_kstep = p.a_mn ? UMMA_K * 128 : UMMA_K * 2;
-            const uint32_t b_kstep = p.b_mn ? UMMA_K * 128 : UMMA_K * 2;
+            const uint32_t a_k1 = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4, a_k2 = 2 * a_k1, a_k3 = 3 * a_k1;
+            const uint32_t b_k1 = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4, b_k2 = 2 * b_k1, b_k3 = 3 * b_k1;
+            const uint64_t desc_a0 = make_desc(stage_base, a_lbo);
+            const uint64_t desc_b0 = make_desc(stage_base + A_TILE_BYTES, b_lbo);
+            const uint32_t a_hi = (uint32_t)(desc_a0 >> 32), b_hi = (uint32_t)(desc_b0 >> 32);
+            const uint32_t a_lo0 = (uint32_t)desc_a0, b_lo0 = (uint32_t)desc_b0;
+            const uint32_t idesc = p.idesc;
             bool ok = true;
+            bool ready = false;             // full_bar(stage) has already been seen complete
+            const bool prof = (p.debug & 32u) != 0;
+            long long t_wait = 0, t_issue = 0, t_commit = 0, t_tmem = 0, t_all = prof ? clock64() : 0, n_rounds = 0;
+
+            auto issue = [&](uint32_t m, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t nsub, uint32_t accum) {
+                const uint32_t j = m / (BK / UMMA_K), kk = m % (BK / UMMA_K);
+                if (SUB > 1 && j >= nsub) return;
+                const uint32_t ak = kk == 0 ? 0u : (kk == 1 ? a_k1 : (kk == 2 ? a_k2 : a_k3));
+                const uint32_t bk = kk == 0 ? 0u : (kk == 1 ? b_k1 : (kk == 2 ? b_k2 : b_k3));
+                umma_lohi<CG>(d_tmem, a_lo + j * (C_::SUB_BYTES >> 4) + ak, a_hi, b_lo + j * (C_::SUB_BYTES >> 4) + bk,
+                              b_hi, idesc, accum);
+            };
+
             for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
                 const WorkUnit w = decode_unit(p, u);
+                long long c0 = prof ? clock64() : 0;
                 ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
                 if (!ok) break;
                 tc_fence_after();
+                if (prof) t_tmem += clock64() - c0;
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                const uint32_t iters = p.npass * w.kb_count;
+                const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
+                const uint32_t iters = p.npass * rounds;
+                const bool more_units = u + num_clusters < total_units;
+                uint32_t r = 0;
                 for (uint32_t it = 0; it < iters; ++it) {
-                    ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, DEV_ERR_WAIT_FULL);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (lane == 0) {
-                        const uint32_t sa = stage_base + stage * C_::STAGE_BYTES;
-                        const uint32_t sb = sa + A_TILE_BYTES;
+                    long long c1 = prof ? clock64() : 0;
+                    if (!ready) {
+                        ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, DEV_ERR_WAIT_FULL);
+                        if (!ok) break;
+                    }
+                    long long c2 = prof ? clock64() : 0;
+                    const uint32_t soff = stage * (C_::STAGE_BYTES >> 4);
+                    const uint32_t a_lo = a_lo0 + soff, b_lo = b_lo0 + soff;
+                    uint32_t nsub = SUB;
+                    if (SUB > 1 && w.kb_count - r * SUB < (uint32_t)SUB) nsub = w.kb_count - r * SUB;  // rest belongs to the next split
+                    const bool do_mma = !(p.debug & 16u);
+                    if (elect_one()) {
+                        if (do_mma) {
 #pragma unroll
-                        for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
-                            const uint64_t da = make_desc(sa + kk * a_kstep, a_lbo);
-                            const uint64_t db = make_desc(sb + kk * b_kstep, b_lbo);
-                            umma<CG>(d_tmem, da, db, p.idesc, (it | kk) ? 1u : 0u);
+                            for (uint32_t m = 0; m < HALF; ++m) issue(m, d_tmem, a_lo, b_lo, nsub, (it | m) ? 1u : 0u);
                         }
-                        umma_commit<CG>(empty_bar(stage));          // frees the smem stage
-                        if (it + 1 == iters) umma_commit<CG>(tmem_full_bar(acc));  // accumulator complete
                     }
                     __syncwarp();
-                    if (++stage == nstages) { stage = 0; phase ^= 1; }
+                    long long c3 = prof ? clock64() : 0;
+                    uint32_t ns = stage + 1, np = phase;
+                    if (ns == nstages) { ns = 0; np ^= 1; }
+                    if (it + 1 < iters || more_units) {
+                        ok = mbar_wait(full_bar(ns), np, abort_flag, p.status, DEV_ERR_WAIT_FULL);
+                        if (!ok) break;
+                        ready = true;
+                    } else {
+                        ready = false;
+                    }
+                    long long c4 = prof ? clock64() : 0;
+                    const bool last = it + 1 == iters;
+                    if (elect_one()) {
+                        if (do_mma) {
+#pragma unroll
+                            for (uint32_t m = HALF; m < MMAS; ++m) issue(m, d_tmem, a_lo, b_lo, nsub, 1u);
+                        }
+                        umma_commit<CG>(empty_bar(stage));                  // frees this round's stage
+                        if (last) umma_commit<CG>(tmem_full_bar(acc));      // accumulator complete
+                    }
+                    __syncwarp();
+                    if (prof) {
+                        long long c5 = clock64();
+                        t_wait += (c2 - c1) + (c4 - c3); t_issue += (c3 - c2) + (c5 - c4); ++n_rounds;
+                    }
+                    if (++r == rounds) r = 0;
+                    stage = ns; phase = np;
                 }
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+            if (prof && lane == 0) {
+                unsigned long long *o = p.prof + (size_t)blockIdx.x * 16;
+                o[0] = (unsigned long long)(clock64() - t_all); o[1] = (unsigned long long)t_wait;
+                o[2] = (unsigned long long)t_issue; o[3] = (unsigned long long)t_commit;
+                o[4] = (unsigned long long)t_tmem; o[5] = (unsigned long long)n_rounds;
             }
         }
     } else {
@@ -439,7 +596,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
             const WorkUnit w = decode_unit(p, u);
-            ok = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
+            ok = mbar_wait_patient(tmem_full_bar(acc), acc_phase, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
             const uint32_t row0 = w.m_blk * BM_CTA * CG + cta_rank * BM_CTA + q * 32;  // first row of this warp
@@ -450,11 +607,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (uint32_t c = 0; c < BN / EPI_COLS; ++c) {
                 const uint32_t col = col0 + c * EPI_COLS;
                 if (col >= p.N || row0 >= p.M) break;   // nothing of this warp's slab is inside C
+                if (p.debug & 4u) break;
                 uint32_t v[32];
                 tmem_ld32(taddr + c * EPI_COLS, v);
                 tmem_ld_wait();
                 if (p.debug & 2u) continue;
-                if (p.epilogue_tma) {
+                if (STAGING && p.epilogue_tma) {
                     // the store issued two chunks ago must have finished reading this buffer
                     if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
                     __syncwarp();
@@ -525,17 +683,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------------------------------------
 struct TcConfig {
     const char *name;
-    int cg, bn;
+    int cg, bn, sub;
+    bool staging;
     uint32_t smem, stages;
     const void *fn;
 };
 
+#define PG_TC_CFG(NAME, CG_, BN_, SUB_, STG_) \
+    {NAME, CG_, BN_, SUB_, STG_, Cfg<CG_, BN_, SUB_, STG_>::SMEM_BYTES, Cfg<CG_, BN_, SUB_, STG_>::STAGES, \
+     (const void *)tc_gemm_kernel<CG_, BN_, SUB_, STG_>}
 static const TcConfig g_cfgs[] = {
-    {"1cta_128x256", 1, 256, Cfg<1, 256>::SMEM_BYTES, Cfg<1, 256>::STAGES, (const void *)tc_gemm_kernel<1, 256>},
-    {"1cta_128x128", 1, 128, Cfg<1, 128>::SMEM_BYTES, Cfg<1, 128>::STAGES, (const void *)tc_gemm_kernel<1, 128>},
-    {"1cta_128x64", 1, 64, Cfg<1, 64>::SMEM_BYTES, Cfg<1, 64>::STAGES, (const void *)tc_gemm_kernel<1, 64>},
-    {"2cta_256x256", 2, 256, Cfg<2, 256>::SMEM_BYTES, Cfg<2, 256>::STAGES, (const void *)tc_gemm_kernel<2, 256>},
-    {"2cta_256x128", 2, 128, Cfg<2, 128>::SMEM_BYTES, Cfg<2, 128>::STAGES, (const void *)tc_gemm_kernel<2, 128>},
+    PG_TC_CFG("1cta_128x256", 1, 256, 1, true),
+    PG_TC_CFG("1cta_128x128", 1, 128, 1, true),
+    PG_TC_CFG("1cta_128x64", 1, 64, 1, true),
+    PG_TC_CFG("2cta_256x256", 2, 256, 1, true),
+    PG_TC_CFG("2cta_256x128", 2, 128, 1, true),
+    PG_TC_CFG("2cta_256x256_k128", 2, 256, 2, true),
+    PG_TC_CFG("1cta_128x256_k128", 1, 256, 2, true),
+    PG_TC_CFG("2cta_256x256_s7", 2, 256, 1, false),
 };
 constexpr int NUM_CFGS = sizeof(g_cfgs) / sizeof(g_cfgs[0]);
 
@@ -723,6 +888,8 @@ int tc_gemm_launch(const TcGemm &g) {
     p.accumulate = g.accumulate ? 1u : 0u;
     p.stages = (g.stages >= 2 && (uint32_t)g.stages < c.stages) ? (uint32_t)g.stages : c.stages;
     p.debug = (uint32_t)g.debug;
+    p.prof = g.prof;
+    if (!p.prof) p.debug &= ~32u;
     p.status = g.dev_status;
     const uint32_t zc = splits > 1 ? splits : g.batch;
     const bool c_vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (zc == 1 || g.c_stride % 4 == 0);
@@ -730,6 +897,7 @@ int tc_gemm_launch(const TcGemm &g) {
     // it wrote up to the next multiple of four columns), so it is used only when N is one.
     const bool c_tma_ok = c_vec_ok && (g.N % 4 == 0);
     p.epilogue_tma = (g.force_epilogue >= 0) ? (uint32_t)(g.force_epilogue && c_tma_ok) : (c_tma_ok ? 1u : 0u);
+    if (!c.staging) p.epilogue_tma = 0;
     p.c_vec4 = c_vec_ok ? 1u : 0u;
 
     CUtensorMap ma, mb, mc;

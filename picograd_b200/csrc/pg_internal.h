@@ -53,6 +53,7 @@ struct TcGemm {
     int debug;                 // timing experiments: 1 = no TMA loads, 2 = no C stores (results are garbage)
     cudaStream_t stream;
     uint32_t *dev_status;      // device status word
+    unsigned long long *prof;  // 16 counters per CTA for debug bit 32 (may be null)
 };
 
 // Returns ST_OK if launched, ST_UNSUPPORTED if the shape/alignment cannot go

@@ -93,7 +93,7 @@ def test_gemm_ex_vs_oracle(pg, oracle, dt, shape, path):
         assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("cfg", range(5))
+@pytest.mark.parametrize("cfg", range(8))
 @pytest.mark.parametrize("epi", [0, 1])
 def test_every_tile_config(pg, oracle, cfg, epi):
     a, b = wl.config2(520, 776, 328)
