@@ -103,6 +103,30 @@ PG_B200_API int pg_b200_gelu_grad(const float *x, const float *gy, float *out, s
 PG_B200_API int pg_b200_cast_f32(const float *src, uint16_t *dst, int dtype16, size_t n);
 PG_B200_API int pg_b200_fill_f32(float *dst, float value, size_t n);
 
+/* ---- for callers that must not allocate ------------------------------------- */
+
+/* No counterpart in picograd.  pg_gemm_ex for f16/bf16 through the split-K tensor-core path, with
+ * the K-slices kept in a fixed array inside the library image instead of a cudaMalloc'ed buffer, so
+ * that the call allocates nothing (no cudaMalloc / cudaFree / cudaMallocHost, directly or through a
+ * library, on the first call or later).  For code that runs where the allocator is off limits: a
+ * service whose arena already owns all free HBM, a loop that may not take the allocator's lock or the
+ * device-wide synchronisation an allocation implies, a plugin forbidden to allocate after start-up.
+ *   - Device pointers only; a, b 16-byte aligned, lda and ldb multiples of 8 elements, K > 64.
+ *   - k_splits: number of K slices (0 = choose, always >= 2).  k_splits * m * round_up(n,4) * 4
+ *     bytes must fit in PG_B200_STATIC_SCRATCH_BYTES, else PG_ERR_UNSUPPORTED with the sizes in
+ *     pg_b200_last_error().
+ *   - The array costs PG_B200_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the
+ *     library, until the process exits.  All calls share it: calls whose kernels overlap on the GPU
+ *     (other streams, other threads) race; calls on one stream are ordered.
+ *   - The first call on a device resolves the array's device address and sets kernel attributes;
+ *     make that call before any stream capture begins.
+ *   - The call synchronises its stream before returning, so a kernel-side failure is returned as
+ *     PG_ERR_GEMM by the call itself. */
+#define PG_B200_STATIC_SCRATCH_BYTES (16u << 20)
+PG_B200_API int pg_b200_gemm_ex_static_scratch(int dtype, size_t m, size_t n, size_t k,
+                                               const void *a, size_t lda, const void *b, size_t ldb,
+                                               float *c, size_t ldc, int k_splits);
+
 /* ---- control ---------------------------------------------------------------- */
 
 /* Device ordinal used by pg_b200_init (picograd uses device 0, cuda.c:49). */

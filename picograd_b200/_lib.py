@@ -34,6 +34,7 @@ SIGNATURES = {
     "pg_b200_gelu_grad": (_i, [_vp, _vp, _vp, _sz]),
     "pg_b200_cast_f32": (_i, [_vp, _vp, _i, _sz]),
     "pg_b200_fill_f32": (_i, [_vp, C.c_float, _sz]),
+    "pg_b200_gemm_ex_static_scratch": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _i]),
     "pg_b200_set_device": (_i, [_i]),
     "pg_b200_set_stream": (_i, [_vp]),
     "pg_b200_last_error": (C.c_char_p, []),

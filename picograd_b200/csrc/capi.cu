@@ -115,6 +115,25 @@ static int do_init() {
 
 static bool ready() { return do_init() == ST_OK; }
 
+// Device facts the kernels' launchers need (SM count, the tensor-map encoder), gathered without
+// allocating anything; for entry points that must not touch the allocator.
+int ensure_device_info() {
+    if (g.encode && g.sm_count > 0) return ST_OK;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); set_error("no current CUDA device"); return ST_UNSUPPORTED; }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { cudaGetLastError(); set_error("cudaGetDeviceProperties failed"); return ST_UNSUPPORTED; }
+    if (prop.major != 10) { set_error("device %d is sm_%d%d; this library holds sm_100a code only", dev, prop.major, prop.minor); return ST_UNSUPPORTED; }
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr);
+    if (e != cudaSuccess || !fn || qr != cudaDriverEntryPointSuccess) { cudaGetLastError(); set_error("cuTensorMapEncodeTiled not available from the driver"); return ST_UNSUPPORTED; }
+    g.sm_count = prop.multiProcessorCount;
+    g.encode = (EncodeTiledFn)fn;
+    return ST_OK;
+}
+cudaStream_t current_stream() { return g.stream; }
+
 static int grow(DeviceBuf &b, size_t bytes) {
     if (bytes <= b.bytes) return ST_OK;
     if (b.ptr) {

@@ -106,5 +106,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 EncodeTiledFn get_encode_tiled();
 
 int device_sm_count();
+int ensure_device_info();        // fills the above without allocating; ST_OK or ST_UNSUPPORTED
+cudaStream_t current_stream();   // the stream set with pg_b200_set_stream
 
 }  // namespace pgb
