@@ -263,7 +263,10 @@ def run_ours(args, rank, world):
                        "kernel": pg.last_path()},
             "pct_of_nominal_peak": 100.0 * tflops / (NOMINAL_BF16_TFLOPS * world),
             "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": burst, "unit": "TFLOP/s",
-                         "frac": tflops / world / burst, "traffic": None,
+                         "frac": tflops / world / burst,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this
+                         # size, from the ncu capture summarised in profiles/tc_gemm_kernel_bf16_8192.md
+                         "traffic": 1.388e9 if world == 1 else None, "algorithmic_bytes": 536870912 // 1,
                          "peak_source": f"{src} burst bf16 (kernel timed alone, back to back)",
                          "frac_of_sustained": tflops / world / sustained},
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": int((M * K + K * n_loc) * 2),
@@ -280,6 +283,85 @@ def run_ours(args, rank, world):
         dist.destroy_process_group()
 
 
+def run_other_config(args):
+    """Configurations 1, 3a, 3b, 4, 5 on one GPU, device-resident: one JSON line with the time of a
+    whole pass, the flop rate, and the HBM rate for the HBM-bound ones."""
+    import torch
+    import workloads as wl
+    from gpu_util import to_dev
+    import picograd_b200 as pg
+    from picograd_b200 import ops
+    torch.cuda.set_device(0)
+    pg.pg_set_device(0)
+    hbm_peak = 6549.1
+    try:
+        hbm_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        pass
+    burst, sustained, src = measured_peaks()
+    cfg = args.config
+    if cfg == "1":
+        a, b = wl.config1(512)
+        ad, bd = to_dev(a, wl.F32), to_dev(b, wl.F32)
+        fn = lambda: pg.pg_matmul(ad, bd)
+        flops, byts, name, dt = 2.0 * 512 ** 3, 3 * 512 * 512 * 4, "pg_matmul f32 512^3", "f32"
+    elif cfg in ("3a", "3b"):
+        m, n, k = (4096, 14336, 4096) if cfg == "3a" else (16, 4096, 4096)
+        a, b = wl.config3(m, n, k)
+        ad, bd = to_dev(a, wl.F16), to_dev(b, wl.F16)
+        c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        fn = lambda: pg.pg_gemm_ex(wl.F16, m, n, k, ad, k, bd, n, c, n)
+        flops, byts, name, dt = 2.0 * m * n * k, (m * k + k * n) * 2 + m * n * 4, f"pg_gemm_ex f16 {m}x{n}x{k}", "f16"
+    elif cfg == "4":
+        q, kt, v = wl.config4()
+        qd, ktd, vd = (to_dev(x, wl.BF16) for x in (q, kt, v))
+        state = {}
+
+        def fn():
+            s = pg.pg_bmm(qd, ktd)
+            p16 = ops.softmax_rows(s, out16=torch.bfloat16)[1]
+            state["o"] = pg.pg_bmm(p16, vd)
+        flops = 2 * 2.0 * 64 * 2048 * 2048 * 128
+        byts = 1140850688 + 637534208
+        name, dt = "pg_bmm QK^T -> softmax -> PV, bf16 [64,2048,128]", "bf16"
+    else:
+        x, w1, w2 = wl.config5()
+        xd, w1d, w2d = (to_dev(t, wl.BF16) for t in (x, w1, w2))
+
+        def fn():
+            h = pg.pg_matmul(xd, w1d)
+            a16 = ops.gelu(h, out16=torch.bfloat16)[1]
+            y = pg.pg_matmul(a16, w2d)
+            dy = torch.ones_like(y)
+            da, dw2 = pg.pg_matmul_backward(a16, w2d, dy)
+            dh = ops.gelu_grad(h, da)
+            pg.pg_matmul_backward(xd, w1d, dh)
+        flops = 6 * 2.0 * 8192 * 4096 * 16384
+        byts = None
+        name, dt = "MLP step 8192x4096 -> 16384 -> 4096, forward + backward", "bf16"
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    pg.pg_dev_sync()
+    l0 = pg.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    pg.pg_dev_sync()
+    ms = e0.elapsed_time(e1) / args.steps
+    line = {"metric": "time of one pass", "config": {"workload": name, "config": cfg, "kernel": pg.last_path()},
+            "ms_per_step": ms, "value": flops / ms / 1e9, "unit": "TFLOP/s", "dtype": dt, "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "data": "synthetic", "higher_is_better": True,
+            "gpu_launches": pg.launch_count() - l0,
+            "frac_of_measured_bf16_burst": flops / ms / 1e9 / burst}
+    if byts:
+        line["algorithmic_GBps"] = byts / ms / 1e6
+        line["frac_of_measured_hbm"] = byts / ms / 1e6 / hbm_peak
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -287,6 +369,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config", default="2", choices=["1", "2", "3a", "3b", "4", "5"],
+                    help="2 (default) is the headline metric; the others time the remaining configurations "
+                         "(single GPU, device-resident) and print one JSON line each")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -300,6 +385,9 @@ def main():
         sys.exit(subprocess.call(cmd))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.config != "2":
+        run_other_config(args)
         return
     run_ours(args, rank, world)
 
