@@ -35,6 +35,7 @@ struct State {
     int opt_splits = 0;
     int opt_f32_parts = 2;   // bf16 pieces an f32 operand is split into when paired with a 16-bit one
     int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
+    int opt_host_pipeline = 1;   // host-pointer pg_gemm_ex: overlap copies and GEMMs block by block
     int opt_stages = 0;      // 0: all smem stages of the tile configuration
     int opt_debug = 0;       // timing experiments only (see TcGemm::debug)
     char err[512] = "";
@@ -381,6 +382,99 @@ static int gemm_ex_host(int dtype, size_t m, size_t n, size_t k, const void *a, 
     return ST_OK;
 }
 
+// Large host-pointer products: the same staging, cut into blocks of C so that the copies in, the
+// GEMMs and the copies out overlap (PCIe is full duplex; C is as many bytes as A and B together).
+// Row slabs of A and column slabs of B are sent alternately, a block of C is multiplied as soon as
+// its two slabs have landed and goes back while later slabs are still arriving.
+struct HostPipe {
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t ev_a[16] = {}, ev_b[16] = {}, ev_c[256] = {};
+    bool ok = false, tried = false;
+};
+static HostPipe g_pipe;
+
+static bool host_pipe_ready(size_t gm, size_t gn) {
+    if (gm > 16 || gn > 16) return false;
+    if (!g_pipe.tried) {
+        g_pipe.tried = true;
+        bool ok = cudaStreamCreateWithFlags(&g_pipe.in, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&g_pipe.out, cudaStreamNonBlocking) == cudaSuccess;
+        for (int i = 0; ok && i < 16; ++i)
+            ok = cudaEventCreateWithFlags(&g_pipe.ev_a[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&g_pipe.ev_b[i], cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < 256; ++i)
+            ok = cudaEventCreateWithFlags(&g_pipe.ev_c[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) cudaGetLastError();
+        g_pipe.ok = ok;
+    }
+    return g_pipe.ok;
+}
+
+static int gemm_ex_host_pipelined(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b,
+                                  size_t ldb, float *c, size_t ldc, size_t bm, size_t bn) {
+    const size_t es = esize(dtype);
+    const size_t k8 = align_up(k, 8), n8 = align_up(n, 8), n4 = align_up(n, 4);
+    const size_t gm = (m + bm - 1) / bm, gn = (n + bn - 1) / bn;
+    int st;
+    if ((st = grow(g.stage_a, m * k8 * es + 256)) != ST_OK) return st;
+    if ((st = grow(g.stage_b, k * n8 * es + 256)) != ST_OK) return st;
+    if ((st = grow(g.stage_c, m * n4 * 4 + 256)) != ST_OK) return st;
+    char *da = (char *)g.stage_a.ptr, *db = (char *)g.stage_b.ptr;
+    float *dc = (float *)g.stage_c.ptr;
+    cudaError_t e = cudaSuccess;
+    // slabs in, alternating A row slabs and B column slabs; order[] remembers when each one lands
+    size_t when_a[16], when_b[16], tick = 0;
+    for (size_t t = 0; t < (gm > gn ? gm : gn) && e == cudaSuccess; ++t) {
+        if (t < gm) {
+            const size_t r0 = t * bm, rh = (m - r0 < bm) ? m - r0 : bm;
+            e = cudaMemcpy2DAsync(da + r0 * k8 * es, k8 * es, (const char *)a + r0 * lda * es, lda * es, k * es, rh,
+                                  cudaMemcpyHostToDevice, g_pipe.in);
+            if (e == cudaSuccess) e = cudaEventRecord(g_pipe.ev_a[t], g_pipe.in);
+            when_a[t] = tick++;
+        }
+        if (t < gn && e == cudaSuccess) {
+            const size_t c0 = t * bn, cw = (n - c0 < bn) ? n - c0 : bn;
+            e = cudaMemcpy2DAsync(db + c0 * es, n8 * es, (const char *)b + c0 * es, ldb * es, cw * es, k,
+                                  cudaMemcpyHostToDevice, g_pipe.in);
+            if (e == cudaSuccess) e = cudaEventRecord(g_pipe.ev_b[t], g_pipe.in);
+            when_b[t] = tick++;
+        }
+    }
+    if (e != cudaSuccess) { set_error("H2D staging failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_COPY; }
+    // blocks of C in the order in which their slabs become available
+    for (size_t step = 0; step < tick; ++step) {
+        for (size_t i = 0; i < gm; ++i)
+            for (size_t j = 0; j < gn; ++j) {
+                const size_t avail = when_a[i] > when_b[j] ? when_a[i] : when_b[j];
+                if (avail != step) continue;
+                const size_t r0 = i * bm, rh = (m - r0 < bm) ? m - r0 : bm;
+                const size_t c0 = j * bn, cw = (n - c0 < bn) ? n - c0 : bn;
+                cudaStreamWaitEvent(g.stream, g_pipe.ev_a[i], 0);
+                cudaStreamWaitEvent(g.stream, g_pipe.ev_b[j], 0);
+                Problem p = {dtype, dtype, 0, 0, 1, rh, cw, k, da + r0 * k8 * es, k8, 0, db + c0 * es, n8, 0,
+                             dc + r0 * n4 + c0, n4, 0, 0};
+                st = run_problem(p);
+                if (st != ST_OK) { cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream); return st; }
+                cudaEvent_t done = g_pipe.ev_c[i * gn + j];
+                cudaEventRecord(done, g.stream);
+                cudaStreamWaitEvent(g_pipe.out, done, 0);
+                e = cudaMemcpy2DAsync(c + r0 * ldc + c0, ldc * 4, dc + r0 * n4 + c0, n4 * 4, cw * 4, rh,
+                                      cudaMemcpyDeviceToHost, g_pipe.out);
+                if (e != cudaSuccess) {
+                    set_error("D2H staging failed: %s", cudaGetErrorString(e));
+                    cudaGetLastError();
+                    cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream);
+                    return ST_COPY;
+                }
+            }
+    }
+    e = cudaStreamSynchronize(g_pipe.out);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g_pipe.in);
+    if (e != cudaSuccess) { set_error("sync after staged GEMM failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_SYNC; }
+    return ST_OK;
+}
+
 static int gemm_ex_any(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
                        float *c, size_t ldc) {
     if (!ready()) return g.init_status;
@@ -391,7 +485,14 @@ static int gemm_ex_any(int dtype, size_t m, size_t n, size_t k, const void *a, s
         Problem p = {dtype, dtype, 0, 0, 1, m, n, k, a, lda, 0, b, ldb, 0, c, ldc, 0, 0};
         return run_problem(p);
     }
-    if (!da && !db && !dc) return gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc);
+    if (!da && !db && !dc) {
+        // pipeline only products whose copies dominate and that cut into at least 2 x 2 blocks
+        const size_t blk = 2048;
+        if (g.opt_host_pipeline && k > 0 && m >= 2 * blk && n >= 2 * blk && (m + blk - 1) / blk <= 16 &&
+            (n + blk - 1) / blk <= 16 && host_pipe_ready((m + blk - 1) / blk, (n + blk - 1) / blk))
+            return gemm_ex_host_pipelined(dtype, m, n, k, a, lda, b, ldb, c, ldc, blk, blk);
+        return gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc);
+    }
     set_error("pg_gemm_ex: A, B and C must all be device pointers or all host pointers");
     return ST_UNSUPPORTED;
 }
@@ -568,6 +669,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "f32_parts")) { if (value != 2 && value != 3) return ST_UNSUPPORTED; g.opt_f32_parts = value; return ST_OK; }
     if (!strcmp(name, "f32_tensor_cores")) { g.opt_f32_tc = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "stages")) { g.opt_stages = value; return ST_OK; }
+    if (!strcmp(name, "host_pipeline")) { g.opt_host_pipeline = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);
     return ST_UNSUPPORTED;

@@ -818,26 +818,27 @@ static const CfgRuntime &prepare_cfg(int cfg) {
 
 static uint32_t cdiv(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 
-// Pick a tile configuration: the 256x256 CTA-pair tile for large problems, narrower
-// tiles when that would leave SMs idle.
+// Pick a tile configuration.  Cost model fitted to measurements on B200 (bf16, K = 8192):
+// relative throughput per configuration at full occupancy, and a last partial wave that costs
+// 0.5 + 0.5 * occupancy of a full one (fewer CTAs run faster: more clock and more L2 each).
 static int choose_cfg(const TcGemm &g) {
     if (g.force_cfg >= 0 && g.force_cfg < NUM_CFGS) return g.force_cfg;
-    const int sms = device_sm_count();
     int best = 0;
     double best_cost = 1e300;
     for (int i = 0; i < NUM_CFGS; ++i) {
         const TcConfig &c = g_cfgs[i];
+        if (c.sub != 1 || !c.staging) continue;          // experimental variants are chosen by hand only
         const CfgRuntime &rt = prepare_cfg(i);
         if (!rt.usable) continue;
-        uint64_t tiles = (uint64_t)g.batch * cdiv(g.M, BM_CTA * c.cg) * cdiv(g.N, c.bn) * (g.splits ? g.splits : 1);
-        uint64_t slots = (uint64_t)rt.max_clusters;
-        uint64_t waves = (tiles + slots - 1) / slots;
-        // time ~ waves * (MMA work per SM of one tile, padded) ; wider tiles stream less per flop
-        double per_tile = (double)BM_CTA * c.bn;                       // MMA columns*rows per SM
-        double eff = c.bn >= 256 ? 1.0 : (c.bn == 128 ? 0.92 : 0.80);  // narrower N wastes smem bandwidth
-        if (c.cg == 2) eff *= 1.04;                                   // pair halves B traffic per SM
-        double cost = (double)waves * per_tile / eff;
-        (void)sms;
+        const uint64_t tiles = (uint64_t)g.batch * cdiv(g.M, BM_CTA * c.cg) * cdiv(g.N, c.bn) * (g.splits ? g.splits : 1);
+        const uint64_t slots = (uint64_t)rt.max_clusters;
+        const uint64_t full = tiles / slots, tail = tiles % slots;
+        const double waves = (double)full + (tail ? 0.5 + 0.5 * (double)tail / (double)slots : 0.0);
+        double eff;
+        if (c.cg == 2) eff = c.bn >= 256 ? 1.0 : 0.75;
+        else eff = c.bn >= 256 ? 0.885 : (c.bn == 128 ? 0.71 : 0.45);
+        // time ~ waves * tile area per SM / efficiency
+        const double cost = waves * (double)BM_CTA * c.bn / eff;
         if (cost < best_cost) { best_cost = cost; best = i; }
     }
     return best;

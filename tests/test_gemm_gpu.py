@@ -168,6 +168,27 @@ def test_host_pointer_gemm_ex(pg, oracle):
     assert wl.relerr(c[:, :200], oracle.gemm_ex(wl.BF16, a, b)) <= wl.tolerance(wl.BF16, 264)
 
 
+def test_host_pointer_gemm_ex_pipelined_blocks(pg):
+    """Large host-pointer products are staged block by block (copies overlap the GEMMs); the result
+    must be the one the plain staging gives, bit for bit, including ragged last blocks and ld slack."""
+    m, n, k = 4096 + 136, 4096 + 72, 264
+    a, b = wl.config2(m, n, k)
+    abuf = np.zeros((m, k + 8), np.uint16); abuf[:, :k] = a
+    bbuf = np.zeros((k, n + 16), np.uint16); bbuf[:, :n] = b
+    outs = []
+    for pipelined in (1, 0):
+        pg.set_option("host_pipeline", pipelined)
+        c = np.full((m, n + 4), 0xAB, np.float32)
+        pg.pg_gemm_ex_host(wl.BF16, m, n, k, abuf, k + 8, bbuf, n + 16, c, n + 4)
+        assert np.all(c[:, n:] == np.float32(0xAB))
+        outs.append(c[:, :n].copy())
+    pg.set_option("host_pipeline", 1)
+    assert np.array_equal(outs[0], outs[1])
+    ad, bd = to_dev(a, wl.BF16), to_dev(b, wl.BF16)
+    want = pg.pg_matmul(ad, bd); pg.pg_dev_sync()
+    assert wl.relerr(outs[0], to_host(want)) <= 1e-6
+
+
 def test_matmul_shape_modes(pg):
     """tests/test_ops.c:368-492: 2-D, vec.vec, vec.mat, mat.vec, bmm, batched.unbatched; 1e-4*(1+|y|)."""
     rng = np.random.default_rng(12)
