@@ -29,6 +29,14 @@ __device__ __forceinline__ float bf16_up(unsigned short h) { return __uint_as_fl
 // x = p0 + p1 (+ p2) with every piece a bf16 and every subtraction exact:
 // p0 = bf16(x), p1 = bf16(x - p0), p2 = bf16(x - p0 - p1).
 // Layout of dst: [batch][part][rows][ld_dst].
+__device__ __forceinline__ void split3(float x, unsigned short &h0, unsigned short &h1, unsigned short &h2) {
+    h0 = bf16_rne(x);
+    const float r1 = x - bf16_up(h0);
+    h1 = bf16_rne(r1);
+    h2 = bf16_rne(r1 - bf16_up(h1));
+}
+
+// General form: any leading dimensions, one element per thread step.
 __global__ void split_f32_kernel(const float *__restrict__ src, uint64_t ld_src, uint64_t src_bs,
                                  unsigned short *__restrict__ dst, uint64_t ld_dst, uint32_t rows, uint32_t cols,
                                  uint32_t batch, uint32_t nparts) {
@@ -39,16 +47,39 @@ __global__ void split_f32_kernel(const float *__restrict__ src, uint64_t ld_src,
         const uint64_t b = i / per_batch;
         const uint64_t r = (i - b * per_batch) / cols;
         const uint64_t c = i - b * per_batch - r * cols;
-        float x = src[b * src_bs + r * ld_src + c];
+        unsigned short h0, h1, h2;
+        split3(src[b * src_bs + r * ld_src + c], h0, h1, h2);
         unsigned short *d = dst + b * nparts * part_stride + r * ld_dst + c;
-        unsigned short h0 = bf16_rne(x);
         d[0] = h0;
-        float r1 = x - bf16_up(h0);
-        unsigned short h1 = bf16_rne(r1);
         d[part_stride] = h1;
-        if (nparts > 2) {
-            float r2 = r1 - bf16_up(h1);
-            d[2 * part_stride] = bf16_rne(r2);
+        if (nparts > 2) d[2 * part_stride] = h2;
+    }
+}
+
+// Fast form for the common case (cols and both leading dimensions multiples of 4, 16-byte aligned
+// bases): four elements per thread step, one 16-byte load and one 8-byte store per piece.
+__global__ void split_f32_vec4_kernel(const float *__restrict__ src, uint64_t ld_src, uint64_t src_bs,
+                                      unsigned short *__restrict__ dst, uint64_t ld_dst, uint32_t rows, uint32_t cols4,
+                                      uint32_t batch, uint32_t nparts) {
+    const uint64_t per_batch = (uint64_t)rows * cols4;
+    const uint64_t total = per_batch * batch;
+    const uint64_t part_stride = (uint64_t)rows * ld_dst;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t b = i / per_batch;
+        const uint64_t r = (i - b * per_batch) / cols4;
+        const uint64_t c = (i - b * per_batch - r * cols4) * 4;
+        const float4 x = *reinterpret_cast<const float4 *>(src + b * src_bs + r * ld_src + c);
+        unsigned short h[3][4];
+        split3(x.x, h[0][0], h[1][0], h[2][0]);
+        split3(x.y, h[0][1], h[1][1], h[2][1]);
+        split3(x.z, h[0][2], h[1][2], h[2][2]);
+        split3(x.w, h[0][3], h[1][3], h[2][3]);
+        unsigned short *d = dst + b * nparts * part_stride + r * ld_dst + c;
+        for (uint32_t p = 0; p < nparts; ++p) {
+            uint2 v;
+            v.x = (uint32_t)h[p][0] | ((uint32_t)h[p][1] << 16);
+            v.y = (uint32_t)h[p][2] | ((uint32_t)h[p][3] << 16);
+            *reinterpret_cast<uint2 *>(d + p * part_stride) = v;
         }
     }
 }
@@ -57,7 +88,13 @@ int split_f32_to_bf16_launch(const float *src, uint64_t ld_src, uint64_t src_bs,
                              uint32_t rows, uint32_t cols, uint32_t batch, uint32_t nparts, cudaStream_t s) {
     const uint64_t total = (uint64_t)rows * cols * batch;
     if (!total) return ST_OK;
-    split_f32_kernel<<<grid_for(total, 256), 256, 0, s>>>(src, ld_src, src_bs, dst, ld_dst, rows, cols, batch, nparts);
+    const bool vec = cols % 4 == 0 && ld_src % 4 == 0 && ld_dst % 4 == 0 && src_bs % 4 == 0 &&
+                     ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 7) == 0;
+    if (vec)
+        split_f32_vec4_kernel<<<grid_for(total / 4, 256), 256, 0, s>>>(src, ld_src, src_bs, dst, ld_dst, rows, cols / 4,
+                                                                       batch, nparts);
+    else
+        split_f32_kernel<<<grid_for(total, 256), 256, 0, s>>>(src, ld_src, src_bs, dst, ld_dst, rows, cols, batch, nparts);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
@@ -141,41 +178,67 @@ int cast_f32_launch(const float *src, uint16_t *dst, uint64_t n, int dtype, cuda
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
-// 0.5 x (1 + erf(x / sqrt 2))   (picograd ops/activations.c:114)
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118f)); }
+__device__ __forceinline__ float gelu_grad_f(float v, float gy) {
+    const float e = erff(v * 0.70710678118f);
+    const float phi = expf(-0.5f * v * v) / 2.50662827463f;
+    return gy * (0.5f * (1.0f + e) + v * phi);
+}
+
+// 0.5 x (1 + erf(x / sqrt 2))   (picograd ops/activations.c:114); four elements per thread step when
+// the buffers are 16-byte aligned, the tail (and unaligned buffers) one by one.
 __global__ void gelu_kernel(const float *__restrict__ src, float *__restrict__ d32, unsigned short *__restrict__ d16,
-                            int dtype16, uint64_t n) {
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-        const float x = src[i];
-        const float y = 0.5f * x * (1.0f + erff(x * 0.70710678118f));
+                            int dtype16, uint64_t n, int vec) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t n4 = vec ? n / 4 : 0;
+    for (uint64_t i = tid; i < n4; i += stride) {
+        const float4 x = reinterpret_cast<const float4 *>(src)[i];
+        const float4 y = make_float4(gelu_f(x.x), gelu_f(x.y), gelu_f(x.z), gelu_f(x.w));
+        if (d32) reinterpret_cast<float4 *>(d32)[i] = y;
+        if (d16) {
+            uint2 v;
+            v.x = (uint32_t)to16(y.x, dtype16) | ((uint32_t)to16(y.y, dtype16) << 16);
+            v.y = (uint32_t)to16(y.z, dtype16) | ((uint32_t)to16(y.w, dtype16) << 16);
+            reinterpret_cast<uint2 *>(d16)[i] = v;
+        }
+    }
+    for (uint64_t i = n4 * 4 + tid; i < n; i += stride) {
+        const float y = gelu_f(src[i]);
         if (d32) d32[i] = y;
         if (d16) d16[i] = to16(y, dtype16);
     }
 }
 int gelu_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16, uint64_t n, cudaStream_t s) {
     if (!n) return ST_OK;
-    gelu_kernel<<<grid_for(n, 256), 256, 0, s>>>(src, dst_f32, dst_16, dtype16, n);
+    const int vec = (((uintptr_t)src | (uintptr_t)dst_f32) & 15) == 0 && ((uintptr_t)dst_16 & 7) == 0;
+    gelu_kernel<<<grid_for(vec ? n / 4 + 1 : n, 256), 256, 0, s>>>(src, dst_f32, dst_16, dtype16, n, vec);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
 // gy * (0.5 (1 + erf(x/sqrt 2)) + x phi(x))   (picograd autograd/autograd.c:794-801, :531-532)
 __global__ void gelu_grad_kernel(const float *__restrict__ x, const float *__restrict__ gy, float *__restrict__ out,
-                                 uint64_t n) {
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-        const float v = x[i];
-        const float e = erff(v * 0.70710678118f);
-        const float phi = expf(-0.5f * v * v) / 2.50662827463f;
-        out[i] = gy[i] * (0.5f * (1.0f + e) + v * phi);
+                                 uint64_t n, int vec) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t n4 = vec ? n / 4 : 0;
+    for (uint64_t i = tid; i < n4; i += stride) {
+        const float4 v = reinterpret_cast<const float4 *>(x)[i];
+        const float4 g = reinterpret_cast<const float4 *>(gy)[i];
+        reinterpret_cast<float4 *>(out)[i] =
+            make_float4(gelu_grad_f(v.x, g.x), gelu_grad_f(v.y, g.y), gelu_grad_f(v.z, g.z), gelu_grad_f(v.w, g.w));
     }
+    for (uint64_t i = n4 * 4 + tid; i < n; i += stride) out[i] = gelu_grad_f(x[i], gy[i]);
 }
 int gelu_grad_launch(const float *x, const float *gy, float *out, uint64_t n, cudaStream_t s) {
     if (!n) return ST_OK;
-    gelu_grad_kernel<<<grid_for(n, 256), 256, 0, s>>>(x, gy, out, n);
+    const int vec = (((uintptr_t)x | (uintptr_t)gy | (uintptr_t)out) & 15) == 0;
+    gelu_grad_kernel<<<grid_for(vec ? n / 4 + 1 : n, 256), 256, 0, s>>>(x, gy, out, n, vec);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
 // One warp per row: max, sum of exp(x - max), normalise (picograd ops/activations.c:22-45).
+// General form: three passes over the row (it stays in L1/L2 between them).
 __global__ void softmax_rows_kernel(const float *__restrict__ src, float *__restrict__ d32,
                                     unsigned short *__restrict__ d16, int dtype16, uint64_t rows, uint32_t len) {
     const uint32_t lane = threadIdx.x & 31;
@@ -196,10 +259,59 @@ __global__ void softmax_rows_kernel(const float *__restrict__ src, float *__rest
         }
     }
 }
+
+// Fast form: the row lives in registers (VEC float4 per lane, len == 128 * VEC), read once with
+// 16-byte loads, exp evaluated once per element, written with 16-byte (f32) / 8-byte (16-bit) stores.
+template <int VEC>
+__global__ void __launch_bounds__(256) softmax_rows_reg_kernel(const float *__restrict__ src, float *__restrict__ d32,
+                                                               unsigned short *__restrict__ d16, int dtype16,
+                                                               uint64_t rows) {
+    constexpr uint32_t LEN = 128 * VEC;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    for (uint64_t row = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
+        const float4 *s = reinterpret_cast<const float4 *>(src + row * LEN);
+        float4 v[VEC];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            v[i] = s[lane + 32 * i];
+            mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+        }
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            v[i].x = expf(v[i].x - mx); v[i].y = expf(v[i].y - mx); v[i].z = expf(v[i].z - mx); v[i].w = expf(v[i].w - mx);
+            sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float inv = 1.0f / sum;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const float4 y = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+            if (d32) reinterpret_cast<float4 *>(d32 + row * LEN)[lane + 32 * i] = y;
+            if (d16) {
+                uint2 u;
+                u.x = (uint32_t)to16(y.x, dtype16) | ((uint32_t)to16(y.y, dtype16) << 16);
+                u.y = (uint32_t)to16(y.z, dtype16) | ((uint32_t)to16(y.w, dtype16) << 16);
+                reinterpret_cast<uint2 *>(d16 + row * LEN)[lane + 32 * i] = u;
+            }
+        }
+    }
+}
+
 int softmax_rows_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16, uint64_t rows, uint32_t len,
                         cudaStream_t s) {
     if (!rows || !len) return ST_OK;
-    softmax_rows_kernel<<<grid_for(rows * 32, 256), 256, 0, s>>>(src, dst_f32, dst_16, dtype16, rows, len);
+    const bool aligned = (((uintptr_t)src | (uintptr_t)dst_f32) & 15) == 0 && ((uintptr_t)dst_16 & 7) == 0;
+    const unsigned grid = grid_for(rows * 32, 256);
+    if (aligned && len == 2048) softmax_rows_reg_kernel<16><<<grid, 256, 0, s>>>(src, dst_f32, dst_16, dtype16, rows);
+    else if (aligned && len == 1024) softmax_rows_reg_kernel<8><<<grid, 256, 0, s>>>(src, dst_f32, dst_16, dtype16, rows);
+    else if (aligned && len == 512) softmax_rows_reg_kernel<4><<<grid, 256, 0, s>>>(src, dst_f32, dst_16, dtype16, rows);
+    else if (aligned && len == 256) softmax_rows_reg_kernel<2><<<grid, 256, 0, s>>>(src, dst_f32, dst_16, dtype16, rows);
+    else if (aligned && len == 128) softmax_rows_reg_kernel<1><<<grid, 256, 0, s>>>(src, dst_f32, dst_16, dtype16, rows);
+    else softmax_rows_kernel<<<grid, 256, 0, s>>>(src, dst_f32, dst_16, dtype16, rows, len);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }

@@ -28,6 +28,7 @@ struct State {
     unsigned long long *prof = nullptr;   // per-CTA cycle counters of the timing experiments
     DeviceBuf ws;                      // scratch: operand pieces, split-K slices
     DeviceBuf stage_a, stage_b, stage_c;  // device staging for host-pointer calls
+    DeviceBuf grad_pieces;             // bf16 pieces of the f32 gradient, shared by both backward products
     // options
     int opt_path = 0;        // 0 choose, 1 tensor-core only, 2 FFMA only
     int opt_cfg = -1;
@@ -170,6 +171,11 @@ struct Problem {
     const void *b; size_t ldb, stride_b;
     float *c; size_t ldc, stride_c;
     int accumulate;
+    // an f32 operand whose bf16 pieces the caller has already made ([batch][piece][rows][ld]): lets
+    // the two products of a backward pass share one split of the gradient
+    const uint16_t *a_pieces = nullptr, *b_pieces = nullptr;
+    size_t pieces_ld = 0;
+    uint32_t pieces_n = 0;
 };
 
 static int run_simt(const Problem &p) {
@@ -198,8 +204,8 @@ static uint32_t parts_for(int dt, int other_dt) {
 // Tensor-core route.  Returns ST_UNSUPPORTED when the operands break a TMA rule.
 static int run_tc(const Problem &p) {
     const bool mixed = p.dtype_a != p.dtype_b || p.dtype_a == DT_F32;
-    const uint32_t npa = mixed ? parts_for(p.dtype_a, p.dtype_b) : 1u;
-    const uint32_t npb = mixed ? parts_for(p.dtype_b, p.dtype_a) : 1u;
+    const uint32_t npa = p.a_pieces ? p.pieces_n : (mixed ? parts_for(p.dtype_a, p.dtype_b) : 1u);
+    const uint32_t npb = p.b_pieces ? p.pieces_n : (mixed ? parts_for(p.dtype_b, p.dtype_a) : 1u);
     if (p.m > 0x7FFFFFFFull || p.n > 0x7FFFFFFFull || p.k > 0x7FFFFFFFull || p.batch > 0x7FFFFFFull) return ST_UNSUPPORTED;
 
     TcGemm t = {};
@@ -233,10 +239,11 @@ static int run_tc(const Problem &p) {
     // ---- scratch layout -------------------------------------------------------
     const size_t a_rows = p.trans_a ? p.k : p.m, a_cols = p.trans_a ? p.m : p.k;
     const size_t b_rows = p.trans_b ? p.n : p.k, b_cols = p.trans_b ? p.k : p.n;
-    const size_t a_ld2 = align_up(a_cols, 8), b_ld2 = align_up(b_cols, 8);
+    const size_t a_ld2 = p.a_pieces ? p.pieces_ld : align_up(a_cols, 8);
+    const size_t b_ld2 = p.b_pieces ? p.pieces_ld : align_up(b_cols, 8);
     size_t off = 0, off_a = 0, off_b = 0, off_k = 0;
-    if (npa > 1) { off_a = off; off = align_up(off + p.batch * npa * a_rows * a_ld2 * 2, 256); }
-    if (npb > 1) { off_b = off; off = align_up(off + p.batch * npb * b_rows * b_ld2 * 2, 256); }
+    if (npa > 1 && !p.a_pieces) { off_a = off; off = align_up(off + p.batch * npa * a_rows * a_ld2 * 2, 256); }
+    if (npb > 1 && !p.b_pieces) { off_b = off; off = align_up(off + p.batch * npb * b_rows * b_ld2 * 2, 256); }
 
     // split-K for shapes that would leave most SMs idle
     uint32_t splits = 1;
@@ -269,7 +276,9 @@ static int run_tc(const Problem &p) {
     char *ws = (char *)g.ws.ptr;
 
     // ---- operand pieces -----------------------------------------------------------
-    if (npa > 1) {
+    if (p.a_pieces) {
+        t.A.ptr = p.a_pieces; t.A.ld = a_ld2; t.A.z_stride = a_rows * a_ld2; t.A.nparts = npa;
+    } else if (npa > 1) {
         uint16_t *dst = (uint16_t *)(ws + off_a);
         int st;
         if (p.dtype_a == DT_F32)
@@ -283,7 +292,9 @@ static int run_tc(const Problem &p) {
     } else if (mixed && p.dtype_a == DT_F16) {
         return ST_UNSUPPORTED;
     }
-    if (npb > 1) {
+    if (p.b_pieces) {
+        t.B.ptr = p.b_pieces; t.B.ld = b_ld2; t.B.z_stride = b_rows * b_ld2; t.B.nparts = npb;
+    } else if (npb > 1) {
         uint16_t *dst = (uint16_t *)(ws + off_b);
         int st;
         if (p.dtype_b == DT_F32)
@@ -601,24 +612,44 @@ int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int trans_b, siz
 int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t k, const void *a, const void *b,
                             int b_batched, const float *gr, float *ga, float *gb) {
     if (!ready()) return g.init_status;
+    if (batch == 0 || m == 0 || n == 0 || k == 0) return ST_OK;
     int st = ST_OK;
+    // The f32 gradient meets the tensor cores as exact bf16 pieces; both products read the same
+    // [batch*m, n] matrix, so it is split once.  (f16 operands and tiny or unaligned shapes go
+    // through the general route, which splits per product or uses the FFMA kernel.)
+    const uint16_t *pieces = nullptr;
+    const size_t ld2 = align_up(n, 8);
+    const uint32_t np = (uint32_t)g.opt_f32_parts;
+    const bool share = dtype == DT_BF16 && g.opt_path != 2 && ga && gb && (uint64_t)batch * m * n * k > (uint64_t)64 * 64 * 64 &&
+                       (uint64_t)batch * m <= 0x7FFFFFFFull && (!b_batched || batch == 1);
+    if (share) {
+        st = grow(g.grad_pieces, (size_t)np * batch * m * ld2 * 2 + 256);
+        if (st != ST_OK) return st;
+        // one "batch" of batch*m rows: pieces laid out [piece][batch*m][ld2]
+        st = split_f32_to_bf16_launch(gr, n, 0, (uint16_t *)g.grad_pieces.ptr, ld2, (uint32_t)(batch * m), (uint32_t)n, 1, np,
+                                      g.stream);
+        if (st != ST_OK) return st;
+        pieces = (const uint16_t *)g.grad_pieces.ptr;
+    }
     if (ga) {
         // ga[batch][m][k] += g[batch][m][n] * B^T : the product's "A" is g (m x n), its "B" is B (stored
         // k x n) read transposed.  A B shared by the batch folds the batch into the rows of g and ga.
         Problem p = {DT_F32, dtype, 0, 1, batch, m, k, n, gr, n, m * n, b, n, k * n, ga, k, m * k, 1};
         if (!b_batched) { p.batch = 1; p.m = batch * m; p.stride_a = p.stride_b = p.stride_c = 0; }
+        if (pieces && p.batch == 1) { p.a_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; }
         st = run_problem(p);
         if (st != ST_OK) return st;
     }
     if (gb) {
-        if (b_batched || batch == 1) {
+        if (b_batched && batch > 1) {
             // gb[batch][k][n] += A^T[batch][k][m] * g[batch][m][n]
             Problem p = {dtype, DT_F32, 1, 0, batch, k, n, m, a, k, m * k, gr, n, m * n, gb, n, k * n, 1};
             st = run_problem(p);
         } else {
-            // B shared by the batch: gb[k][n] += sum_b A[b]^T g[b]  ==  one product with the batch folded into the
-            // contraction: A as [(batch*m)][k], g as [(batch*m)][n]
+            // B shared by the batch (or no batch): gb[k][n] += sum_b A[b]^T g[b]  ==  one product with the
+            // batch folded into the contraction: A as [(batch*m)][k], g as [(batch*m)][n]
             Problem p = {dtype, DT_F32, 1, 0, 1, k, n, batch * m, a, k, 0, gr, n, 0, gb, n, 0, 1};
+            if (pieces) { p.b_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; }
             st = run_problem(p);
         }
     }
