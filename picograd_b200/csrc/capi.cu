@@ -26,6 +26,8 @@ struct State {
     uint32_t *dev_status = nullptr;
     uint32_t *host_status = nullptr;   // pinned mirror
     unsigned long long *prof = nullptr;   // per-CTA cycle counters of the timing experiments
+    uint32_t *counters = nullptr;         // arrival counters of the fused split-K reduction (zero between launches)
+    uint32_t num_counters = 0;
     DeviceBuf ws;                      // scratch: operand pieces, split-K slices
     DeviceBuf stage_a, stage_b, stage_c;  // device staging for host-pointer calls
     DeviceBuf grad_pieces;             // bf16 pieces of the f32 gradient, shared by both backward products
@@ -37,6 +39,8 @@ struct State {
     int opt_f32_parts = 2;   // bf16 pieces an f32 operand is split into when paired with a 16-bit one
     int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
     int opt_host_pipeline = 1;   // host-pointer pg_gemm_ex: overlap copies and GEMMs block by block
+    int opt_fused_splitk = 1;    // split-K slices summed by the GEMM kernel itself (else a second kernel)
+    int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
     int opt_stages = 0;      // 0: all smem stages of the tile configuration
     int opt_debug = 0;       // timing experiments only (see TcGemm::debug)
     char err[512] = "";
@@ -112,6 +116,12 @@ static int do_init() {
     *g.host_status = 0;
     if (cudaMalloc((void **)&g.prof, 512 * 16 * 8) == cudaSuccess) cudaMemset(g.prof, 0, 512 * 16 * 8);
     else { g.prof = nullptr; cudaGetLastError(); }
+    g.num_counters = 1u << 16;
+    if (cudaMalloc((void **)&g.counters, (size_t)g.num_counters * 4) == cudaSuccess) {
+        cudaMemset(g.counters, 0, (size_t)g.num_counters * 4);
+    } else {
+        g.counters = nullptr; g.num_counters = 0; cudaGetLastError();
+    }
     return g.init_status = ST_OK;
 }
 
@@ -245,6 +255,11 @@ static int run_tc(const Problem &p) {
     if (npa > 1 && !p.a_pieces) { off_a = off; off = align_up(off + p.batch * npa * a_rows * a_ld2 * 2, 256); }
     if (npb > 1 && !p.b_pieces) { off_b = off; off = align_up(off + p.batch * npb * b_rows * b_ld2 * 2, 256); }
 
+    // Skinny M (decode-like): multiply with the operands swapped, C^T = B^T A^T, so that N fills the
+    // 128 tensor-memory lanes and M becomes a 16- or 32-wide UMMA N: a stage then holds 16 KB of B and
+    // only 2-4 KB of A (12 stages in flight), and the transposed store is coalesced.
+    const bool swap = g.opt_swap_skinny && g.opt_cfg < 0 && !mixed && p.batch == 1 && !p.trans_a && p.m <= 32 &&
+                      p.n >= 256;
     // split-K for shapes that would leave most SMs idle
     uint32_t splits = 1;
     const uint32_t k_blocks = (uint32_t)((p.k + 63) / 64);
@@ -252,7 +267,7 @@ static int run_tc(const Problem &p) {
         if (g.opt_splits > 0) {
             splits = (uint32_t)g.opt_splits;
         } else {
-            const uint64_t tiles = ((p.m + 127) / 128) * ((p.n + 127) / 128);
+            const uint64_t tiles = swap ? (p.n + 127) / 128 : ((p.m + 127) / 128) * ((p.n + 127) / 128);
             const uint32_t sms = (uint32_t)device_sm_count();
             if (tiles * 2 <= sms && k_blocks >= 8) {
                 uint32_t want = (uint32_t)(sms / tiles);
@@ -323,17 +338,38 @@ static int run_tc(const Problem &p) {
         t.npass = np; t.a_sel = asel; t.b_sel = bsel;
     }
 
+    bool fused = false;
     if (splits > 1) {
         t.splits = splits;
         t.C = (float *)(ws + off_k);
         t.ldc = ws_ld;
         t.c_stride = p.m * ws_ld;
-        t.accumulate = 0;
+        fused = g.opt_fused_splitk && g.counters != nullptr;
+        if (fused) {
+            t.Cout = p.c; t.ldc_out = p.ldc; t.counters = g.counters; t.num_counters = g.num_counters;
+            t.accumulate = p.accumulate;           // applied by the final sum only
+        } else {
+            t.accumulate = 0;
+        }
+    }
+    if (swap) {
+        // A' = B (its N runs along the tile rows), B' = A, tile stored transposed into the same C
+        TcOperand opa = t.A;
+        t.A = t.B; t.A.mn_major = p.trans_b ? 0u : 1u;
+        t.B = opa; t.B.mn_major = 0u;
+        t.M = (uint32_t)p.n; t.N = (uint32_t)p.m;
+        t.c_trans = 1;
+        t.force_cfg = p.m <= 16 ? tc_config_index("1cta_128x16_t") : tc_config_index("1cta_128x32_t");
     }
     if (g.opt_path != 1 && !tc_gemm_supported(t)) return ST_UNSUPPORTED;
     int st = tc_gemm_launch(t);
+    if (st == ST_UNSUPPORTED && fused) {           // more slabs than counters: fall back to the two-kernel form
+        fused = false;
+        t.Cout = nullptr; t.accumulate = 0;
+        st = tc_gemm_launch(t);
+    }
     if (st != ST_OK) return st;
-    if (splits > 1) {
+    if (splits > 1 && !fused) {
         st = reduce_splits_launch((const float *)(ws + off_k), p.m * ws_ld, splits, p.c, p.ldc, (uint32_t)p.m,
                                   (uint32_t)p.n, ws_ld, p.accumulate, g.stream);
         if (st != ST_OK) return st;
@@ -573,6 +609,7 @@ int pg_b200_sync(void) {
         set_error("a GEMM kernel gave up waiting (status bits 0x%x)", *g.host_status);
         *g.host_status = 0;
         cudaMemsetAsync(g.dev_status, 0, 4, g.stream);
+        if (g.counters) cudaMemsetAsync(g.counters, 0, (size_t)g.num_counters * 4, g.stream);   // an aborted kernel may leave counts
         cudaStreamSynchronize(g.stream);
         return ST_GEMM;
     }
@@ -701,6 +738,8 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "f32_tensor_cores")) { g.opt_f32_tc = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "stages")) { g.opt_stages = value; return ST_OK; }
     if (!strcmp(name, "host_pipeline")) { g.opt_host_pipeline = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "fused_splitk")) { g.opt_fused_splitk = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "swap_skinny")) { g.opt_swap_skinny = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);
     return ST_UNSUPPORTED;

@@ -26,6 +26,7 @@
 #include "pg_internal.h"
 
 #include <stdio.h>
+#include <string.h>
 
 namespace pgb {
 
@@ -36,31 +37,37 @@ constexpr uint32_t BM_CTA = 128;                 // C rows per CTA == TMEM lanes
 constexpr uint32_t BK = 64;                      // 64 x 16-bit = one 128-byte swizzle row
 constexpr uint32_t UMMA_K = 16;                  // K of one tcgen05.mma for 16-bit inputs
 constexpr uint32_t A_TILE_BYTES = BM_CTA * BK * 2;
-constexpr uint32_t EPI_WARPS = 4;
 constexpr uint32_t EPI_COLS = 32;                // columns per tcgen05.ld / per TMA-store box
 constexpr uint32_t EPI_BUF_BYTES = 32 * EPI_COLS * 4;
-constexpr uint32_t EPI_BUFS = 2;
-constexpr uint32_t NUM_THREADS = 32 * (2 + EPI_WARPS);
 constexpr uint32_t SMEM_LIMIT = 232448;          // 227 KB opt-in maximum per CTA
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
-template <int CG, int BN, int SUB, bool STAGING>
+// CG      CTAs per tile (1, or 2 = cta_group::2 pair)
+// BN      columns of the tile (UMMA N)
+// SUB     64-deep K blocks per pipeline stage
+// STAGING epilogue goes through shared memory and TMA stores (else straight from registers)
+// EW      epilogue warps (4, or 8: two per TMEM lane quadrant, alternating column chunks)
+// EB      staging buffers per epilogue warp
+template <int CG, int BN, int SUB, bool STAGING, int EW, int EB>
 struct Cfg {
     static constexpr uint32_t BN_CTA = BN / CG;                      // B columns loaded by one CTA
     static constexpr uint32_t B_TILE_BYTES = BN_CTA * BK * 2;
     static constexpr uint32_t SUB_BYTES = A_TILE_BYTES + B_TILE_BYTES;  // one 64-deep K block of A and B
     static constexpr uint32_t STAGE_BYTES = SUB * SUB_BYTES;            // SUB K blocks share one barrier round
-    // staging buffers of the TMA-store epilogue; a configuration without them stores C straight
-    // from registers and spends the memory on one more pipeline stage
-    static constexpr uint32_t EPI_BYTES = STAGING ? EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES : 0;
+    static constexpr uint32_t EPI_BYTES = STAGING ? EW * EB * EPI_BUF_BYTES : 0;
     static constexpr uint32_t BAR_BYTES = 512;
     static constexpr uint32_t STAGES_RAW = (SMEM_LIMIT - 1024 - EPI_BYTES - BAR_BYTES) / STAGE_BYTES;
     static constexpr uint32_t STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
     static constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
-    static constexpr uint32_t TMEM_COLS = 2 * BN;                    // two accumulators
+    static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
+    static constexpr uint32_t THREADS = 32 * (2 + EW);
+    static constexpr uint32_t EPI_W = BN < 32 ? BN : 32;             // columns per epilogue chunk
+    static_assert(EW == 4 || EW == 8, "epilogue warps");
     static_assert(STAGES >= 2, "pipeline too shallow");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
     static_assert(SUB_BYTES % 1024 == 0, "tiles must keep the 1024-byte swizzle alignment");
+    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
+    static_assert(STAGING ? BN >= 32 : true, "the TMA-store epilogue works on 32-column chunks");
 };
 
 struct TcParams {
@@ -78,8 +85,13 @@ struct TcParams {
     uint32_t stages;              // smem stages in use (<= the configuration's maximum)
     uint32_t debug;               // timing experiments only (results are garbage): 1 = no TMA loads, 2 = no C
                                   // stores, 4 = no TMEM reads, 8 = alternate accumulators, 16 = no MMAs
-    float *C;
+    uint32_t c_trans;             // element (row, col) of the tile goes to C[col*ldc + row] (swapped operands)
+    float *C;                     // splits > 1: the K-slices [split][rows][ldc]; else the result
     uint64_t ldc, c_stride;
+    // fused split-K reduction: the last warp to finish a slab sums the slices (in slice order) into Cout
+    float *Cout;
+    uint64_t ldc_out;
+    uint32_t *counters;           // one per (tile, CTA of the pair, epilogue warp); zero between launches
     uint32_t *status;
     unsigned long long *prof;     // debug & 32: 16 cycle counters per CTA
 };
@@ -317,6 +329,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor for a 128-byte-swizzled tile (version 1 = Blackwell).
@@ -362,11 +383,12 @@ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-template <int CG, int BN, int SUB, bool STAGING>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int CG, int BN, int SUB, bool STAGING, int EW, int EB>
+__global__ void __launch_bounds__(32 * (2 + EW), 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const TcParams p) {
-    using C_ = Cfg<CG, BN, SUB, STAGING>;
+    using C_ = Cfg<CG, BN, SUB, STAGING, EW, EB>;
+    constexpr uint32_t EPI_WARPS = EW, EPI_BUFS = EB;
     constexpr uint32_t STAGES = C_::STAGES;     // allocated; p.stages of them are cycled through
     const uint32_t nstages = p.stages;
 
@@ -587,13 +609,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         // ------------------------------ epilogue ------------------------------
+        constexpr uint32_t W = C_::EPI_W;               // columns per chunk
+        constexpr uint32_t CHUNKS = BN / W;
         const uint32_t q = warp & 3;                    // TMEM lane quadrant this warp may read
-        const uint32_t ew = warp - 2;                   // staging buffer owner index
+        const uint32_t ew = warp - 2;                   // 0 .. EW-1
+        const uint32_t half = ew >> 2;                  // with 8 warps: which of the alternating chunks
+        constexpr uint32_t CSTEP = EW / 4;
         const uint32_t my_epi = epi_base + ew * EPI_BUFS * EPI_BUF_BYTES;
         uint8_t *my_epi_gen = smem_gen + (my_epi - smem_base);
         uint32_t acc = 0, acc_phase = 0;
         uint32_t buf = 0;
         bool ok = true;
+        const bool fused = p.splits > 1 && p.Cout != nullptr;
         for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
             const WorkUnit w = decode_unit(p, u);
             ok = mbar_wait_patient(tmem_full_bar(acc), acc_phase, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
@@ -603,17 +630,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t col0 = w.n_blk * BN;
             const uint32_t zc = p.splits > 1 ? w.split : w.batch;
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+            const uint32_t row = row0 + lane;
+            float *cbase = p.C + (uint64_t)zc * p.c_stride;
+            const bool accum = p.accumulate && !fused;      // K-slices are plain stores; only the final sum accumulates
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN / EPI_COLS; ++c) {
-                const uint32_t col = col0 + c * EPI_COLS;
+            for (uint32_t c = half; c < CHUNKS; c += CSTEP) {
+                const uint32_t col = col0 + c * W;
                 if (col >= p.N || row0 >= p.M) break;   // nothing of this warp's slab is inside C
                 if (p.debug & 4u) break;
                 uint32_t v[32];
-                tmem_ld32(taddr + c * EPI_COLS, v);
+                if constexpr (W == 32) tmem_ld32(taddr + c * W, v); else tmem_ld16(taddr + c * W, v);
                 tmem_ld_wait();
                 if (p.debug & 2u) continue;
                 if (STAGING && p.epilogue_tma) {
-                    // the store issued two chunks ago must have finished reading this buffer
+                    // the store issued EPI_BUFS chunks ago must have finished reading this buffer
                     if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
                     __syncwarp();
                     uint8_t *dst = my_epi_gen + buf * EPI_BUF_BYTES + lane * 128;
@@ -625,29 +655,40 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (p.accumulate)
+                        if (accum)
                             tma_reduce_add_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc);
                         else
                             tma_store_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc);
                         tma_store_commit();
                     }
-                    buf ^= 1;
-                } else {
-                    const uint32_t row = row0 + lane;
+                    if (++buf == EPI_BUFS) buf = 0;
+                } else if (p.c_trans) {
+                    // swapped operands: this lane's row is a COLUMN of C, so for each j the warp writes
+                    // 32 consecutive floats
                     if (row < p.M) {
-                        float *crow = p.C + (uint64_t)zc * p.c_stride + (uint64_t)row * p.ldc + col;
-                        if (p.accumulate) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 32; ++j)
+                        for (uint32_t j = 0; j < W; ++j) {
+                            if (col + j < p.N) {
+                                float *d = cbase + (uint64_t)(col + j) * p.ldc + row;
+                                *d = accum ? *d + __uint_as_float(v[j]) : __uint_as_float(v[j]);
+                            }
+                        }
+                    }
+                } else {
+                    if (row < p.M) {
+                        float *crow = cbase + (uint64_t)row * p.ldc + col;
+                        if (accum) {
+#pragma unroll
+                            for (uint32_t j = 0; j < W; ++j)
                                 if (col + j < p.N) crow[j] += __uint_as_float(v[j]);
-                        } else if (p.c_vec4 && col + EPI_COLS <= p.N) {
+                        } else if (p.c_vec4 && col + W <= p.N) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 8; ++j)
+                            for (uint32_t j = 0; j < W / 4; ++j)
                                 *reinterpret_cast<uint4 *>(crow + 4 * j) =
                                     make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                         } else {
 #pragma unroll
-                            for (uint32_t j = 0; j < 32; ++j)
+                            for (uint32_t j = 0; j < W; ++j)
                                 if (col + j < p.N) crow[j] = __uint_as_float(v[j]);
                         }
                     }
@@ -665,6 +706,67 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+
+            if (fused && row0 < p.M && !(p.debug & 6u)) {
+                // Fused split-K reduction.  This warp's slab of slice `split` is in global memory
+                // (plain stores); publish it and count.  The warp that finds all other slices already
+                // counted sums the slab over the slices in slice order — the result does not depend on
+                // which warp arrives last — writes it to Cout and re-arms the counter.
+                const uint32_t slab = (((w.m_blk * p.n_tiles + w.n_blk) * CG + cta_rank) * EPI_WARPS) + ew;
+                __threadfence();
+                __syncwarp();
+                uint32_t old = 0;
+                if (lane == 0) old = atomicAdd(p.counters + slab, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == p.splits - 1) {
+                    __threadfence();
+                    for (uint32_t c = half; c < CHUNKS; c += CSTEP) {
+                        const uint32_t col = col0 + c * W;
+                        if (col >= p.N) break;
+                        // Each lane owns up to 32 elements of the chunk; all loads of one slice are
+                        // issued before any is used, slices are added in slice order.
+                        //   transposed tile: lane = tile row (consecutive addresses), e = column
+                        //   plain tile:      lane = column of the chunk,              e = row of the slab
+                        constexpr uint32_t E = 32;
+                        float sum[E];
+                        uint64_t stride_e, base;
+                        uint32_t n_e;
+                        bool lane_ok;
+                        if (p.c_trans) {
+                            n_e = (p.N - col) < W ? (p.N - col) : W;
+                            lane_ok = row < p.M;
+                            base = (uint64_t)col * p.ldc + row;
+                            stride_e = p.ldc;
+                        } else {
+                            n_e = (p.M - row0) < 32u ? (p.M - row0) : 32u;
+                            lane_ok = lane < W && col + lane < p.N;
+                            base = (uint64_t)row0 * p.ldc + col + lane;
+                            stride_e = p.ldc;
+                        }
+                        if (lane_ok) {
+#pragma unroll
+                            for (uint32_t e = 0; e < E; ++e) sum[e] = e < n_e ? __ldcg(p.C + base + e * stride_e) : 0.0f;
+                            for (uint32_t sidx = 1; sidx < p.splits; ++sidx) {
+                                const float *sl = p.C + (uint64_t)sidx * p.c_stride + base;
+#pragma unroll
+                                for (uint32_t e = 0; e < E; ++e)
+                                    if (e < n_e) sum[e] += __ldcg(sl + e * stride_e);
+                            }
+                            const uint64_t obase = p.c_trans ? (uint64_t)col * p.ldc_out + row
+                                                             : (uint64_t)row0 * p.ldc_out + col + lane;
+#pragma unroll
+                            for (uint32_t e = 0; e < E; ++e) {
+                                if (e < n_e) {
+                                    float *d = p.Cout + obase + e * p.ldc_out;
+                                    *d = p.accumulate ? *d + sum[e] : sum[e];
+                                }
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) p.counters[slab] = 0;
+                }
+            }
         }
         if (lane == 0) tma_store_wait_all();
     }
@@ -685,27 +787,39 @@ struct TcConfig {
     const char *name;
     int cg, bn, sub;
     bool staging;
-    uint32_t smem, stages;
+    int ew;
+    bool auto_ok;          // may be picked by the cost model (others only by hand or by a dedicated route)
+    uint32_t smem, stages, threads;
     const void *fn;
 };
 
-#define PG_TC_CFG(NAME, CG_, BN_, SUB_, STG_) \
-    {NAME, CG_, BN_, SUB_, STG_, Cfg<CG_, BN_, SUB_, STG_>::SMEM_BYTES, Cfg<CG_, BN_, SUB_, STG_>::STAGES, \
-     (const void *)tc_gemm_kernel<CG_, BN_, SUB_, STG_>}
+#define PG_TC_CFG(NAME, CG_, BN_, SUB_, STG_, EW_, EB_, AUTO_) \
+    {NAME, CG_, BN_, SUB_, STG_, EW_, AUTO_, Cfg<CG_, BN_, SUB_, STG_, EW_, EB_>::SMEM_BYTES, \
+     Cfg<CG_, BN_, SUB_, STG_, EW_, EB_>::STAGES, Cfg<CG_, BN_, SUB_, STG_, EW_, EB_>::THREADS, \
+     (const void *)tc_gemm_kernel<CG_, BN_, SUB_, STG_, EW_, EB_>}
 static const TcConfig g_cfgs[] = {
-    PG_TC_CFG("1cta_128x256", 1, 256, 1, true),
-    PG_TC_CFG("1cta_128x128", 1, 128, 1, true),
-    PG_TC_CFG("1cta_128x64", 1, 64, 1, true),
-    PG_TC_CFG("2cta_256x256", 2, 256, 1, true),
-    PG_TC_CFG("2cta_256x128", 2, 128, 1, true),
-    PG_TC_CFG("2cta_256x256_k128", 2, 256, 2, true),
-    PG_TC_CFG("1cta_128x256_k128", 1, 256, 2, true),
-    PG_TC_CFG("2cta_256x256_s7", 2, 256, 1, false),
+    PG_TC_CFG("1cta_128x256", 1, 256, 1, true, 4, 2, true),
+    PG_TC_CFG("1cta_128x128", 1, 128, 1, true, 4, 2, true),
+    PG_TC_CFG("1cta_128x64", 1, 64, 1, true, 4, 2, true),
+    PG_TC_CFG("2cta_256x256", 2, 256, 1, true, 4, 2, true),
+    PG_TC_CFG("2cta_256x128", 2, 128, 1, true, 4, 2, true),
+    PG_TC_CFG("2cta_256x256_k128", 2, 256, 2, true, 4, 2, false),
+    PG_TC_CFG("1cta_128x256_k128", 1, 256, 2, true, 4, 2, false),
+    PG_TC_CFG("2cta_256x256_s7", 2, 256, 1, false, 4, 2, false),
+    PG_TC_CFG("2cta_256x256_e8", 2, 256, 1, true, 8, 2, false),   // store-bound shapes (small K): 8 epilogue warps
+    PG_TC_CFG("1cta_128x16_t", 1, 16, 1, false, 4, 2, false),     // swapped operands for M <= 16
+    PG_TC_CFG("1cta_128x32_t", 1, 32, 1, false, 4, 2, false),     // swapped operands for M <= 32
 };
 constexpr int NUM_CFGS = sizeof(g_cfgs) / sizeof(g_cfgs[0]);
 
 int tc_num_configs() { return NUM_CFGS; }
 const char *tc_config_name(int cfg) { return (cfg >= 0 && cfg < NUM_CFGS) ? g_cfgs[cfg].name : "?"; }
+
+int tc_config_index(const char *name) {
+    for (int i = 0; i < NUM_CFGS; ++i)
+        if (!strcmp(g_cfgs[i].name, name)) return i;
+    return -1;
+}
 
 static bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
 
@@ -794,7 +908,7 @@ static const CfgRuntime &prepare_cfg(int cfg) {
     } else {
         cudaLaunchConfig_t lc = {};
         lc.gridDim = dim3((unsigned)(sms / 2 * 2), 1, 1);
-        lc.blockDim = dim3(NUM_THREADS, 1, 1);
+        lc.blockDim = dim3(c.threads, 1, 1);
         lc.dynamicSmemBytes = c.smem;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
@@ -827,7 +941,7 @@ static int choose_cfg(const TcGemm &g) {
     double best_cost = 1e300;
     for (int i = 0; i < NUM_CFGS; ++i) {
         const TcConfig &c = g_cfgs[i];
-        if (c.sub != 1 || !c.staging) continue;          // experimental variants are chosen by hand only
+        if (!c.auto_ok) continue;
         const CfgRuntime &rt = prepare_cfg(i);
         if (!rt.usable) continue;
         const uint64_t tiles = (uint64_t)g.batch * cdiv(g.M, BM_CTA * c.cg) * cdiv(g.N, c.bn) * (g.splits ? g.splits : 1);
@@ -851,6 +965,10 @@ int tc_gemm_launch(const TcGemm &g) {
     const CfgRuntime &rt = prepare_cfg(cfg);
     if (!rt.usable) return ST_GEMM;
 
+    if (g.B.mn_major && c.bn / c.cg < 64) {
+        set_error("tc_gemm: tile %s cannot take an MN-major B operand", c.name);
+        return ST_UNSUPPORTED;
+    }
     const uint32_t splits = g.splits ? g.splits : 1;
     TcParams p = {};
     p.M = g.M; p.N = g.N; p.K = g.K;
@@ -886,6 +1004,16 @@ int tc_gemm_launch(const TcGemm &g) {
         p.group_m = best;
     }
     p.C = g.C; p.ldc = g.ldc; p.c_stride = g.c_stride;
+    p.c_trans = g.c_trans ? 1u : 0u;
+    p.Cout = (splits > 1) ? g.Cout : nullptr; p.ldc_out = g.ldc_out; p.counters = g.counters;
+    if (p.Cout) {
+        const uint64_t slabs = (uint64_t)p.m_tiles * p.n_tiles * c.cg * c.ew;
+        if (!g.counters || slabs > g.num_counters) {
+            set_error("tc_gemm: %llu slab counters needed for the fused split-K reduction, %u available",
+                      (unsigned long long)slabs, g.num_counters);
+            return ST_UNSUPPORTED;
+        }
+    }
     p.accumulate = g.accumulate ? 1u : 0u;
     p.stages = (g.stages >= 2 && (uint32_t)g.stages < c.stages) ? (uint32_t)g.stages : c.stages;
     p.debug = (uint32_t)g.debug;
@@ -898,7 +1026,7 @@ int tc_gemm_launch(const TcGemm &g) {
     // it wrote up to the next multiple of four columns), so it is used only when N is one.
     const bool c_tma_ok = c_vec_ok && (g.N % 4 == 0);
     p.epilogue_tma = (g.force_epilogue >= 0) ? (uint32_t)(g.force_epilogue && c_tma_ok) : (c_tma_ok ? 1u : 0u);
-    if (!c.staging) p.epilogue_tma = 0;
+    if (!c.staging || p.c_trans || p.Cout) p.epilogue_tma = 0;   // K-slices of a fused reduction are plain stores
     p.c_vec4 = c_vec_ok ? 1u : 0u;
 
     CUtensorMap ma, mb, mc;
@@ -919,7 +1047,7 @@ int tc_gemm_launch(const TcGemm &g) {
 
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(clusters * c.cg, 1, 1);
-    lc.blockDim = dim3(NUM_THREADS, 1, 1);
+    lc.blockDim = dim3(c.threads, 1, 1);
     lc.dynamicSmemBytes = c.smem;
     lc.stream = g.stream;
     cudaLaunchAttribute at[1];
@@ -937,7 +1065,8 @@ int tc_gemm_launch(const TcGemm &g) {
         return ST_GEMM;
     }
     note_launch();
-    set_last_path("tc:%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "");
+    set_last_path("tc:%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
+                  p.Cout ? ":fused" : "");
     return ST_OK;
 }
 

@@ -46,6 +46,12 @@ struct TcGemm {
     float *C;
     uint64_t ldc, c_stride;    // elements; c_stride between batch elements (or split-K slices)
     int accumulate;            // C += A*B instead of C = A*B
+    int c_trans;               // store the tile transposed: element (row, col) -> C[col*ldc + row]
+    // splits > 1 with Cout set: C holds the K-slices and the kernel itself sums them into Cout
+    float *Cout;
+    uint64_t ldc_out;
+    uint32_t *counters;        // zeroed device words, one per (tile, CTA, epilogue warp)
+    uint32_t num_counters;
     uint32_t splits;           // >1: split-K, slice s goes to C + s*c_stride (batch must be 1)
     int force_cfg;             // -1 = choose; else index into the config table
     int force_epilogue;        // -1 = choose; 0 = direct stores; 1 = TMA stores
@@ -63,6 +69,7 @@ int tc_gemm_launch(const TcGemm &g);
 bool tc_gemm_supported(const TcGemm &g);
 int tc_num_configs();
 const char *tc_config_name(int cfg);
+int tc_config_index(const char *name);   // -1 if unknown
 
 // Generic FFMA fallback: any dtype (per operand), any strides.
 struct SimtGemm {

@@ -93,7 +93,7 @@ def test_gemm_ex_vs_oracle(pg, oracle, dt, shape, path):
         assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("cfg", range(8))
+@pytest.mark.parametrize("cfg", range(9))
 @pytest.mark.parametrize("epi", [0, 1])
 def test_every_tile_config(pg, oracle, cfg, epi):
     a, b = wl.config2(520, 776, 328)
@@ -109,6 +109,39 @@ def test_config3b_skinny_split_k(pg, oracle):
     got = gemm_dev(pg, wl.F16, a, b)
     assert "splitk" in pg.last_path()
     assert wl.relerr(got, oracle.gemm_ex(wl.F16, a, b)) <= wl.tolerance(wl.F16, 4096)
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 17, 32])
+@pytest.mark.parametrize("dt", [wl.BF16, wl.F16])
+def test_skinny_m_swapped_operands(pg, oracle, m, dt):
+    """M <= 32 goes through C^T = B^T A^T with narrow tiles; with and without K splits, ragged N."""
+    for n, k in ((4096, 1024), (1000, 520), (256, 64)):
+        a, b = (wl.config2(m, n, k) if dt == wl.BF16 else wl.config3(m, n, k))
+        want = oracle.gemm_ex(dt, a, b)
+        got = gemm_dev(pg, dt, a, b)
+        if m * n * k > 64 ** 3:                     # tinier products go to the FFMA kernel
+            assert "_t" in pg.last_path(), pg.last_path()
+        assert wl.relerr(got, want) <= wl.tolerance(dt, k), (m, n, k, pg.last_path())
+        pg.set_option("swap_skinny", 0)
+        plain = gemm_dev(pg, dt, a, b)
+        pg.set_option("swap_skinny", 1)
+        assert wl.relerr(got, plain) <= 1e-6
+
+
+def test_fused_split_k_equals_two_kernel_form(pg, oracle):
+    """The slices are summed in slice order either way, so the two forms agree bit for bit."""
+    a, b = wl.config2(200, 520, 2056)
+    outs = {}
+    for fused in (1, 0):
+        pg.set_option("fused_splitk", fused); pg.set_option("k_splits", 5); pg.set_option("path", 1)
+        outs[fused] = gemm_dev(pg, wl.BF16, a, b, lda=2056, ldb=520, ldc=524)
+        assert ("fused" in pg.last_path()) == bool(fused), pg.last_path()
+    assert np.array_equal(outs[0], outs[1])
+    assert wl.relerr(outs[1], oracle.gemm_ex(wl.BF16, a, b)) <= wl.tolerance(wl.BF16, 2056)
+    # twice more: the arrival counters re-arm themselves
+    for _ in range(2):
+        pg.set_option("fused_splitk", 1); pg.set_option("k_splits", 5); pg.set_option("path", 1)
+        assert np.array_equal(gemm_dev(pg, wl.BF16, a, b, lda=2056, ldb=520, ldc=524), outs[1])
 
 
 SIZES = [1, 2, 3, 7, 8, 9, 16, 17, 127, 128, 129, 255, 256, 257]
