@@ -143,6 +143,11 @@ PG_B200_API const char *pg_b200_last_error(void);
 PG_B200_API int pg_b200_set_option(const char *name, int value);
 PG_B200_API int pg_b200_num_tile_configs(void);
 PG_B200_API const char *pg_b200_tile_config_name(int index);
+/* Failure-detection self-test (no counterpart in picograd, whose launch failure is an assert,
+ * cuda.c:173): launches a kernel that waits on a barrier nothing completes, with the bounded wait the
+ * GEMM kernels use and a limit of `limit_ms` (<= 1000).  The kernel returns normally after the limit
+ * and the NEXT pg_b200_sync() reports PG_ERR_GEMM; the device stays usable. */
+PG_B200_API int pg_b200_selftest_wait_timeout(unsigned limit_ms);
 /* Diagnostics of the timing experiments (option "debug" bit 32): copies per-CTA cycle counters
  * of the last tensor-core launch, 16 per CTA, to `out`. */
 PG_B200_API int pg_b200_debug_counters(uint64_t *out, size_t count);

@@ -722,6 +722,11 @@ int pg_b200_debug_counters(uint64_t *out, size_t count) {
     return cudaMemcpy(out, g.prof, count * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? ST_OK : ST_COPY;
 }
 
+int pg_b200_selftest_wait_timeout(unsigned limit_ms) {
+    if (!ready()) return g.init_status;
+    return wait_timeout_selftest_launch(g.dev_status, limit_ms, g.stream);
+}
+
 const char *pg_b200_last_error(void) { return g.err; }
 const char *pg_b200_last_path(void) { return g.last_path; }
 uint64_t pg_b200_launch_count(void) { return g.launches; }

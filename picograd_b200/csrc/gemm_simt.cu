@@ -9,7 +9,7 @@
 // bit, not merely within tolerance.  No TF32, no reordering.
 //
 // Tiling: 256 threads, a TILE x TILE block of C per CTA, (TILE/16)^2 outputs per
-// thread, K in slabs of 16 staged through shared memory.  Operands are read
+// thread, K in slabs of 16 staged through shared memory with register prefetch.  Operands are read
 // through generic (row, column, batch) element strides, so transposed views and
 // mixed dtypes need no separate kernel.
 
@@ -37,20 +37,22 @@ __device__ __forceinline__ float load_as_f32(const void *base, long long idx, in
 
 constexpr int SK = 16;
 
+// The next K slab is fetched into registers while the current one is multiplied out of shared
+// memory, so the global-load latency overlaps the FFMA work; each thread owns a T x T block of
+// contiguous rows and columns and reads its operands from shared memory as 16-byte vectors.
 template <int TILE>
 __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     constexpr int T = TILE / 16;              // outputs per thread per dimension
-    __shared__ float As[SK][TILE + 1];
-    __shared__ float Bs[SK][TILE + 1];
+    constexpr int PER = TILE * SK / 256;      // elements of each operand a thread stages per slab
+    constexpr int LD = TILE + 4;              // row pitch: keeps 16-byte alignment, spreads banks
+    __shared__ __align__(16) float As[SK][LD];
+    __shared__ __align__(16) float Bs[SK][LD];
 
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const uint32_t bz = blockIdx.z;
     const long long m0 = (long long)blockIdx.y * TILE, n0 = (long long)blockIdx.x * TILE;
-    const char *Ab = reinterpret_cast<const char *>(p.A);
-    const char *Bb = reinterpret_cast<const char *>(p.B);
     const long long a_off = (long long)bz * p.a_bs, b_off = (long long)bz * p.b_bs;
-    (void)Ab; (void)Bb;
 
     float acc[T][T];
 #pragma unroll
@@ -58,51 +60,52 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
 #pragma unroll
         for (int j = 0; j < T; ++j) acc[i][j] = 0.0f;
 
-    // walk the contiguous dimension with consecutive threads
+    // walk the contiguous dimension of each operand with consecutive threads
     const bool a_k_contig = (p.a_cs == 1);
     const bool b_n_contig = (p.b_cs == 1);
-
-    for (uint32_t k0 = 0; k0 < p.K; k0 += SK) {
-        for (int idx = tid; idx < TILE * SK; idx += 256) {
-            int kk, mm;
-            if (a_k_contig) { kk = idx % SK; mm = idx / SK; } else { mm = idx % TILE; kk = idx / TILE; }
-            const long long gm = m0 + mm, gk = (long long)k0 + kk;
-            float v = 0.0f;
-            if (gm < p.M && gk < p.K) v = load_as_f32(p.A, a_off + gm * p.a_rs + gk * p.a_cs, p.dtype_a);
-            As[kk][mm] = v;
+    int a_kk[PER], a_mm[PER], b_kk[PER], b_nn[PER];
+#pragma unroll
+    for (int r = 0; r < PER; ++r) {
+        const int idx = tid + r * 256;
+        if (a_k_contig) { a_kk[r] = idx % SK; a_mm[r] = idx / SK; } else { a_mm[r] = idx % TILE; a_kk[r] = idx / TILE; }
+        if (b_n_contig) { b_nn[r] = idx % TILE; b_kk[r] = idx / TILE; } else { b_kk[r] = idx % SK; b_nn[r] = idx / SK; }
+    }
+    float ra[PER], rb[PER];
+    auto fetch = [&](uint32_t k0) {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            const long long gm = m0 + a_mm[r], gka = (long long)k0 + a_kk[r];
+            ra[r] = (gm < p.M && gka < p.K) ? load_as_f32(p.A, a_off + gm * p.a_rs + gka * p.a_cs, p.dtype_a) : 0.0f;
+            const long long gn = n0 + b_nn[r], gkb = (long long)k0 + b_kk[r];
+            rb[r] = (gn < p.N && gkb < p.K) ? load_as_f32(p.B, b_off + gkb * p.b_rs + gn * p.b_cs, p.dtype_b) : 0.0f;
         }
-        for (int idx = tid; idx < TILE * SK; idx += 256) {
-            int kk, nn;
-            if (b_n_contig) { nn = idx % TILE; kk = idx / TILE; } else { kk = idx % SK; nn = idx / SK; }
-            const long long gn = n0 + nn, gk = (long long)k0 + kk;
-            float v = 0.0f;
-            if (gn < p.N && gk < p.K) v = load_as_f32(p.B, b_off + gk * p.b_rs + gn * p.b_cs, p.dtype_b);
-            Bs[kk][nn] = v;
+    };
+
+    if (p.K) fetch(0);
+    for (uint32_t k0 = 0; k0 < p.K; k0 += SK) {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            As[a_kk[r]][a_mm[r]] = ra[r];
+            Bs[b_kk[r]][b_nn[r]] = rb[r];
         }
         __syncthreads();
+        if (k0 + SK < p.K) fetch(k0 + SK);
+        // stop at the true K so that the chain of each element is exactly its K fused multiply-adds
         const int kmax = (p.K - k0) < (uint32_t)SK ? (int)(p.K - k0) : SK;
-        if (kmax == SK) {
+#pragma unroll 4
+        for (int kk = 0; kk < kmax; ++kk) {
+            float a[T], b[T];
 #pragma unroll
-            for (int kk = 0; kk < SK; ++kk) {
-                float a[T], b[T];
-#pragma unroll
-                for (int i = 0; i < T; ++i) a[i] = As[kk][ty + 16 * i];
-#pragma unroll
-                for (int j = 0; j < T; ++j) b[j] = Bs[kk][tx + 16 * j];
-#pragma unroll
-                for (int i = 0; i < T; ++i)
-#pragma unroll
-                    for (int j = 0; j < T; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+            for (int i = 0; i < T; i += 4) {
+                const float4 va = *reinterpret_cast<const float4 *>(&As[kk][ty * T + i]);
+                a[i] = va.x; a[i + 1] = va.y; a[i + 2] = va.z; a[i + 3] = va.w;
+                const float4 vb = *reinterpret_cast<const float4 *>(&Bs[kk][tx * T + i]);
+                b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
             }
-        } else {
-            // K tail: stop at the true K so that no "+ 0*0" step is added to the chain
-            for (int kk = 0; kk < kmax; ++kk) {
 #pragma unroll
-                for (int i = 0; i < T; ++i)
+            for (int i = 0; i < T; ++i)
 #pragma unroll
-                    for (int j = 0; j < T; ++j)
-                        acc[i][j] = __fmaf_rn(As[kk][ty + 16 * i], Bs[kk][tx + 16 * j], acc[i][j]);
-            }
+                for (int j = 0; j < T; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
         }
         __syncthreads();
     }
@@ -110,11 +113,11 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     float *Cb = p.C + (long long)bz * p.c_bs;
 #pragma unroll
     for (int i = 0; i < T; ++i) {
-        const long long gm = m0 + ty + 16 * i;
+        const long long gm = m0 + ty * T + i;
         if (gm >= p.M) continue;
 #pragma unroll
         for (int j = 0; j < T; ++j) {
-            const long long gn = n0 + tx + 16 * j;
+            const long long gn = n0 + tx * T + j;
             if (gn >= p.N) continue;
             float *dst = Cb + gm * p.ldc + gn;
             *dst = p.accumulate ? (*dst + acc[i][j]) : acc[i][j];

@@ -781,6 +781,35 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: a barrier that nothing will ever complete.  The warp polls it with
+// the same spin primitive as the GEMM roles, gives up after `limit_ns`, records DEV_ERR_SELFTEST in
+// the status word and returns normally — no trap, no fault, the context stays usable.
+// ---------------------------------------------------------------------------------------------
+__global__ void wait_timeout_selftest_kernel(uint32_t *status, unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        const uint32_t done = mbar_spin(b, 0, 64);
+        if (__all_sync(0xffffffffu, done)) return;          // cannot happen: nobody arrives
+        if (globaltimer_ns() - t0 > limit_ns) break;
+    }
+    if (threadIdx.x == 0) atomicOr(status, DEV_ERR_SELFTEST);
+}
+
+int wait_timeout_selftest_launch(uint32_t *status, unsigned limit_ms, cudaStream_t stream) {
+    if (limit_ms > 1000) limit_ms = 1000;                   // a second at most
+    wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(status, (unsigned long long)limit_ms * 1000000ull);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
 struct TcConfig {

@@ -22,6 +22,7 @@ enum : uint32_t {
     DEV_ERR_WAIT_FULL = 1u << 1,       // MMA issuer: TMA bytes never landed
     DEV_ERR_WAIT_TMEM_EMPTY = 1u << 2, // MMA issuer: epilogue never drained TMEM
     DEV_ERR_WAIT_TMEM_FULL = 1u << 3,  // epilogue: accumulator never completed
+    DEV_ERR_SELFTEST = 1u << 8,        // the wait-timeout self-test kernel ran out of time, as it must
 };
 
 // One operand of the tensor-core GEMM as it lies in HBM.
@@ -67,6 +68,7 @@ struct TcGemm {
 int tc_gemm_launch(const TcGemm &g);
 // true if operands satisfy the TMA rules (16-byte aligned bases and strides)
 bool tc_gemm_supported(const TcGemm &g);
+int wait_timeout_selftest_launch(uint32_t *status, unsigned limit_ms, cudaStream_t stream);
 int tc_num_configs();
 const char *tc_config_name(int cfg);
 int tc_config_index(const char *name);   // -1 if unknown

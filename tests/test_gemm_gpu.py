@@ -192,6 +192,20 @@ def test_empty_and_k0(pg):
     assert torch.all(c == 0.0)
 
 
+def test_bounded_wait_reports_and_leaves_the_device_usable(pg, oracle):
+    """Failure detection without a fault: a kernel waits (bounded, 20 ms) on a barrier nothing sets,
+    returns normally with a status bit, pg_dev_sync raises PG_ERR_GEMM once, and the next GEMM is fine."""
+    from picograd_b200._lib import lib
+    pg.pg_dev_sync()
+    assert lib.pg_b200_selftest_wait_timeout(20) == 0
+    with pytest.raises(pg.PgError) as e:
+        pg.pg_dev_sync()
+    assert e.value.status == -5 and "gave up waiting" in str(e.value)
+    pg.pg_dev_sync()                                        # the status word was cleared
+    a, b = wl.config2(256, 256, 256)
+    assert wl.relerr(gemm_dev(pg, wl.BF16, a, b), oracle.gemm_ex(wl.BF16, a, b)) <= wl.tolerance(wl.BF16, 256)
+
+
 def test_host_pointer_gemm_ex(pg, oracle):
     """pg_gemm_ex as ops/matmul.c:264-271 calls it: host buffers in, host buffer out."""
     a, b = wl.config2(300, 200, 264)
