@@ -41,6 +41,8 @@ struct State {
     int opt_host_pipeline = 1;   // host-pointer pg_gemm_ex: overlap copies and GEMMs block by block
     int opt_fused_splitk = 1;    // split-K slices summed by the GEMM kernel itself (else a second kernel)
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
+    int opt_l2_hints = 0;    // see TcParams::l2_hints
+    int opt_group_m = 0;     // 0: choose
     int opt_stages = 0;      // 0: all smem stages of the tile configuration
     int opt_debug = 0;       // timing experiments only (see TcGemm::debug)
     char err[512] = "";
@@ -228,7 +230,7 @@ static int run_tc(const Problem &p) {
     t.accumulate = p.accumulate;
     t.splits = 1;
     t.force_cfg = g.opt_cfg; t.force_epilogue = g.opt_epilogue;
-    t.stages = g.opt_stages; t.debug = g.opt_debug;
+    t.stages = g.opt_stages; t.debug = g.opt_debug; t.l2_hints = g.opt_l2_hints; t.group_m = g.opt_group_m;
     t.stream = g.stream; t.dev_status = g.dev_status; t.prof = g.prof;
 
     // a batch-shared operand (stride 0) with batch > 1 cannot be a TMA dimension of stride 0
@@ -742,6 +744,8 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "f32_parts")) { if (value != 2 && value != 3) return ST_UNSUPPORTED; g.opt_f32_parts = value; return ST_OK; }
     if (!strcmp(name, "f32_tensor_cores")) { g.opt_f32_tc = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "stages")) { g.opt_stages = value; return ST_OK; }
+    if (!strcmp(name, "l2_hints")) { g.opt_l2_hints = value; return ST_OK; }
+    if (!strcmp(name, "group_m")) { g.opt_group_m = value; return ST_OK; }
     if (!strcmp(name, "host_pipeline")) { g.opt_host_pipeline = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "fused_splitk")) { g.opt_fused_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "swap_skinny")) { g.opt_swap_skinny = value ? 1 : 0; return ST_OK; }

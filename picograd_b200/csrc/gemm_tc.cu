@@ -28,6 +28,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#ifndef PG_SUSPEND_HINT_NS
+#define PG_SUSPEND_HINT_NS 1000
+#endif
+
 namespace pgb {
 
 // ---------------------------------------------------------------------------------------------
@@ -85,6 +89,7 @@ struct TcParams {
     uint32_t stages;              // smem stages in use (<= the configuration's maximum)
     uint32_t debug;               // timing experiments only (results are garbage): 1 = no TMA loads, 2 = no C
                                   // stores, 4 = no TMEM reads, 8 = alternate accumulators, 16 = no MMAs
+    uint32_t l2_hints;            // 2 bits each for A loads, B loads, C stores: 0 normal, 1 evict_first, 2 evict_last
     uint32_t c_trans;             // element (row, col) of the tile goes to C[col*ldc + row] (swapped operands)
     float *C;                     // splits > 1: the K-slices [split][rows][ldc]; else the result
     uint64_t ldc, c_stride;
@@ -136,6 +141,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Upper bound, in nanoseconds, that the hardware may keep a waiting thread suspended inside one
+// try_wait before it returns "not yet" (a hint; the wait still ends as soon as the phase completes).
+constexpr uint32_t g_suspend_hint_ns = PG_SUSPEND_HINT_NS;
+
 // Spins on try_wait inside one asm block (so that the compiler sees straight-line, warp-uniform
 // code around it) for at most `tries` attempts; returns 1 if the phase completed.
 __device__ __forceinline__ uint32_t mbar_spin(uint32_t bar, uint32_t parity, uint32_t tries) {
@@ -144,7 +153,7 @@ __device__ __forceinline__ uint32_t mbar_spin(uint32_t bar, uint32_t parity, uin
         "{\n\t.reg .pred p;\n\t.reg .b32 n;\n\t"
         "mov.b32 n, %3;\n"
         "PG_WAIT_LOOP:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %4;\n\t"
         "@p bra PG_WAIT_DONE;\n\t"
         "sub.u32 n, n, 1;\n\t"
         "setp.ne.u32 p, n, 0;\n\t"
@@ -153,7 +162,7 @@ __device__ __forceinline__ uint32_t mbar_spin(uint32_t bar, uint32_t parity, uin
         "PG_WAIT_DONE:\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(tries)
+        : "r"(bar), "r"(parity), "r"(tries), "r"(g_suspend_hint_ns)
         : "memory");
     return done;
 }
@@ -286,23 +295,35 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     }
 }
 
+// L2 eviction-priority policies for the bulk copies
+__device__ __forceinline__ uint64_t l2_policy(int kind) {   // 0 normal, 1 evict_first, 2 evict_last
+    uint64_t pol;
+    if (kind == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    else if (kind == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
 // TMA tile load global -> shared, completion counted on `bar` (for CG == 2 the barrier of the
 // leader CTA, a shared::cluster address).
 template <int CG>
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
-                                            int32_t c0, int32_t c1, int32_t c2) {
+                                            int32_t c0, int32_t c1, int32_t c2, uint64_t policy) {
     if constexpr (CG == 1)
         asm volatile(
-            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy) : "memory");
     else
         asm volatile(
-            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy) : "memory");
 }
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1, int32_t c2,
+                                             uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "l"(policy) : "memory");
 }
 // C tile += smem tile, performed by the TMA unit in L2
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
@@ -449,6 +470,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         const bool prof = (p.debug & 32u) != 0;
         long long tp_wait = 0, tp_issue = 0;
+        const uint64_t pol_a = l2_policy((int)(p.l2_hints & 3u)), pol_b = l2_policy((int)((p.l2_hints >> 2) & 3u));
         for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
             const WorkUnit w = decode_unit(p, u);
             const int32_t m0 = (int32_t)(w.m_blk * BM_CTA * CG + cta_rank * BM_CTA);
@@ -479,18 +501,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 const uint32_t sa = sbase + j * C_::SUB_BYTES;
                                 const uint32_t sb = sa + A_TILE_BYTES;
                                 if (!p.a_mn) {
-                                    tma_load_3d<CG>(sa, &map_a, bar, k0, m0, za);
+                                    tma_load_3d<CG>(sa, &map_a, bar, k0, m0, za, pol_a);
                                 } else {
 #pragma unroll
                                     for (uint32_t c = 0; c < BM_CTA / 64; ++c)
-                                        tma_load_3d<CG>(sa + c * (BK * 128), &map_a, bar, m0 + (int32_t)(c * 64), k0, za);
+                                        tma_load_3d<CG>(sa + c * (BK * 128), &map_a, bar, m0 + (int32_t)(c * 64), k0, za, pol_a);
                                 }
                                 if (!p.b_mn) {
-                                    tma_load_3d<CG>(sb, &map_b, bar, k0, n0, zb);
+                                    tma_load_3d<CG>(sb, &map_b, bar, k0, n0, zb, pol_b);
                                 } else {
 #pragma unroll
                                     for (uint32_t c = 0; c < C_::BN_CTA / 64; ++c)
-                                        tma_load_3d<CG>(sb + c * (BK * 128), &map_b, bar, n0 + (int32_t)(c * 64), k0, zb);
+                                        tma_load_3d<CG>(sb + c * (BK * 128), &map_b, bar, n0 + (int32_t)(c * 64), k0, zb, pol_b);
                                 }
                             }
                         }
@@ -621,6 +643,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t buf = 0;
         bool ok = true;
         const bool fused = p.splits > 1 && p.Cout != nullptr;
+        const uint64_t pol_c = l2_policy((int)((p.l2_hints >> 4) & 3u));
         for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
             const WorkUnit w = decode_unit(p, u);
             ok = mbar_wait_patient(tmem_full_bar(acc), acc_phase, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
@@ -658,7 +681,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (accum)
                             tma_reduce_add_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc);
                         else
-                            tma_store_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc);
+                            tma_store_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc, pol_c);
                         tma_store_commit();
                     }
                     if (++buf == EPI_BUFS) buf = 0;
@@ -1046,6 +1069,8 @@ int tc_gemm_launch(const TcGemm &g) {
     p.accumulate = g.accumulate ? 1u : 0u;
     p.stages = (g.stages >= 2 && (uint32_t)g.stages < c.stages) ? (uint32_t)g.stages : c.stages;
     p.debug = (uint32_t)g.debug;
+    p.l2_hints = (uint32_t)g.l2_hints;
+    if (g.group_m > 0) p.group_m = (uint32_t)g.group_m;
     p.prof = g.prof;
     if (!p.prof) p.debug &= ~32u;
     p.status = g.dev_status;

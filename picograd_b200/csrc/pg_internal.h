@@ -57,6 +57,8 @@ struct TcGemm {
     int force_cfg;             // -1 = choose; else index into the config table
     int force_epilogue;        // -1 = choose; 0 = direct stores; 1 = TMA stores
     int stages;                // 0 = all the configuration has; else use this many smem stages
+    int l2_hints;              // L2 eviction priorities of the bulk copies (see TcParams::l2_hints)
+    int group_m;               // 0 = choose; else M tiles per rasterisation group
     int debug;                 // timing experiments: 1 = no TMA loads, 2 = no C stores (results are garbage)
     cudaStream_t stream;
     uint32_t *dev_status;      // device status word
