@@ -124,11 +124,14 @@ def cpu_time_rows(fn, a, b, rows):
 def cpu_baseline(a, b, budget_s=15.0):
     """Times the CPU implementation on a row-slab of the same product sized for ~budget_s."""
     fn, kind, threads = cpu_gemm_fn()
-    probe = 64
-    t = cpu_time_rows(fn, a, b, probe)
-    rows = int(min(M, max(probe, probe * budget_s / max(t, 1e-3))))
-    rows = max(8, rows // 8 * 8)
-    t = cpu_time_rows(fn, a, b, rows)
+    # size the slab in two steps (small slabs run at a lower rate per row: thread start-up, cold caches)
+    rows, t = 64, cpu_time_rows(fn, a, b, 64)
+    for _ in range(2):
+        want = int(min(M, max(rows, rows * budget_s / max(t, 1e-3)))) // 8 * 8
+        if want <= rows * 1.5:
+            break
+        rows = max(8, want)
+        t = cpu_time_rows(fn, a, b, rows)
     tf = 2.0 * rows * N * K / t / 1e12
     return {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind,
             "sample": f"rows [0,{rows}) of the 8192^3 bf16 product ({rows}x8192x8192), one run, {t:.2f} s"}

@@ -401,6 +401,50 @@ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
     return w;
 }
 
+// Fused split-K reduction of one chunk (32 tile rows x `w` tile columns) by one warp: the K-slices
+// are summed in slice order into Cout.  Each lane owns up to 32 elements; the loads of one slice are
+// all issued before any is used.
+//   transposed tile: lane = tile row (consecutive addresses of C), e = tile column
+//   plain tile:      lane = tile column of the chunk,              e = tile row of the slab
+// Kept out of line so that its registers do not weigh on the main loops.
+__device__ __noinline__ void sum_slices_chunk(const TcParams &p, uint32_t row0, uint32_t col, uint32_t w, uint32_t lane) {
+    constexpr uint32_t E = 16;
+    const uint32_t row = row0 + lane;
+    uint32_t n_e;
+    bool lane_ok;
+    uint64_t base, obase;
+    if (p.c_trans) {
+        n_e = (p.N - col) < w ? (p.N - col) : w;
+        lane_ok = row < p.M;
+        base = (uint64_t)col * p.ldc + row;
+        obase = (uint64_t)col * p.ldc_out + row;
+    } else {
+        n_e = (p.M - row0) < 32u ? (p.M - row0) : 32u;
+        lane_ok = lane < w && col + lane < p.N;
+        base = (uint64_t)row0 * p.ldc + col + lane;
+        obase = (uint64_t)row0 * p.ldc_out + col + lane;
+    }
+    if (!lane_ok) return;
+    for (uint32_t e0 = 0; e0 < n_e; e0 += E) {
+        float sum[E];
+#pragma unroll
+        for (uint32_t e = 0; e < E; ++e) sum[e] = e0 + e < n_e ? __ldcg(p.C + base + (uint64_t)(e0 + e) * p.ldc) : 0.0f;
+        for (uint32_t sidx = 1; sidx < p.splits; ++sidx) {
+            const float *sl = p.C + (uint64_t)sidx * p.c_stride + base;
+#pragma unroll
+            for (uint32_t e = 0; e < E; ++e)
+                if (e0 + e < n_e) sum[e] += __ldcg(sl + (uint64_t)(e0 + e) * p.ldc);
+        }
+#pragma unroll
+        for (uint32_t e = 0; e < E; ++e) {
+            if (e0 + e < n_e) {
+                float *d = p.Cout + obase + (uint64_t)(e0 + e) * p.ldc_out;
+                *d = p.accumulate ? *d + sum[e] : sum[e];
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
@@ -746,45 +790,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (uint32_t c = half; c < CHUNKS; c += CSTEP) {
                         const uint32_t col = col0 + c * W;
                         if (col >= p.N) break;
-                        // Each lane owns up to 32 elements of the chunk; all loads of one slice are
-                        // issued before any is used, slices are added in slice order.
-                        //   transposed tile: lane = tile row (consecutive addresses), e = column
-                        //   plain tile:      lane = column of the chunk,              e = row of the slab
-                        constexpr uint32_t E = 32;
-                        float sum[E];
-                        uint64_t stride_e, base;
-                        uint32_t n_e;
-                        bool lane_ok;
-                        if (p.c_trans) {
-                            n_e = (p.N - col) < W ? (p.N - col) : W;
-                            lane_ok = row < p.M;
-                            base = (uint64_t)col * p.ldc + row;
-                            stride_e = p.ldc;
-                        } else {
-                            n_e = (p.M - row0) < 32u ? (p.M - row0) : 32u;
-                            lane_ok = lane < W && col + lane < p.N;
-                            base = (uint64_t)row0 * p.ldc + col + lane;
-                            stride_e = p.ldc;
-                        }
-                        if (lane_ok) {
-#pragma unroll
-                            for (uint32_t e = 0; e < E; ++e) sum[e] = e < n_e ? __ldcg(p.C + base + e * stride_e) : 0.0f;
-                            for (uint32_t sidx = 1; sidx < p.splits; ++sidx) {
-                                const float *sl = p.C + (uint64_t)sidx * p.c_stride + base;
-#pragma unroll
-                                for (uint32_t e = 0; e < E; ++e)
-                                    if (e < n_e) sum[e] += __ldcg(sl + e * stride_e);
-                            }
-                            const uint64_t obase = p.c_trans ? (uint64_t)col * p.ldc_out + row
-                                                             : (uint64_t)row0 * p.ldc_out + col + lane;
-#pragma unroll
-                            for (uint32_t e = 0; e < E; ++e) {
-                                if (e < n_e) {
-                                    float *d = p.Cout + obase + e * p.ldc_out;
-                                    *d = p.accumulate ? *d + sum[e] : sum[e];
-                                }
-                            }
-                        }
+                        sum_slices_chunk(p, row0, col, W, lane);
                     }
                     __syncwarp();
                     if (lane == 0) p.counters[slab] = 0;
