@@ -18,7 +18,6 @@ library compiled into oracle/_ref when that build travelled with the repository,
 restatement in oracle/) on the host cores, each step a bounded row-slab of the same product.
 """
 import argparse
-import ctypes
 import json
 import os
 import statistics

@@ -173,7 +173,6 @@ static int grow(DeviceBuf &b, size_t bytes) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static size_t esize(int dt) { return dt == DT_F32 ? 4 : 2; }
-static bool is16(int dt) { return dt == DT_F16 || dt == DT_BF16; }
 
 // One GEMM, device pointers.
 struct Problem {

@@ -553,7 +553,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 }
                                 if (!p.b_mn) {
                                     tma_load_3d<CG>(sb, &map_b, bar, k0, n0, zb, pol_b);
-                                } else {
+                                } else if constexpr (C_::BN_CTA >= 64) {   // narrower tiles take a K-major B only
 #pragma unroll
                                     for (uint32_t c = 0; c < C_::BN_CTA / 64; ++c)
                                         tma_load_3d<CG>(sb + c * (BK * 128), &map_b, bar, n0 + (int32_t)(c * 64), k0, zb, pol_b);
