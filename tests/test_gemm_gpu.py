@@ -338,6 +338,21 @@ def test_backward_accumulates_into_existing_grads(pg, oracle):
     assert wl.relerr(to_host(gb) - gb0, gb_ref) <= wl.tolerance(wl.BF16, m)
 
 
+def test_backward_f16_operands(pg, oracle):
+    """f16 A and B with the f32 gradient: both sides meet the tensor cores as exact bf16 pieces."""
+    rng = np.random.default_rng(16)
+    m, n, k = 200, 264, 136
+    a = wl.to_f16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = wl.to_f16_bits(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+    g = rng.standard_normal((m, n), dtype=np.float32)
+    ga, gb = pg.pg_matmul_backward(to_dev(a, wl.F16), to_dev(b, wl.F16), to_dev(g, wl.F32))
+    pg.pg_dev_sync()
+    assert pg.last_path().startswith("tc:"), pg.last_path()
+    ga_ref, gb_ref = oracle.matmul_backward(wl.F16, a, b, g)
+    assert wl.relerr(to_host(ga), ga_ref) <= wl.tolerance(wl.F16, n)
+    assert wl.relerr(to_host(gb), gb_ref) <= wl.tolerance(wl.F16, m)
+
+
 def test_backward_batched_and_shared_b(pg, oracle):
     rng = np.random.default_rng(15)
     bt, m, n, k = 3, 72, 136, 64
