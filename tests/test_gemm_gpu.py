@@ -253,6 +253,24 @@ def test_matmul_shape_modes(pg):
     assert pg.pg_bmm(to_dev(f(2, 4, 5), wl.F32), to_dev(f(3, 5, 4), wl.F32)) is None
 
 
+def test_matmul_bf16_batch_broadcast_on_tensor_cores(pg, oracle):
+    """Batched x unbatched (and the reverse) for 16-bit operands: ops/matmul.c:209-225 broadcasting."""
+    rng = np.random.default_rng(17)
+    a3 = wl.to_bf16_bits(rng.standard_normal((3, 136, 72), dtype=np.float32))
+    b2 = wl.to_bf16_bits(rng.standard_normal((72, 264), dtype=np.float32))
+    y = pg.pg_matmul(to_dev(a3, wl.BF16), to_dev(b2, wl.BF16)); pg.pg_dev_sync()
+    assert pg.last_path().startswith("tc:")
+    for i in range(3):
+        assert wl.relerr(to_host(y[i]), oracle.gemm_ex(wl.BF16, a3[i], b2)) <= wl.tolerance(wl.BF16, 72)
+    a2 = wl.to_bf16_bits(rng.standard_normal((136, 72), dtype=np.float32))
+    b4 = wl.to_bf16_bits(rng.standard_normal((2, 2, 72, 264), dtype=np.float32))
+    y = pg.pg_matmul(to_dev(a2, wl.BF16), to_dev(b4, wl.BF16)); pg.pg_dev_sync()
+    assert tuple(y.shape) == (2, 2, 136, 264)
+    for i in range(2):
+        for j in range(2):
+            assert wl.relerr(to_host(y[i, j]), oracle.gemm_ex(wl.BF16, a2, b4[i, j])) <= wl.tolerance(wl.BF16, 72)
+
+
 def test_tensordot(pg):
     """tests/test_ops.c:451-484 shapes: contraction over one and over two axes."""
     rng = np.random.default_rng(13)
