@@ -40,6 +40,8 @@ struct State {
     int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
     int opt_host_pipeline = 1;   // host-pointer pg_gemm_ex: overlap copies and GEMMs block by block
     int opt_fused_splitk = 1;    // split-K slices summed by the GEMM kernel itself (else a second kernel)
+    int opt_stream_k = 0;        // stream-K for a partly filled last wave: correct, but measured 5-20 % slower
+                                 // than the plain schedule on B200 (partial waves already run faster), so off
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
     int opt_l2_hints = 0;    // see TcParams::l2_hints
     int opt_group_m = 0;     // 0: choose
@@ -231,6 +233,8 @@ static int run_tc(const Problem &p) {
     t.force_cfg = g.opt_cfg; t.force_epilogue = g.opt_epilogue;
     t.stages = g.opt_stages; t.debug = g.opt_debug; t.l2_hints = g.opt_l2_hints; t.group_m = g.opt_group_m;
     t.stream = g.stream; t.dev_status = g.dev_status; t.prof = g.prof;
+    t.allow_stream_k = g.opt_stream_k;
+    t.counters = g.counters; t.num_counters = g.num_counters;
 
     // a batch-shared operand (stride 0) with batch > 1 cannot be a TMA dimension of stride 0
     if (p.batch > 1 && (p.stride_a == 0 || p.stride_b == 0)) {
@@ -748,6 +752,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "host_pipeline")) { g.opt_host_pipeline = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "fused_splitk")) { g.opt_fused_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "swap_skinny")) { g.opt_swap_skinny = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);
     return ST_UNSUPPORTED;

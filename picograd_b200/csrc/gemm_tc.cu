@@ -97,6 +97,12 @@ struct TcParams {
     float *Cout;
     uint64_t ldc_out;
     uint32_t *counters;           // one per (tile, CTA of the pair, epilogue warp); zero between launches
+    // Stream-K schedule (when units != nullptr): the host lists the work units; cluster c runs
+    // units[unit_start[c] .. unit_start[c+1]).  A tile whose K range is shared by several clusters
+    // has its partial sums in `ws` (tile-local slices) and is finished by the last arriver.
+    const struct TcUnit *units;
+    const uint32_t *unit_start;
+    float *ws;
     uint32_t *status;
     unsigned long long *prof;     // debug & 32: 16 cycle counters per CTA
 };
@@ -378,7 +384,23 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 struct WorkUnit {
     uint32_t m_blk, n_blk, batch, split;
     uint32_t kb_begin, kb_count;
+    uint32_t nslices, ws_slice0, ws_tile;   // stream-K: slices of this tile, its first slice and index in ws
 };
+
+// One entry of the host-made work list (32 bytes).
+struct TcUnit {
+    uint32_t m_blk, n_blk, batch, kb_begin;
+    uint32_t kb_count, slice, nslices, ws_slice0;
+};
+
+__device__ __forceinline__ WorkUnit load_unit(const TcUnit *u) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(u));
+    const uint4 b = __ldg(reinterpret_cast<const uint4 *>(u) + 1);
+    WorkUnit w;
+    w.m_blk = a.x; w.n_blk = a.y; w.batch = a.z; w.kb_begin = a.w;
+    w.kb_count = b.x; w.split = b.y; w.nslices = b.z & 0xFFFFu; w.ws_tile = b.z >> 16; w.ws_slice0 = b.w;
+    return w;
+}
 
 __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
     WorkUnit w;
@@ -398,6 +420,7 @@ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
     uint32_t kb_end = w.kb_begin + p.kb_per_split;
     if (kb_end > p.k_blocks) kb_end = p.k_blocks;
     w.kb_count = kb_end - w.kb_begin;
+    w.nslices = 1; w.ws_slice0 = 0; w.ws_tile = 0;
     return w;
 }
 
@@ -445,6 +468,48 @@ __device__ __noinline__ void sum_slices_chunk(const TcParams &p, uint32_t row0, 
     }
 }
 
+// Stream-K: the same for a tile whose partial sums lie in tile-local slices of `ws`
+// ([slice][tile rows][bn] f32): the warp sums its 32 rows x `w` columns over the slices, in slice
+// order, into the final C.  16-byte loads, eight (w = 32) in flight per lane and slice: lane l owns
+// columns 4*(l % (w/4)) .. +3 of rows l / (w/4) + (32*4/w) * i.
+__device__ __noinline__ void sum_ws_chunk(const TcParams &p, const float *ws_tile, uint32_t nslices, uint32_t tile_elems,
+                                          uint32_t bn, uint32_t lrow0, uint32_t lcol, uint32_t w, float *c_tile_origin,
+                                          uint32_t rows_left, uint32_t cols_left, uint32_t lane) {
+    const uint32_t lanes_per_row = w / 4;                 // 8 or 4
+    const uint32_t rows_per_pass = 32 / lanes_per_row;    // 4 or 8
+    const uint32_t passes = 32 / rows_per_pass;           // 8 or 4
+    const uint32_t r_in = lane / lanes_per_row, c4 = (lane % lanes_per_row) * 4;
+    const float *base = ws_tile + (uint64_t)(lrow0 + r_in) * bn + lcol + c4;
+    float4 sum[8];
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i)
+        if (i < passes) sum[i] = __ldcg(reinterpret_cast<const float4 *>(base + (uint64_t)(i * rows_per_pass) * bn));
+    for (uint32_t sidx = 1; sidx < nslices; ++sidx) {
+        const float *sl = base + (uint64_t)sidx * tile_elems;
+        float4 v[8];
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i)
+            if (i < passes) v[i] = __ldcg(reinterpret_cast<const float4 *>(sl + (uint64_t)(i * rows_per_pass) * bn));
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i)
+            if (i < passes) { sum[i].x += v[i].x; sum[i].y += v[i].y; sum[i].z += v[i].z; sum[i].w += v[i].w; }
+    }
+    const bool vec_ok = p.c_vec4 != 0;
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        if (i >= passes) break;
+        const uint32_t r = r_in + i * rows_per_pass;
+        if (r >= rows_left || c4 >= cols_left) continue;
+        float *d = c_tile_origin + (uint64_t)r * p.ldc + c4;
+        if (vec_ok && c4 + 4 <= cols_left && !p.accumulate) {
+            *reinterpret_cast<float4 *>(d) = sum[i];
+        } else {
+            const float s4[4] = {sum[i].x, sum[i].y, sum[i].z, sum[i].w};
+            for (uint32_t j = 0; j < 4 && c4 + j < cols_left; ++j) d[j] = p.accumulate ? d[j] + s4[j] : s4[j];
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
@@ -480,6 +545,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t cluster_id = blockIdx.x / CG;
     const uint32_t num_clusters = gridDim.x / CG;
     const uint32_t total_units = p.batch * p.m_tiles * p.n_tiles * p.splits;
+    // work units of this cluster: a strided walk over the implicit list, or a range of the host-made one
+    const bool listed = p.units != nullptr;
+    const uint32_t u_begin = listed ? __ldg(p.unit_start + cluster_id) : cluster_id;
+    const uint32_t u_end = listed ? __ldg(p.unit_start + cluster_id + 1) : total_units;
+    const uint32_t u_step = listed ? 1u : num_clusters;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -515,8 +585,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool prof = (p.debug & 32u) != 0;
         long long tp_wait = 0, tp_issue = 0;
         const uint64_t pol_a = l2_policy((int)(p.l2_hints & 3u)), pol_b = l2_policy((int)((p.l2_hints >> 2) & 3u));
-        for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
-            const WorkUnit w = decode_unit(p, u);
+        for (uint32_t u = u_begin; u < u_end && ok; u += u_step) {
+            const WorkUnit w = listed ? load_unit(p.units + u) : decode_unit(p, u);
             const int32_t m0 = (int32_t)(w.m_blk * BM_CTA * CG + cta_rank * BM_CTA);
             const int32_t n0 = (int32_t)(w.n_blk * BN + cta_rank * C_::BN_CTA);
             const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
@@ -605,8 +675,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                               b_hi, idesc, accum);
             };
 
-            for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
-                const WorkUnit w = decode_unit(p, u);
+            for (uint32_t u = u_begin; u < u_end && ok; u += u_step) {
+                const WorkUnit w = listed ? load_unit(p.units + u) : decode_unit(p, u);
                 long long c0 = prof ? clock64() : 0;
                 ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
                 if (!ok) break;
@@ -615,7 +685,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
                 const uint32_t iters = p.npass * rounds;
-                const bool more_units = u + num_clusters < total_units;
+                const bool more_units = u + u_step < u_end;
                 uint32_t r = 0;
                 for (uint32_t it = 0; it < iters; ++it) {
                     long long c1 = prof ? clock64() : 0;
@@ -688,8 +758,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         const bool fused = p.splits > 1 && p.Cout != nullptr;
         const uint64_t pol_c = l2_policy((int)((p.l2_hints >> 4) & 3u));
-        for (uint32_t u = cluster_id; u < total_units && ok; u += num_clusters) {
-            const WorkUnit w = decode_unit(p, u);
+        for (uint32_t u = u_begin; u < u_end && ok; u += u_step) {
+            const WorkUnit w = listed ? load_unit(p.units + u) : decode_unit(p, u);
             ok = mbar_wait_patient(tmem_full_bar(acc), acc_phase, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
@@ -700,6 +770,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t row = row0 + lane;
             float *cbase = p.C + (uint64_t)zc * p.c_stride;
             const bool accum = p.accumulate && !fused;      // K-slices are plain stores; only the final sum accumulates
+            // stream-K: this unit covers only part of the tile's K range -> tile-local slice in ws
+            const bool partial = w.nslices > 1;
+            constexpr uint32_t TILE_ELEMS = BM_CTA * CG * BN;
+            const uint32_t lrow0 = cta_rank * BM_CTA + q * 32;              // tile-local first row of this warp
+            float *ws_slice = partial ? p.ws + (uint64_t)(w.ws_slice0 + w.split) * TILE_ELEMS : nullptr;
 #pragma unroll 1
             for (uint32_t c = half; c < CHUNKS; c += CSTEP) {
                 const uint32_t col = col0 + c * W;
@@ -709,7 +784,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if constexpr (W == 32) tmem_ld32(taddr + c * W, v); else tmem_ld16(taddr + c * W, v);
                 tmem_ld_wait();
                 if (p.debug & 2u) continue;
-                if (STAGING && p.epilogue_tma) {
+                if (partial) {
+                    // always in bounds: the slice holds the whole tile
+                    float *d = ws_slice + (uint64_t)(lrow0 + lane) * BN + c * W;
+#pragma unroll
+                    for (uint32_t j = 0; j < W / 4; ++j)
+                        *reinterpret_cast<uint4 *>(d + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else if (STAGING && p.epilogue_tma) {
                     // the store issued EPI_BUFS chunks ago must have finished reading this buffer
                     if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
                     __syncwarp();
@@ -774,6 +855,28 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
 
+            if (partial && row0 < p.M && !(p.debug & 6u)) {
+                // Stream-K hand-over, same protocol as the fused split-K reduction below.
+                const uint32_t slab = ((w.ws_tile * CG + cta_rank) * EPI_WARPS) + ew;
+                __threadfence();
+                __syncwarp();
+                uint32_t old = 0;
+                if (lane == 0) old = atomicAdd(p.counters + slab, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == w.nslices - 1) {
+                    __threadfence();
+                    const float *ws_tile = p.ws + (uint64_t)w.ws_slice0 * TILE_ELEMS;
+                    for (uint32_t c = half; c < CHUNKS; c += CSTEP) {
+                        const uint32_t col = col0 + c * W;
+                        if (col >= p.N) break;
+                        sum_ws_chunk(p, ws_tile, w.nslices, TILE_ELEMS, BN, lrow0, c * W, W,
+                                     p.C + (uint64_t)w.batch * p.c_stride + (uint64_t)row0 * p.ldc + col, p.M - row0,
+                                     p.N - col, lane);
+                    }
+                    __syncwarp();
+                    if (lane == 0) p.counters[slab] = 0;
+                }
+            }
             if (fused && row0 < p.M && !(p.debug & 6u)) {
                 // Fused split-K reduction.  This warp's slab of slice `split` is in global memory
                 // (plain stores); publish it and count.  The warp that finds all other slices already
@@ -1016,6 +1119,171 @@ static int choose_cfg(const TcGemm &g) {
     return best;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Stream-K schedule.  With T tiles on S resident clusters and T % S != 0 the last wave is partly
+// empty.  The first floor(T / S) waves stay whole tiles; the K blocks of the remaining T % S tiles are
+// dealt out evenly, as contiguous runs, to all S clusters.  A tile shared by several clusters gets one
+// slice of `ws` per sharer; the kernel's last arriver sums them in slice order.
+// The list depends only on the shape and the configuration, so it is built once and cached.
+// ---------------------------------------------------------------------------------------------
+struct SkPlan {
+    uint64_t key[6] = {};
+    bool valid = false;
+    TcUnit *d_units = nullptr;
+    uint32_t *d_start = nullptr;
+    uint32_t ws_slices = 0, ws_tiles = 0;
+    uint64_t age = 0;
+};
+static SkPlan g_sk[8];
+static uint64_t g_sk_clock = 0;
+static float *g_sk_ws = nullptr;
+static size_t g_sk_ws_bytes = 0;
+
+static void host_decode_tile(const TcParams &p, uint32_t t, uint32_t &batch, uint32_t &m_blk, uint32_t &n_blk) {
+    const uint32_t per_batch = p.m_tiles * p.n_tiles;
+    batch = t / per_batch;
+    const uint32_t r = t - batch * per_batch;
+    const uint32_t gsz = p.group_m * p.n_tiles;
+    const uint32_t grp = r / gsz;
+    const uint32_t first_m = grp * p.group_m;
+    const uint32_t gm = p.m_tiles - first_m < p.group_m ? p.m_tiles - first_m : p.group_m;
+    const uint32_t in_g = r - grp * gsz;
+    m_blk = first_m + in_g % gm;
+    n_blk = in_g / gm;
+}
+
+// Returns the plan to use, or nullptr when a plain schedule is as good (or scratch cannot be had).
+static const SkPlan *stream_k_plan(const TcParams &p, const TcConfig &c, int cfg, uint32_t slots, cudaStream_t stream) {
+    const uint32_t tiles = p.batch * p.m_tiles * p.n_tiles;
+    const uint32_t rem = tiles % slots, full = tiles / slots;
+    const uint32_t kb = p.k_blocks;
+    if (rem == 0 || kb < 8) return nullptr;
+    // estimated cost in tile-times: plain = full + 0.5 + 0.5 * occupancy of the last wave
+    const double plain = full + 0.5 + 0.5 * (double)rem / slots;
+    const double sk = (double)tiles / slots + 0.06;
+    if (sk > plain * 0.985) return nullptr;
+    if ((uint64_t)rem * kb / slots < 4) return nullptr;          // runs shorter than 4 K blocks are not worth it
+
+    const uint64_t key[6] = {((uint64_t)p.M << 32) | p.N, ((uint64_t)p.K << 32) | p.batch, (uint64_t)cfg, p.group_m, slots, 0};
+    SkPlan *hit = nullptr, *victim = nullptr;
+    for (SkPlan &e : g_sk) {
+        if (e.valid && !memcmp(e.key, key, sizeof key)) hit = &e;
+        if (!victim) victim = &e;
+        else if (victim->valid && (!e.valid || e.age < victim->age)) victim = &e;   // a free entry, else the oldest
+    }
+    if (hit) { hit->age = ++g_sk_clock; return hit; }
+
+    // ---- build the list on the host
+    struct HostUnit { TcUnit u; };
+    const uint32_t dp_tiles = tiles - rem;
+    const uint64_t total_kb = (uint64_t)rem * kb;
+    const uint64_t base = total_kb / slots, extra = total_kb % slots;
+    // slices per stream-K tile
+    uint32_t *nsl = (uint32_t *)calloc(rem, sizeof(uint32_t));
+    uint32_t *slice0 = (uint32_t *)calloc(rem + 1, sizeof(uint32_t));
+    if (!nsl || !slice0) { free(nsl); free(slice0); return nullptr; }
+    uint64_t pos = 0;
+    for (uint32_t cl = 0; cl < slots; ++cl) {
+        uint64_t len = base + (cl < extra ? 1 : 0), end = pos + len;
+        for (uint64_t q = pos; q < end;) {
+            const uint32_t t = (uint32_t)(q / kb);
+            const uint64_t tile_end = (uint64_t)(t + 1) * kb;
+            const uint64_t stop = end < tile_end ? end : tile_end;
+            nsl[t]++;
+            q = stop;
+        }
+        pos = end;
+    }
+    uint32_t ws_slices = 0, ws_tiles = 0;
+    uint32_t *ws_tile_idx = (uint32_t *)calloc(rem, sizeof(uint32_t));
+    if (!ws_tile_idx) { free(nsl); free(slice0); return nullptr; }
+    for (uint32_t t = 0; t < rem; ++t) {
+        slice0[t] = ws_slices;
+        if (nsl[t] > 1) { ws_tile_idx[t] = ws_tiles++; ws_slices += nsl[t]; }
+    }
+    if (ws_tiles > 0xFFFFu) { free(nsl); free(slice0); free(ws_tile_idx); return nullptr; }
+    const uint32_t max_units = full * slots + rem + 2 * slots + 8;
+    TcUnit *units = (TcUnit *)malloc((size_t)max_units * sizeof(TcUnit));
+    uint32_t *start = (uint32_t *)malloc((size_t)(slots + 1) * sizeof(uint32_t));
+    uint32_t *seen = (uint32_t *)calloc(rem, sizeof(uint32_t));     // slices handed out so far per tile
+    if (!units || !start || !seen) { free(nsl); free(slice0); free(ws_tile_idx); free(units); free(start); free(seen); return nullptr; }
+    uint32_t n = 0;
+    pos = 0;
+    // NOTE: slice indices must follow ascending K within a tile; clusters are walked in ascending order
+    // of their runs, so `seen` counts in that order.  Build per-cluster SK runs first.
+    struct Run { uint32_t t, kb0, cnt, slice; };
+    Run *runs = (Run *)malloc((size_t)(2 * slots + rem + 8) * sizeof(Run));
+    uint32_t *run_start = (uint32_t *)malloc((size_t)(slots + 1) * sizeof(uint32_t));
+    if (!runs || !run_start) { free(nsl); free(slice0); free(ws_tile_idx); free(units); free(start); free(seen); free(runs); free(run_start); return nullptr; }
+    uint32_t nr = 0;
+    for (uint32_t cl = 0; cl < slots; ++cl) {
+        run_start[cl] = nr;
+        uint64_t len = base + (cl < extra ? 1 : 0), end = pos + len;
+        for (uint64_t q = pos; q < end;) {
+            const uint32_t t = (uint32_t)(q / kb);
+            const uint64_t tile_end = (uint64_t)(t + 1) * kb;
+            const uint64_t stop = end < tile_end ? end : tile_end;
+            runs[nr++] = {t, (uint32_t)(q - (uint64_t)t * kb), (uint32_t)(stop - q), seen[t]++};
+            q = stop;
+        }
+        pos = end;
+    }
+    run_start[slots] = nr;
+    for (uint32_t cl = 0; cl < slots; ++cl) {
+        start[cl] = n;
+        for (uint32_t w = 0; w < full; ++w) {                       // whole tiles, strided like the plain schedule
+            TcUnit u = {};
+            host_decode_tile(p, w * slots + cl, u.batch, u.m_blk, u.n_blk);
+            u.kb_begin = 0; u.kb_count = kb; u.slice = 0; u.nslices = 1; u.ws_slice0 = 0;
+            units[n++] = u;
+        }
+        for (uint32_t r = run_start[cl]; r < run_start[cl + 1]; ++r) {
+            TcUnit u = {};
+            host_decode_tile(p, dp_tiles + runs[r].t, u.batch, u.m_blk, u.n_blk);
+            u.kb_begin = runs[r].kb0; u.kb_count = runs[r].cnt; u.slice = runs[r].slice;
+            u.nslices = nsl[runs[r].t] | (ws_tile_idx[runs[r].t] << 16);
+            u.ws_slice0 = slice0[runs[r].t];
+            units[n++] = u;
+        }
+    }
+    start[slots] = n;
+    free(nsl); free(slice0); free(ws_tile_idx); free(seen); free(runs); free(run_start);
+
+    // ---- device copies
+    SkPlan *e = victim;
+    if (e->valid) {
+        cudaStreamSynchronize(stream);       // a launch in flight may still read the old list
+        cudaFree(e->d_units); cudaFree(e->d_start);
+        e->valid = false; e->d_units = nullptr; e->d_start = nullptr;
+    }
+    const size_t tile_bytes = (size_t)BM_CTA * c.cg * c.bn * sizeof(float);
+    const size_t need_ws = (size_t)ws_slices * tile_bytes;
+    if (need_ws > g_sk_ws_bytes) {
+        cudaStreamSynchronize(stream);
+        if (g_sk_ws) cudaFree(g_sk_ws);
+        g_sk_ws = nullptr; g_sk_ws_bytes = 0;
+        if (cudaMalloc((void **)&g_sk_ws, need_ws) != cudaSuccess) { cudaGetLastError(); free(units); free(start); return nullptr; }
+        g_sk_ws_bytes = need_ws;
+    }
+    bool ok = cudaMalloc((void **)&e->d_units, (size_t)n * sizeof(TcUnit)) == cudaSuccess &&
+              cudaMalloc((void **)&e->d_start, (size_t)(slots + 1) * sizeof(uint32_t)) == cudaSuccess &&
+              cudaMemcpyAsync(e->d_units, units, (size_t)n * sizeof(TcUnit), cudaMemcpyHostToDevice, stream) == cudaSuccess &&
+              cudaMemcpyAsync(e->d_start, start, (size_t)(slots + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    if (ok) ok = cudaStreamSynchronize(stream) == cudaSuccess;      // the host arrays are freed below
+    free(units); free(start);
+    if (!ok) {
+        cudaGetLastError();
+        if (e->d_units) cudaFree(e->d_units);
+        if (e->d_start) cudaFree(e->d_start);
+        e->d_units = nullptr; e->d_start = nullptr;
+        return nullptr;
+    }
+    memcpy(e->key, key, sizeof key);
+    e->ws_slices = ws_slices; e->ws_tiles = ws_tiles;
+    e->valid = true; e->age = ++g_sk_clock;
+    return e;
+}
+
 int tc_gemm_launch(const TcGemm &g) {
     if (!tc_gemm_supported(g)) return ST_UNSUPPORTED;
     const int cfg = choose_cfg(g);
@@ -1104,6 +1372,15 @@ int tc_gemm_launch(const TcGemm &g) {
     const uint64_t units = (uint64_t)g.batch * p.m_tiles * p.n_tiles * p.splits;
     if (units > 0xFFFFFFFFull) return ST_UNSUPPORTED;
     uint32_t clusters = (uint32_t)(units < (uint64_t)rt.max_clusters ? units : (uint64_t)rt.max_clusters);
+    bool stream_k = false;
+    if (g.allow_stream_k && p.splits == 1 && p.npass == 1 && !p.c_trans && g.counters && c.bn >= 32 && !(p.debug & 31u)) {
+        const SkPlan *plan = stream_k_plan(p, c, cfg, (uint32_t)rt.max_clusters, g.stream);
+        if (plan && (uint64_t)plan->ws_tiles * c.cg * c.ew <= g.num_counters) {
+            p.units = plan->d_units; p.unit_start = plan->d_start; p.ws = g_sk_ws; p.counters = g.counters;
+            clusters = (uint32_t)rt.max_clusters;
+            stream_k = true;
+        }
+    }
 
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(clusters * c.cg, 1, 1);
@@ -1125,8 +1402,8 @@ int tc_gemm_launch(const TcGemm &g) {
         return ST_GEMM;
     }
     note_launch();
-    set_last_path("tc:%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
-                  p.Cout ? ":fused" : "");
+    set_last_path("tc:%s%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
+                  p.Cout ? ":fused" : "", stream_k ? ":streamk" : "");
     return ST_OK;
 }
 

@@ -144,6 +144,30 @@ def test_fused_split_k_equals_two_kernel_form(pg, oracle):
         assert np.array_equal(gemm_dev(pg, wl.BF16, a, b, lda=2056, ldb=520, ldc=524), outs[1])
 
 
+@pytest.mark.parametrize("shape", [(8192, 1024, 2048), (2048, 3000, 1096), (1304, 1800, 8192)])
+def test_stream_k_schedule(pg, oracle, shape):
+    """A partly filled last wave is dealt out over all SMs by K blocks; tiles shared by several CTAs are
+    finished by the last arriver.  Must agree with the plain schedule and with the oracle."""
+    m, n, k = shape
+    a, b = wl.config2(m, n, k)
+    ad, bd = to_dev(a, wl.BF16), to_dev(b, wl.BF16)
+    outs = {}
+    for sk in (1, 0):
+        pg.set_option("stream_k", sk); pg.set_option("path", 1); pg.set_option("tile_config", 3)
+        c = torch.full((m, n), 5.0, device="cuda")
+        for _ in range(2):                      # second call: cached list, re-armed counters
+            pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c, n)
+        pg.pg_dev_sync()
+        assert ("streamk" in pg.last_path()) == bool(sk), pg.last_path()
+        outs[sk] = c
+    assert wl.relerr(to_host(outs[1]), to_host(outs[0])) <= wl.tolerance(wl.BF16, k) / 10   # other K cuts, other rounding
+    for r0, r1, c0, c1 in ((0, 40, 0, 64), (m - 24, m, n - 40, n), (m // 2, m // 2 + 16, n // 3, n // 3 + 48)):
+        want = oracle.gemm_ex_panel(wl.BF16, a, b, r0, r1, c0, c1)
+        assert wl.relerr(to_host(outs[1][r0:r1, c0:c1]), want) <= wl.tolerance(wl.BF16, k)
+    from gpu_util import freivalds
+    assert freivalds(outs[1], ad.double(), bd.double()) <= wl.tolerance(wl.BF16, k) / 10
+
+
 SIZES = [1, 2, 3, 7, 8, 9, 16, 17, 127, 128, 129, 255, 256, 257]
 
 
