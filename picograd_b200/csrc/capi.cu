@@ -259,6 +259,18 @@ static int run_tc(const Problem &p) {
     size_t off = 0, off_a = 0, off_b = 0, off_k = 0;
     if (npa > 1 && !p.a_pieces) { off_a = off; off = align_up(off + p.batch * npa * a_rows * a_ld2 * 2, 256); }
     if (npb > 1 && !p.b_pieces) { off_b = off; off = align_up(off + p.batch * npb * b_rows * b_ld2 * 2, 256); }
+    // A 16-bit operand that breaks a TMA rule (base not 16-byte aligned, leading dimension or batch
+    // stride not a multiple of 8 elements) is copied once into scratch with an aligned pitch when the
+    // product is large enough for the copy to be noise; small ones go to the FFMA kernel instead.
+    auto misaligned = [&](const void *ptr, size_t ld, size_t stride) {
+        return ((uintptr_t)ptr & 15u) != 0 || ld % 8 != 0 || (p.batch > 1 && stride % 8 != 0);
+    };
+    const bool big = (double)p.m * (double)p.n * (double)p.k * (double)p.batch >= (double)(1u << 27);
+    const bool repitch_a = npa == 1 && !mixed && big && misaligned(p.a, p.lda, p.stride_a) && (p.batch == 1 || p.stride_a != 0);
+    const bool repitch_b = npb == 1 && !mixed && big && misaligned(p.b, p.ldb, p.stride_b) && (p.batch == 1 || p.stride_b != 0);
+    size_t off_ra = 0, off_rb = 0;
+    if (repitch_a) { off_ra = off; off = align_up(off + p.batch * a_rows * a_ld2 * 2, 256); }
+    if (repitch_b) { off_rb = off; off = align_up(off + p.batch * b_rows * b_ld2 * 2, 256); }
 
     // Skinny M (decode-like): multiply with the operands swapped, C^T = B^T A^T, so that N fills the
     // 128 tensor-memory lanes and M becomes a 16- or 32-wide UMMA N: a stage then holds 16 KB of B and
@@ -294,6 +306,25 @@ static int run_tc(const Problem &p) {
         if (st != ST_OK) return st;
     }
     char *ws = (char *)g.ws.ptr;
+
+    // ---- re-pitched copies ----------------------------------------------------------
+    if (repitch_a || repitch_b) {
+        for (int which = 0; which < 2; ++which) {
+            if (!(which == 0 ? repitch_a : repitch_b)) continue;
+            const char *src = (const char *)(which == 0 ? p.a : p.b);
+            const size_t ld = which == 0 ? p.lda : p.ldb, stride = which == 0 ? p.stride_a : p.stride_b;
+            const size_t rows = which == 0 ? a_rows : b_rows, cols = which == 0 ? a_cols : b_cols;
+            const size_t ld2 = which == 0 ? a_ld2 : b_ld2;
+            char *dst = ws + (which == 0 ? off_ra : off_rb);
+            for (size_t bi = 0; bi < p.batch; ++bi) {
+                cudaError_t e = cudaMemcpy2DAsync(dst + bi * rows * ld2 * 2, ld2 * 2, src + bi * stride * 2, ld * 2, cols * 2, rows,
+                                                  cudaMemcpyDeviceToDevice, g.stream);
+                if (e != cudaSuccess) { set_error("re-pitch copy failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_COPY; }
+            }
+            TcOperand &o = which == 0 ? t.A : t.B;
+            o.ptr = dst; o.ld = ld2; o.z_stride = rows * ld2;
+        }
+    }
 
     // ---- operand pieces -----------------------------------------------------------
     if (p.a_pieces) {

@@ -204,6 +204,22 @@ def test_unaligned_operands_fall_to_ffma_not_to_garbage(pg, oracle):
     assert e.value.status == -1                # PG_ERR_UNSUPPORTED: the dispatcher may then go elsewhere
 
 
+def test_large_unaligned_operands_are_repitched_for_the_tensor_cores(pg, oracle):
+    """Odd leading dimensions on a large product: operands are copied once to an aligned pitch instead
+    of sending a teraflop-sized problem to the FFMA kernel."""
+    m, n, k = 520, 1031, 777
+    a, b = wl.config2(m, n, k)
+    got = gemm_dev(pg, wl.BF16, a, b, lda=k + 1, ldb=n, ldc=n + 2)     # lda 778, ldb 1031: both break the 16-byte rule
+    assert pg.last_path().startswith("tc:"), pg.last_path()
+    assert wl.relerr(got, oracle.gemm_ex(wl.BF16, a, b)) <= wl.tolerance(wl.BF16, k)
+    # batched, odd batch stride
+    q = wl.to_bf16_bits(np.random.default_rng(18).standard_normal((5, 200, 136), dtype=np.float32))
+    kt = wl.to_bf16_bits(np.random.default_rng(19).standard_normal((5, 136, 1001), dtype=np.float32))
+    s = pg.pg_bmm(to_dev(q, wl.BF16), to_dev(kt, wl.BF16)); pg.pg_dev_sync()
+    assert pg.last_path().startswith("tc:"), pg.last_path()
+    assert wl.relerr(to_host(s), oracle.bmm(wl.BF16, q, kt)) <= wl.tolerance(wl.BF16, 136)
+
+
 def test_empty_and_k0(pg):
     c = torch.full((4, 4), 3.0, device="cuda")
     a = torch.zeros(4, 8, device="cuda").bfloat16()
