@@ -94,12 +94,14 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
         const int kmax = (p.K - k0) < (uint32_t)SK ? (int)(p.K - k0) : SK;
 #pragma unroll 4
         for (int kk = 0; kk < kmax; ++kk) {
+            // a thread's T rows (columns) are groups of four, 64 apart: the 16 threads of a half-warp
+            // then read 256 contiguous bytes per 16-byte load — no shared-memory bank conflict
             float a[T], b[T];
 #pragma unroll
             for (int i = 0; i < T; i += 4) {
-                const float4 va = *reinterpret_cast<const float4 *>(&As[kk][ty * T + i]);
+                const float4 va = *reinterpret_cast<const float4 *>(&As[kk][ty * 4 + i * 16]);
                 a[i] = va.x; a[i + 1] = va.y; a[i + 2] = va.z; a[i + 3] = va.w;
-                const float4 vb = *reinterpret_cast<const float4 *>(&Bs[kk][tx * T + i]);
+                const float4 vb = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4 + i * 16]);
                 b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
             }
 #pragma unroll
@@ -113,11 +115,11 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     float *Cb = p.C + (long long)bz * p.c_bs;
 #pragma unroll
     for (int i = 0; i < T; ++i) {
-        const long long gm = m0 + ty * T + i;
+        const long long gm = m0 + ty * 4 + (i / 4) * 64 + (i % 4);
         if (gm >= p.M) continue;
 #pragma unroll
         for (int j = 0; j < T; ++j) {
-            const long long gn = n0 + tx * T + j;
+            const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
             if (gn >= p.N) continue;
             float *dst = Cb + gm * p.ldc + gn;
             *dst = p.accumulate ? (*dst + acc[i][j]) : acc[i][j];
