@@ -127,6 +127,120 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// f32 x f32, both operands row-major with unit column stride and 16-byte aligned rows (the shape of
+// pg_gemm): 128 x 128 tile, K slabs of 16, 16-byte global loads, double-buffered shared memory (one
+// barrier per slab), 8 x 8 outputs per thread.  Same arithmetic as above: one fmaf chain per element,
+// k ascending (zero-filled slab tails add exact zeros).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
+    constexpr int TILE = 128, LD = TILE + 4;
+    __shared__ __align__(16) float As[2][SK][LD];
+    __shared__ __align__(16) float Bs[2][SK][LD];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const uint32_t bz = blockIdx.z;
+    const long long m0 = (long long)blockIdx.y * TILE, n0 = (long long)blockIdx.x * TILE;
+    const float *A = reinterpret_cast<const float *>(p.A) + (long long)bz * p.a_bs;
+    const float *B = reinterpret_cast<const float *>(p.B) + (long long)bz * p.b_bs;
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    // staging roles: A as 2 x float4 along k (rows a_r, a_r + 64), B as 2 x float4 along n (k rows b_k, b_k + 8)
+    const int a_r = tid >> 2, a_kq = (tid & 3) * 4;
+    const int b_k = tid >> 5, b_nq = (tid & 31) * 4;
+    float4 ra[2], rb[2];
+    auto fetch = [&](uint32_t k0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const long long gm = m0 + a_r + 64 * i, gk = (long long)k0 + a_kq;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gm < p.M) {
+                const float *src = A + gm * p.a_rs + gk;
+                if (gk + 3 < p.K) v = *reinterpret_cast<const float4 *>(src);
+                else {
+                    if (gk + 0 < p.K) v.x = src[0];
+                    if (gk + 1 < p.K) v.y = src[1];
+                    if (gk + 2 < p.K) v.z = src[2];
+                }
+            }
+            ra[i] = v;
+            const long long gkb = (long long)k0 + b_k + 8 * i, gn = n0 + b_nq;
+            float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gkb < p.K) {
+                const float *src = B + gkb * p.b_rs + gn;
+                if (gn + 3 < p.N) w = *reinterpret_cast<const float4 *>(src);
+                else {
+                    if (gn + 0 < p.N) w.x = src[0];
+                    if (gn + 1 < p.N) w.y = src[1];
+                    if (gn + 2 < p.N) w.z = src[2];
+                }
+            }
+            rb[i] = w;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            As[buf][a_kq + 0][a_r + 64 * i] = ra[i].x;
+            As[buf][a_kq + 1][a_r + 64 * i] = ra[i].y;
+            As[buf][a_kq + 2][a_r + 64 * i] = ra[i].z;
+            As[buf][a_kq + 3][a_r + 64 * i] = ra[i].w;
+            *reinterpret_cast<float4 *>(&Bs[buf][b_k + 8 * i][b_nq]) = rb[i];
+        }
+    };
+
+    int buf = 0;
+    if (p.K) { fetch(0); stash(0); }
+    __syncthreads();
+    for (uint32_t k0 = 0; k0 < p.K; k0 += SK) {
+        const bool more = k0 + SK < p.K;
+        if (more) fetch(k0 + SK);
+#pragma unroll
+        for (int kk = 0; kk < SK; ++kk) {
+            float a[8], b[8];
+#pragma unroll
+            for (int i = 0; i < 8; i += 4) {
+                const float4 va = *reinterpret_cast<const float4 *>(&As[buf][kk][ty * 4 + i * 16]);
+                a[i] = va.x; a[i + 1] = va.y; a[i + 2] = va.z; a[i + 3] = va.w;
+                const float4 vb = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4 + i * 16]);
+                b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+        buf ^= 1;
+    }
+
+    float *Cb = p.C + (long long)bz * p.c_bs;
+    const bool vec = (p.ldc % 4 == 0) && (((uintptr_t)Cb & 15) == 0) && !p.accumulate;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const long long gm = m0 + ty * 4 + (i / 4) * 64 + (i % 4);
+        if (gm >= p.M) continue;
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh) {
+            const long long gn = n0 + tx * 4 + jh * 64;
+            float *dst = Cb + gm * p.ldc + gn;
+            if (vec && gn + 3 < p.N) {
+                *reinterpret_cast<float4 *>(dst) = make_float4(acc[i][jh * 4], acc[i][jh * 4 + 1], acc[i][jh * 4 + 2], acc[i][jh * 4 + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (gn + j < p.N) dst[j] = p.accumulate ? dst[j] + acc[i][jh * 4 + j] : acc[i][jh * 4 + j];
+            }
+        }
+    }
+}
+
 int simt_gemm_launch(const SimtGemm &g) {
     if (g.M == 0 || g.N == 0 || g.batch == 0) return ST_OK;
     SimtParams p;
@@ -149,7 +263,11 @@ int simt_gemm_launch(const SimtGemm &g) {
         q.C = g.C + (long long)done * g.c_bs;
         dim3 grid((g.N + tile - 1) / tile, (g.M + tile - 1) / tile, nb);
         if (grid.y > 65535u) { set_error("simt gemm: M too large for one launch"); return ST_UNSUPPORTED; }
-        if (big) simt_gemm_kernel<128><<<grid, 256, 0, g.stream>>>(q);
+        const bool nn_f32 = big && g.dtype_a == DT_F32 && g.dtype_b == DT_F32 && g.a_cs == 1 && g.b_cs == 1 &&
+                            g.a_rs % 4 == 0 && g.b_rs % 4 == 0 && g.a_bs % 4 == 0 && g.b_bs % 4 == 0 &&
+                            (((uintptr_t)g.A | (uintptr_t)g.B) & 15) == 0;
+        if (nn_f32) sgemm_nn_kernel<<<grid, 256, 0, g.stream>>>(q);
+        else if (big) simt_gemm_kernel<128><<<grid, 256, 0, g.stream>>>(q);
         else simt_gemm_kernel<64><<<grid, 256, 0, g.stream>>>(q);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { set_error("simt gemm launch: %s", cudaGetErrorString(e)); return ST_GEMM; }
