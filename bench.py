@@ -330,6 +330,23 @@ def run_other_config(args):
         flops = 2 * 2.0 * 64 * 2048 * 2048 * 128
         byts = 1140850688 + 637534208
         name, dt = "pg_bmm QK^T -> softmax -> PV, bf16 [64,2048,128]", "bf16"
+    elif cfg in ("linear", "linear-unfused"):
+        # nn/nn.c:46-96 (Linear forward) at the first layer of configuration 5, GELU instead of ReLU,
+        # a bf16 copy of the output for the next layer: one kernel, or GEMM + a separate GELU/cast pass
+        m, k, n = 8192, 4096, 16384
+        x, w1, _ = wl.config5()
+        xd, w1d = to_dev(x, wl.BF16), to_dev(w1, wl.BF16)
+        bias = torch.linspace(-1, 1, n, device="cuda")
+        c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        c16 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        if cfg == "linear":
+            fn = lambda: pg.pg_gemm_fused_ex(wl.BF16, m, n, k, xd, k, w1d, n, c, n, bias, pg.PG_ACT_GELU, c16, n)
+        else:
+            def fn():
+                pg.pg_gemm_fused_ex(wl.BF16, m, n, k, xd, k, w1d, n, c, n, bias, pg.PG_ACT_NONE)
+                ops.gelu(c, out16=torch.bfloat16, want_f32=True)
+        flops, byts = 2.0 * m * n * k, (m * k + k * n) * 2 + m * n * 6 + n * 4
+        name, dt = f"Linear forward bf16 {m}x{k} -> {n}, bias + GELU + bf16 copy ({cfg})", "bf16"
     else:
         x, w1, w2 = wl.config5()
         xd, w1d, w2d = (to_dev(t, wl.BF16) for t in (x, w1, w2))
@@ -375,7 +392,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--config", default="2", choices=["1", "2", "3a", "3b", "4", "5"],
+    ap.add_argument("--config", default="2", choices=["1", "2", "3a", "3b", "4", "5", "linear", "linear-unfused"],
                     help="2 (default) is the headline metric; the others time the remaining configurations "
                          "(single GPU, device-resident) and print one JSON line each")
     args = ap.parse_args()

@@ -66,6 +66,34 @@ PG_B200_API void pg_b200_bgemm(size_t m, size_t n, size_t k, const uint16_t *a, 
 PG_B200_API int pg_b200_gemm_ex(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda,
                     const void *b, size_t ldb, float *c, size_t ldc);
 
+/* ---- fused epilogues: backend/cpu/gemm.c:632-817, used by nn/nn.c:60,85 ------ */
+
+/* pg_act of backend/cpu/gemm.h */
+#define PG_B200_ACT_NONE 0
+#define PG_B200_ACT_RELU 1
+#define PG_B200_ACT_GELU 2   /* 0.5 x (1 + erf(x / sqrt 2)) */
+
+/* pg_cpu_gemm_fused_ex (gemm.c:806-817): C = act(bias[j] + A*B), bias of n floats or NULL.
+ * In picograd each row of C starts as the bias row and the micro-kernels accumulate onto it, so
+ * the sum of column j is a chain that STARTS at bias[j]; the FFMA path here does the same and
+ * agrees bit for bit for ACT_NONE and ACT_RELU (ACT_GELU to the last bits of erff); the
+ * tensor-core path adds the bias to the finished f32 sum.  Either way bias and activation are
+ * applied in the GEMM kernel's own epilogue, on the accumulators, before C is written once.
+ * Device pointers (bias too), or host pointers throughout, staged like pg_b200_gemm_ex. */
+PG_B200_API int pg_b200_gemm_fused_ex(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda,
+                          const void *b, size_t ldb, float *c, size_t ldc, const float *bias, int act);
+/* pg_cpu_gemm_fused (gemm.c:685-716): the f32 form; void like the entry it replaces, errors are
+ * kept for pg_b200_last_error() and pg_b200_sync(). */
+PG_B200_API void pg_b200_gemm_fused(size_t m, size_t n, size_t k, const float *a, size_t lda, const float *b,
+                        size_t ldb, float *c, size_t ldc, const float *bias, int act);
+/* No counterpart in picograd, where the next layer re-reads the f32 C and converts it
+ * (ops/cast.c): the same call also writes C rounded to f16/bf16 (round-to-nearest-even) into
+ * c16 (m x n, leading dimension ldc16 elements), so that a 16-bit consumer reads 2 bytes per
+ * element instead of 4 and no cast kernel runs.  Device pointers only. */
+PG_B200_API int pg_b200_gemm_fused_out16(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda,
+                             const void *b, size_t ldb, float *c, size_t ldc, const float *bias, int act,
+                             uint16_t *c16, size_t ldc16, int dtype16);
+
 /* ---- the callers' shapes: ops/matmul.c and autograd/autograd.c ------------- */
 
 /* General strided-batched product behind pg_matmul / pg_bmm / pg_tensordot

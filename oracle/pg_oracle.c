@@ -196,7 +196,16 @@ static inline float load1(int dtype, const void *p, size_t i)
 typedef struct {
     int dtype; size_t k; const void *a; size_t lda; const void *b; size_t ldb;
     float *c; size_t ldc; size_t r0, r1, c0, c1, nstrip;
+    const float *bias; int act;
 } panel_ctx;
+
+/* backend/cpu/gemm.c:632-636 (act_apply) */
+static inline float act_apply(float x, int act)
+{
+    if (act == PGO_ACT_RELU) return x > 0 ? x : 0;
+    if (act == PGO_ACT_GELU) return 0.5f * x * (1.0f + erff(x * 0.70710678118f));
+    return x;
+}
 
 static void panel_range(void *vctx, size_t begin, size_t end)
 {
@@ -208,6 +217,9 @@ static void panel_range(void *vctx, size_t begin, size_t end)
         size_t j0 = x->c0 + (t % x->nstrip) * PGO_JB;
         size_t w = x->c1 - j0 < PGO_JB ? x->c1 - j0 : PGO_JB;
         memset(acc, 0, sizeof acc);
+        if (x->bias)                 /* gemm.c:729-735: the C rows start as the bias row */
+            for (size_t r = 0; r < h; r++)
+                memcpy(acc[r], x->bias + j0, w * sizeof(float));
         for (size_t p = 0; p < x->k; p++) {
             const float *bp;
             if (x->dtype == PGO_F32) {
@@ -223,6 +235,9 @@ static void panel_range(void *vctx, size_t begin, size_t end)
                 for (size_t j = 0; j < w; j++)
                     acc[r][j] = __builtin_fmaf(av[r], bp[j], acc[r][j]);
         }
+        if (x->act != PGO_ACT_NONE)  /* gemm.c:770-779: over the finished rows */
+            for (size_t r = 0; r < h; r++)
+                for (size_t j = 0; j < w; j++) acc[r][j] = act_apply(acc[r][j], x->act);
         for (size_t r = 0; r < h; r++)
             memcpy(x->c + (i0 + r) * x->ldc + j0, acc[r], w * sizeof(float));
     }
@@ -239,8 +254,23 @@ void pgo_gemm_ex_panel(int dtype, size_t m, size_t n, size_t k,
     if (c1 > n) c1 = n;
     if (r0 >= r1 || c0 >= c1) return;
     panel_ctx x = {dtype, k, a, lda, b, ldb, c, ldc, r0, r1, c0, c1,
-                   (c1 - c0 + PGO_JB - 1) / PGO_JB};
+                   (c1 - c0 + PGO_JB - 1) / PGO_JB, NULL, PGO_ACT_NONE};
     pgo_parallel_for(((r1 - r0 + PGO_IB - 1) / PGO_IB) * x.nstrip, panel_range, &x);
+}
+
+/* backend/cpu/gemm.c:685-716 (pg_cpu_gemm_fused) and :718-817 (pg_cpu_gemm_fused_ex): every
+ * row of C is set to the bias row (zeros without a bias), the same micro-kernels as pg_gemm_ex
+ * accumulate A*B onto it K block by K block -- so each element is ONE chain of fused
+ * multiply-adds that starts at bias[j], k ascending -- and the activation runs over the
+ * finished rows.  With k == 0 the result is act(bias). */
+void pgo_gemm_fused_ex(int dtype, size_t m, size_t n, size_t k,
+                       const void *a, size_t lda, const void *b, size_t ldb,
+                       float *c, size_t ldc, const float *bias, int act)
+{
+    if (m == 0 || n == 0) return;
+    panel_ctx x = {dtype, k, a, lda, b, ldb, c, ldc, 0, m, 0, n,
+                   (n + PGO_JB - 1) / PGO_JB, bias, act};
+    pgo_parallel_for(((m + PGO_IB - 1) / PGO_IB) * x.nstrip, panel_range, &x);
 }
 
 void pgo_gemm_ex(int dtype, size_t m, size_t n, size_t k,

@@ -39,6 +39,14 @@ void pgo_gemm_ex(int dtype, size_t m, size_t n, size_t k,
 
 /* Only rows [r0,r1) x columns [c0,c1) of C are computed (same arithmetic);
  * lets a test check panels of a full-size product in seconds. */
+/* pg_cpu_gemm_fused_ex: C = act(bias[j] + A*B), the chain of column j starting at bias[j]
+ * (bias may be NULL).  act: PGO_ACT_* = PG_ACT_* of backend/cpu/gemm.h:37-39. */
+#define PGO_ACT_NONE 0
+#define PGO_ACT_RELU 1
+#define PGO_ACT_GELU 2
+void pgo_gemm_fused_ex(int dtype, size_t m, size_t n, size_t k,
+                       const void *a, size_t lda, const void *b, size_t ldb,
+                       float *c, size_t ldc, const float *bias, int act);
 void pgo_gemm_ex_panel(int dtype, size_t m, size_t n, size_t k,
                        const void *a, size_t lda, const void *b, size_t ldb,
                        float *c, size_t ldc,

@@ -26,6 +26,9 @@ SIGNATURES = {
     "pg_b200_hgemm": (None, [_sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]),
     "pg_b200_bgemm": (None, [_sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]),
     "pg_b200_gemm_ex": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]),
+    "pg_b200_gemm_fused_ex": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _i]),
+    "pg_b200_gemm_fused": (None, [_sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _i]),
+    "pg_b200_gemm_fused_out16": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _i, _vp, _sz, _i]),
     "pg_b200_gemm_batched": (_i, [_i, _i, _i, _i, _sz, _sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz,
                                   _vp, _sz, _sz, _i]),
     "pg_b200_matmul_backward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _vp, _i, _vp, _vp, _vp]),

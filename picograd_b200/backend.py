@@ -105,6 +105,51 @@ def pg_bgemm(m, n, k, a, lda, b, ldb, c, ldc):
     pg_gemm_ex(PG_DTYPE_BF16, m, n, k, a, lda, b, ldb, c, ldc)
 
 
+PG_ACT_NONE, PG_ACT_RELU, PG_ACT_GELU = 0, 1, 2   # backend/cpu/gemm.h:37-39
+
+
+def pg_gemm_fused_ex(dtype, m, n, k, a, lda, b, ldb, c, ldc, bias=None, act=PG_ACT_NONE, c16=None, ldc16=0):
+    """pg_cpu_gemm_fused_ex (backend/cpu/gemm.c:806-817): C = act(bias[j] + A*B), bias an f32
+    tensor of n elements or None, applied in the GEMM kernel's epilogue.  Device tensors, or host
+    tensors / numpy arrays throughout (staged inside the call).  c16 (device only, optional): an
+    f16/bf16 tensor that receives C rounded to its dtype in the same pass."""
+    _ready()
+
+    def ptr(x):
+        if x is None:
+            return None
+        return x.data_ptr() if isinstance(x, torch.Tensor) else x.ctypes.data
+
+    if c16 is None:
+        _check(lib.pg_b200_gemm_fused_ex(dtype, m, n, k, ptr(a), lda, ptr(b), ldb, ptr(c), ldc, ptr(bias), act),
+               "pg_gemm_fused_ex")
+        return
+    dt16 = {torch.float16: PG_DTYPE_F16, torch.bfloat16: PG_DTYPE_BF16}.get(c16.dtype)
+    if dt16 is None:
+        raise TypeError("c16 must be float16 or bfloat16")
+    _check(lib.pg_b200_gemm_fused_out16(dtype, m, n, k, ptr(a), lda, ptr(b), ldb, ptr(c), ldc, ptr(bias), act,
+                                        ptr(c16), ldc16 or n, dt16), "pg_gemm_fused_ex(out16)")
+
+
+def pg_gemm_fused(m, n, k, a, lda, b, ldb, c, ldc, bias=None, act=PG_ACT_NONE):
+    """pg_cpu_gemm_fused (backend/cpu/gemm.c:685-716), the f32 entry nn/nn.c:60,85 calls."""
+    pg_gemm_fused_ex(PG_DTYPE_F32, m, n, k, a, lda, b, ldb, c, ldc, bias, act)
+
+
+def pg_linear_forward(x, weight, bias=None, relu=False, out16=None):
+    """pg_linear_forward / pg_linear_forward_relu (nn/nn.c:46-96) on device tensors:
+    x [m, in] times weight [in, out] plus bias [out], optionally through ReLU, one kernel."""
+    m, k = x.shape
+    k2, n = weight.shape
+    if k != k2 or x.dtype != weight.dtype:
+        raise ValueError("pg_linear_forward: x [m,in] and weight [in,out] of one dtype")
+    dt = {torch.float32: PG_DTYPE_F32, torch.float16: PG_DTYPE_F16, torch.bfloat16: PG_DTYPE_BF16}[x.dtype]
+    out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    pg_gemm_fused_ex(dt, m, n, k, x.contiguous(), k, weight.contiguous(), n, out, n, bias,
+                     PG_ACT_RELU if relu else PG_ACT_NONE, out16, n if out16 is not None else 0)
+    return out
+
+
 def pg_gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc):
     """pg_gemm_ex with HOST buffers, the way ops/matmul.c:264-271 calls it: a, b, c are CPU
     tensors (pinned or pageable) or numpy arrays; staging copies happen inside the call."""

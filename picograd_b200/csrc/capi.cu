@@ -29,7 +29,7 @@ struct State {
     uint32_t *counters = nullptr;         // arrival counters of the fused split-K reduction (zero between launches)
     uint32_t num_counters = 0;
     DeviceBuf ws;                      // scratch: operand pieces, split-K slices
-    DeviceBuf stage_a, stage_b, stage_c;  // device staging for host-pointer calls
+    DeviceBuf stage_a, stage_b, stage_c, stage_bias;  // device staging for host-pointer calls
     DeviceBuf grad_pieces;             // bf16 pieces of the f32 gradient, shared by both backward products
     // options
     int opt_path = 0;        // 0 choose, 1 tensor-core only, 2 FFMA only
@@ -189,6 +189,14 @@ struct Problem {
     const uint16_t *a_pieces = nullptr, *b_pieces = nullptr;
     size_t pieces_ld = 0;
     uint32_t pieces_n = 0;
+    // pg_cpu_gemm_fused_ex (backend/cpu/gemm.c:718-817): C = act(bias[col] + A*B), batch == 1, no
+    // accumulate; c16 (optional) receives C rounded to dtype16
+    const float *bias = nullptr;
+    int act = 0;
+    uint16_t *c16 = nullptr;
+    size_t ld16 = 0;
+    int dtype16 = DT_BF16;
+    bool has_epilogue() const { return bias != nullptr || act != 0 || c16 != nullptr; }
 };
 
 static int run_simt(const Problem &p) {
@@ -201,6 +209,7 @@ static int run_simt(const Problem &p) {
     s.a_bs = (int64_t)p.stride_a; s.b_bs = (int64_t)p.stride_b;
     s.C = p.c; s.ldc = (int64_t)p.ldc; s.c_bs = (int64_t)p.stride_c;
     s.accumulate = p.accumulate;
+    s.bias = p.bias; s.act = p.act; s.c16 = p.c16; s.ld16 = (int64_t)p.ld16; s.dtype16 = p.dtype16;
     s.stream = g.stream;
     int st = simt_gemm_launch(s);
     if (st == ST_OK) set_last_path("simt");
@@ -388,6 +397,10 @@ static int run_tc(const Problem &p) {
             t.accumulate = 0;
         }
     }
+    // Bias and activation ride in the kernel's epilogue when every tile holds finished sums; K-slices
+    // and the swapped route finish C first and one elementwise pass follows.
+    const bool epi_in_kernel = p.has_epilogue() && splits == 1 && !swap;
+    if (epi_in_kernel) { t.bias = p.bias; t.act = p.act; t.c16 = p.c16; t.ld16 = p.ld16; t.dtype16 = p.dtype16; }
     if (swap) {
         // A' = B (its N runs along the tile rows), B' = A, tile stored transposed into the same C
         TcOperand opa = t.A;
@@ -410,6 +423,10 @@ static int run_tc(const Problem &p) {
                                   (uint32_t)p.n, ws_ld, p.accumulate, g.stream);
         if (st != ST_OK) return st;
     }
+    if (p.has_epilogue() && !epi_in_kernel) {
+        st = bias_act_launch(p.c, p.ldc, p.bias, p.act, p.c16, p.ld16, p.dtype16, p.m, p.n, g.stream);
+        if (st != ST_OK) return st;
+    }
     return ST_OK;
 }
 
@@ -417,6 +434,10 @@ static int run_problem(const Problem &p) {
     if (!ready()) return g.init_status;
     if (p.m == 0 || p.n == 0 || p.batch == 0) return ST_OK;
     if (!p.a || !p.b || !p.c) { set_error("null operand"); return ST_GEMM; }
+    if (p.has_epilogue() && (p.batch != 1 || p.accumulate)) {
+        set_error("fused bias/activation takes one product and overwrites C");
+        return ST_UNSUPPORTED;
+    }
     const bool f32f32 = p.dtype_a == DT_F32 && p.dtype_b == DT_F32;
     bool want_tc = g.opt_path != 2 && p.k > 0;
     if (f32f32 && !g.opt_f32_tc && g.opt_path != 1) want_tc = false;
@@ -441,7 +462,7 @@ static bool is_device_ptr(const void *p) {
 
 // Host-pointer pg_gemm_ex: stage compact copies through device memory.
 static int gemm_ex_host(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
-                        float *c, size_t ldc) {
+                        float *c, size_t ldc, const float *dev_bias, int act) {
     const size_t es = esize(dtype);
     const size_t k8 = align_up(k, 8), n8 = align_up(n, 8), n4 = align_up(n, 4);
     int st;
@@ -457,6 +478,7 @@ static int gemm_ex_host(int dtype, size_t m, size_t n, size_t k, const void *a, 
     }
     Problem p = {dtype, dtype, 0, 0, 1, m, n, k, g.stage_a.ptr, k8, 0, g.stage_b.ptr, n8, 0,
                  (float *)g.stage_c.ptr, n4, 0, 0};
+    p.bias = dev_bias; p.act = act;
     st = run_problem(p);
     if (st != ST_OK) return st;
     e = cudaMemcpy2DAsync(c, ldc * 4, g.stage_c.ptr, n4 * 4, n * 4, m, cudaMemcpyDeviceToHost, g.stream);
@@ -494,7 +516,8 @@ static bool host_pipe_ready(size_t gm, size_t gn) {
 }
 
 static int gemm_ex_host_pipelined(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b,
-                                  size_t ldb, float *c, size_t ldc, size_t bm, size_t bn) {
+                                  size_t ldb, float *c, size_t ldc, size_t bm, size_t bn, const float *dev_bias,
+                                  int act) {
     const size_t es = esize(dtype);
     const size_t k8 = align_up(k, 8), n8 = align_up(n, 8), n4 = align_up(n, 4);
     const size_t gm = (m + bm - 1) / bm, gn = (n + bn - 1) / bn;
@@ -536,6 +559,7 @@ static int gemm_ex_host_pipelined(int dtype, size_t m, size_t n, size_t k, const
                 cudaStreamWaitEvent(g.stream, g_pipe.ev_b[j], 0);
                 Problem p = {dtype, dtype, 0, 0, 1, rh, cw, k, da + r0 * k8 * es, k8, 0, db + c0 * es, n8, 0,
                              dc + r0 * n4 + c0, n4, 0, 0};
+                p.bias = dev_bias ? dev_bias + c0 : nullptr; p.act = act;
                 st = run_problem(p);
                 if (st != ST_OK) { cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream); return st; }
                 cudaEvent_t done = g_pipe.ev_c[i * gn + j];
@@ -559,22 +583,41 @@ static int gemm_ex_host_pipelined(int dtype, size_t m, size_t n, size_t k, const
 }
 
 static int gemm_ex_any(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
-                       float *c, size_t ldc) {
+                       float *c, size_t ldc, const float *bias = nullptr, int act = 0, uint16_t *c16 = nullptr,
+                       size_t ld16 = 0, int dtype16 = DT_BF16) {
     if (!ready()) return g.init_status;
     if (dtype != DT_F32 && dtype != DT_F16 && dtype != DT_BF16) { set_error("bad dtype %d", dtype); return ST_UNSUPPORTED; }
+    if (act < 0 || act > 2) { set_error("bad activation %d", act); return ST_UNSUPPORTED; }
+    if (c16 && dtype16 != DT_F16 && dtype16 != DT_BF16) { set_error("bad 16-bit output dtype %d", dtype16); return ST_UNSUPPORTED; }
     if (m == 0 || n == 0) return ST_OK;
     const bool da = is_device_ptr(a), db = is_device_ptr(b), dc = is_device_ptr(c);
     if (da && db && dc) {
+        if ((bias && !is_device_ptr(bias)) || (c16 && !is_device_ptr(c16))) {
+            set_error("pg_gemm_fused_ex: bias and the 16-bit output must be device pointers like A, B and C");
+            return ST_UNSUPPORTED;
+        }
         Problem p = {dtype, dtype, 0, 0, 1, m, n, k, a, lda, 0, b, ldb, 0, c, ldc, 0, 0};
+        p.bias = bias; p.act = act; p.c16 = c16; p.ld16 = ld16; p.dtype16 = dtype16;
         return run_problem(p);
     }
     if (!da && !db && !dc) {
+        if (c16) { set_error("pg_gemm_fused_ex: the 16-bit output is for device pointers only"); return ST_UNSUPPORTED; }
+        const float *dev_bias = nullptr;
+        if (bias) {
+            if (is_device_ptr(bias)) { set_error("pg_gemm_fused_ex: host operands need a host bias"); return ST_UNSUPPORTED; }
+            int st = grow(g.stage_bias, n * 4 + 256);
+            if (st != ST_OK) return st;
+            if (cudaMemcpyAsync(g.stage_bias.ptr, bias, n * 4, cudaMemcpyHostToDevice, g.stream) != cudaSuccess) {
+                set_error("H2D staging of the bias failed"); cudaGetLastError(); return ST_COPY;
+            }
+            dev_bias = (const float *)g.stage_bias.ptr;
+        }
         // pipeline only products whose copies dominate and that cut into at least 2 x 2 blocks
         const size_t blk = 2048;
         if (g.opt_host_pipeline && k > 0 && m >= 2 * blk && n >= 2 * blk && (m + blk - 1) / blk <= 16 &&
             (n + blk - 1) / blk <= 16 && host_pipe_ready((m + blk - 1) / blk, (n + blk - 1) / blk))
-            return gemm_ex_host_pipelined(dtype, m, n, k, a, lda, b, ldb, c, ldc, blk, blk);
-        return gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc);
+            return gemm_ex_host_pipelined(dtype, m, n, k, a, lda, b, ldb, c, ldc, blk, blk, dev_bias, act);
+        return gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc, dev_bias, act);
     }
     set_error("pg_gemm_ex: A, B and C must all be device pointers or all host pointers");
     return ST_UNSUPPORTED;
@@ -670,6 +713,20 @@ void pg_b200_bgemm(size_t m, size_t n, size_t k, const uint16_t *a, size_t lda, 
 int pg_b200_gemm_ex(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
                     float *c, size_t ldc) {
     return gemm_ex_any(dtype, m, n, k, a, lda, b, ldb, c, ldc);
+}
+
+int pg_b200_gemm_fused_ex(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+                          float *c, size_t ldc, const float *bias, int act) {
+    return gemm_ex_any(dtype, m, n, k, a, lda, b, ldb, c, ldc, bias, act);
+}
+void pg_b200_gemm_fused(size_t m, size_t n, size_t k, const float *a, size_t lda, const float *b, size_t ldb, float *c,
+                        size_t ldc, const float *bias, int act) {
+    (void)gemm_ex_any(DT_F32, m, n, k, a, lda, b, ldb, c, ldc, bias, act);
+}
+int pg_b200_gemm_fused_out16(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b,
+                             size_t ldb, float *c, size_t ldc, const float *bias, int act, uint16_t *c16, size_t ldc16,
+                             int dtype16) {
+    return gemm_ex_any(dtype, m, n, k, a, lda, b, ldb, c, ldc, bias, act, c16, ldc16, dtype16);
 }
 
 int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int trans_b, size_t batch, size_t m, size_t n,

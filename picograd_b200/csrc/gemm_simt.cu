@@ -26,7 +26,21 @@ struct SimtParams {
     const void *B; long long b_rs, b_cs, b_bs;
     float *C; long long ldc, c_bs;
     int dtype_a, dtype_b, accumulate;
+    // fused epilogue of pg_cpu_gemm_fused_ex (backend/cpu/gemm.c:718-817): each row of C starts as the
+    // bias row, the micro-kernels accumulate onto it, the activation runs over the finished row
+    const float *bias; int act;
+    unsigned short *c16; long long ld16, c16_bs; int dtype16;
 };
+
+__device__ __forceinline__ float simt_act(float x, int act) {
+    if (act == 1) return x > 0.0f ? x : 0.0f;
+    if (act == 2) return 0.5f * x * (1.0f + erff(x * 0.70710678118f));
+    return x;
+}
+__device__ __forceinline__ unsigned short simt_to16(float v, int dtype16) {
+    if (dtype16 == DT_BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    return __half_as_ushort(__float2half_rn(v));
+}
 
 __device__ __forceinline__ float load_as_f32(const void *base, long long idx, int dtype) {
     if (dtype == DT_F32) return reinterpret_cast<const float *>(base)[idx];
@@ -54,11 +68,16 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     const long long m0 = (long long)blockIdx.y * TILE, n0 = (long long)blockIdx.x * TILE;
     const long long a_off = (long long)bz * p.a_bs, b_off = (long long)bz * p.b_bs;
 
+    // the chain of column gn starts at bias[gn], as in picograd, where the micro-kernel accumulates onto
+    // a C row that was initialised with the bias
     float acc[T][T];
 #pragma unroll
-    for (int i = 0; i < T; ++i)
+    for (int j = 0; j < T; ++j) {
+        const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
+        const float b0 = (p.bias && gn < p.N) ? p.bias[gn] : 0.0f;
 #pragma unroll
-        for (int j = 0; j < T; ++j) acc[i][j] = 0.0f;
+        for (int i = 0; i < T; ++i) acc[i][j] = b0;
+    }
 
     // walk the contiguous dimension of each operand with consecutive threads
     const bool a_k_contig = (p.a_cs == 1);
@@ -122,7 +141,9 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
             const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
             if (gn >= p.N) continue;
             float *dst = Cb + gm * p.ldc + gn;
-            *dst = p.accumulate ? (*dst + acc[i][j]) : acc[i][j];
+            const float r = simt_act(acc[i][j], p.act);
+            *dst = p.accumulate ? (*dst + r) : r;
+            if (p.c16) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn] = simt_to16(r, p.dtype16);
         }
     }
 }
@@ -146,9 +167,12 @@ __global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
 
     float acc[8][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int j = 0; j < 8; ++j) {
+        const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
+        const float b0 = (p.bias && gn < p.N) ? p.bias[gn] : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int i = 0; i < 8; ++i) acc[i][j] = b0;
+    }
 
     // staging roles: A as 2 x float4 along k (rows a_r, a_r + 64), B as 2 x float4 along n (k rows b_k, b_k + 8)
     const int a_r = tid >> 2, a_kq = (tid & 3) * 4;
@@ -222,10 +246,23 @@ __global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
 
     float *Cb = p.C + (long long)bz * p.c_bs;
     const bool vec = (p.ldc % 4 == 0) && (((uintptr_t)Cb & 15) == 0) && !p.accumulate;
+    if (p.act) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i][j] = simt_act(acc[i][j], p.act);
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const long long gm = m0 + ty * 4 + (i / 4) * 64 + (i % 4);
         if (gm >= p.M) continue;
+        if (p.c16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
+                if (gn < p.N) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn] = simt_to16(acc[i][j], p.dtype16);
+            }
+        }
 #pragma unroll
         for (int jh = 0; jh < 2; ++jh) {
             const long long gn = n0 + tx * 4 + jh * 64;
@@ -249,6 +286,8 @@ int simt_gemm_launch(const SimtGemm &g) {
     p.B = g.B; p.b_rs = g.b_rs; p.b_cs = g.b_cs; p.b_bs = g.b_bs;
     p.C = g.C; p.ldc = g.ldc; p.c_bs = g.c_bs;
     p.dtype_a = g.dtype_a; p.dtype_b = g.dtype_b; p.accumulate = g.accumulate;
+    p.bias = g.bias; p.act = g.act; p.c16 = (unsigned short *)g.c16; p.ld16 = g.ld16;
+    p.c16_bs = (long long)g.M * g.ld16; p.dtype16 = g.dtype16;
     // grid.z is limited to 65535: launch the batch in slices
     const bool big = (uint64_t)g.M * g.N >= (uint64_t)512 * 512 * 4;
     const int tile = big ? 128 : 64;
@@ -261,6 +300,7 @@ int simt_gemm_launch(const SimtGemm &g) {
         q.A = (const char *)g.A + (long long)done * g.a_bs * (long long)esa;
         q.B = (const char *)g.B + (long long)done * g.b_bs * (long long)esb;
         q.C = g.C + (long long)done * g.c_bs;
+        if (q.c16) q.c16 = p.c16 + (long long)done * p.c16_bs;
         dim3 grid((g.N + tile - 1) / tile, (g.M + tile - 1) / tile, nb);
         if (grid.y > 65535u) { set_error("simt gemm: M too large for one launch"); return ST_UNSUPPORTED; }
         const bool nn_f32 = big && g.dtype_a == DT_F32 && g.dtype_b == DT_F32 && g.a_cs == 1 && g.b_cs == 1 &&

@@ -91,6 +91,13 @@ struct TcParams {
                                   // stores, 4 = no TMEM reads, 8 = alternate accumulators, 16 = no MMAs
     uint32_t l2_hints;            // 2 bits each for A loads, B loads, C stores: 0 normal, 1 evict_first, 2 evict_last
     uint32_t c_trans;             // element (row, col) of the tile goes to C[col*ldc + row] (swapped operands)
+    // fused epilogue (picograd pg_cpu_gemm_fused_ex): C = act(A*B + bias[col]); optional 16-bit copy of C
+    const float *bias;
+    uint32_t act;                 // 0 none, 1 relu, 2 gelu (erf form)
+    unsigned short *c16;
+    uint64_t ld16;
+    uint32_t dtype16;
+    uint32_t bias_vec4, c16_vec;  // bias 16-byte aligned; c16 rows 16-byte aligned
     float *C;                     // splits > 1: the K-slices [split][rows][ldc]; else the result
     uint64_t ldc, c_stride;
     // fused split-K reduction: the last warp to finish a slab sums the slices (in slice order) into Cout
@@ -422,6 +429,50 @@ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
     w.kb_count = kb_end - w.kb_begin;
     w.nslices = 1; w.ws_slice0 = 0; w.ws_tile = 0;
     return w;
+}
+
+// 0.5 x (1 + erf(x / sqrt 2)), picograd's act_apply (backend/cpu/gemm.c:632-636), with
+// erf(a) = sign(a) (1 - 2^(t Q(t))), t = min(|a|, 4): one piece, no branch, 13 instructions, so the
+// epilogue warps take few issue slots from the MMA and producer warps they share schedulers with.
+// Coefficients and their check (erf to 8e-8 absolute, GELU to 5e-7 at |x| = 6) come from
+// fit_erf_coefficients.py.
+__device__ __forceinline__ float erf_nodiv(float a) {
+    const float t = fminf(fabsf(a), 4.0f);
+    float r = fmaf(-4.477160110e-05f, t, 4.406937805e-04f);
+    r = fmaf(r, t, -1.474020537e-03f);
+    r = fmaf(r, t, -7.993229083e-04f);
+    r = fmaf(r, t, 2.827465348e-02f);
+    r = fmaf(r, t, -1.484908313e-01f);
+    r = fmaf(r, t, -9.184145331e-01f);
+    r = fmaf(r, t, -1.627908707e+00f);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(r * t));     // argument in [-25, 0]: no denormal result
+    return copysignf(1.0f - e, a);
+}
+__device__ __forceinline__ float gelu_erf(float x) {
+    const float h = 0.5f * x;
+    return fmaf(h, erf_nodiv(x * 0.70710678118f), h);
+}
+__device__ __forceinline__ uint32_t pack_bf16(uint32_t lo, uint32_t hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16(uint32_t lo, uint32_t hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+    return r;
+}
+__device__ __forceinline__ unsigned short f32_to_16(float v, uint32_t dtype16) {
+    if (dtype16 == (uint32_t)DT_BF16) {
+        uint32_t u = __float_as_uint(v);
+        if ((u & 0x7F800000u) == 0x7F800000u && (u & 0x007FFFFFu)) return (unsigned short)(0x7FC0u | ((u >> 16) & 1u));
+        u += 0x7FFFu + ((u >> 16) & 1u);
+        return (unsigned short)(u >> 16);
+    }
+    unsigned short h;
+    asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(v));
+    return h;
 }
 
 // Fused split-K reduction of one chunk (32 tile rows x `w` tile columns) by one warp: the K-slices
@@ -758,11 +809,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         const bool fused = p.splits > 1 && p.Cout != nullptr;
         const uint64_t pol_c = l2_policy((int)((p.l2_hints >> 4) & 3u));
+        const bool prof = (p.debug & 32u) != 0 && ew == 0;
+        long long te_wait = 0, te_ld = 0, te_math = 0, te_store = 0, last_e3 = 0;
         for (uint32_t u = u_begin; u < u_end && ok; u += u_step) {
             const WorkUnit w = listed ? load_unit(p.units + u) : decode_unit(p, u);
+            // Bias of a chunk: lane l holds bias[col + l], fetched one chunk ahead (the first one before the
+            // wait for the accumulator) and handed round by shuffles, so no chunk waits for a load.
+            auto bias_fetch = [&](uint32_t c) -> float {
+                const uint32_t bc = w.n_blk * BN + c * W + lane;
+                return (p.bias && c < CHUNKS && lane < W && bc < p.N) ? __ldg(p.bias + bc) : 0.0f;
+            };
+            float bias_next = bias_fetch(half);
+            long long e0 = prof ? clock64() : 0;
             ok = mbar_wait_patient(tmem_full_bar(acc), acc_phase, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
+            if (prof) te_wait += clock64() - e0;
             const uint32_t row0 = w.m_blk * BM_CTA * CG + cta_rank * BM_CTA + q * 32;  // first row of this warp
             const uint32_t col0 = w.n_blk * BN;
             const uint32_t zc = p.splits > 1 ? w.split : w.batch;
@@ -781,9 +843,83 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (col >= p.N || row0 >= p.M) break;   // nothing of this warp's slab is inside C
                 if (p.debug & 4u) break;
                 uint32_t v[32];
+                const float bias_cur = bias_next;
+                bias_next = bias_fetch(c + CSTEP);
+                long long e1 = prof ? clock64() : 0;
+                if (prof && last_e3) te_store += e1 - last_e3;
                 if constexpr (W == 32) tmem_ld32(taddr + c * W, v); else tmem_ld16(taddr + c * W, v);
                 tmem_ld_wait();
+                long long e2 = prof ? clock64() : 0;
                 if (p.debug & 2u) continue;
+                if (p.bias || p.act || p.c16) {
+                    // bias and activation on the f32 accumulators, in registers (no split/partial route reaches here)
+                    if (p.bias) {
+#pragma unroll
+                        for (uint32_t j = 0; j < W; ++j)
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + __shfl_sync(0xffffffffu, bias_cur, j));
+                    }
+                    if (p.act == 1) {
+#pragma unroll
+                        for (uint32_t j = 0; j < W; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
+                    } else if (p.act == 2) {
+#pragma unroll
+                        for (uint32_t j = 0; j < W; ++j) v[j] = __float_as_uint(gelu_erf(__uint_as_float(v[j])));
+                    }
+                    if (p.c16 && row < p.M) {
+                        unsigned short *d16 = p.c16 + (uint64_t)zc * p.M * p.ld16 + (uint64_t)row * p.ld16 + col;
+                        if (p.c16_vec && col + W <= p.N && row0 + 32 <= p.M) {
+                            // A lane's W values are W/8 16-byte pieces of its row.  Neighbouring lanes swap
+                            // every other piece, so that each store instruction writes whole 32-byte sectors:
+                            // the even lane's row in one instruction, the odd lane's row in the next.
+                            const bool odd = lane & 1u;
+                            unsigned short *pair_row = p.c16 + (uint64_t)zc * p.M * p.ld16 + (uint64_t)(row & ~1u) * p.ld16 + col;
+#pragma unroll
+                            for (uint32_t j = 0; j < W; j += 16) {
+                                uint4 lo, hi;           // pieces j/8 and j/8 + 1 of this lane's row
+                                if (p.dtype16 == (uint32_t)DT_BF16) {
+                                    lo = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                    pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+                                    hi = make_uint4(pack_bf16(v[j + 8], v[j + 9]), pack_bf16(v[j + 10], v[j + 11]),
+                                                    pack_bf16(v[j + 12], v[j + 13]), pack_bf16(v[j + 14], v[j + 15]));
+                                } else {
+                                    lo = make_uint4(pack_f16(v[j], v[j + 1]), pack_f16(v[j + 2], v[j + 3]),
+                                                    pack_f16(v[j + 4], v[j + 5]), pack_f16(v[j + 6], v[j + 7]));
+                                    hi = make_uint4(pack_f16(v[j + 8], v[j + 9]), pack_f16(v[j + 10], v[j + 11]),
+                                                    pack_f16(v[j + 12], v[j + 13]), pack_f16(v[j + 14], v[j + 15]));
+                                }
+                                uint4 give = odd ? lo : hi, got;
+                                got.x = __shfl_xor_sync(0xffffffffu, give.x, 1);
+                                got.y = __shfl_xor_sync(0xffffffffu, give.y, 1);
+                                got.z = __shfl_xor_sync(0xffffffffu, give.z, 1);
+                                got.w = __shfl_xor_sync(0xffffffffu, give.w, 1);
+                                // even row: even lane writes its lo, odd lane the even lane's hi
+                                *reinterpret_cast<uint4 *>(pair_row + j + (odd ? 8 : 0)) = odd ? got : lo;
+                                // odd row: even lane writes the odd lane's lo, odd lane its own hi
+                                *reinterpret_cast<uint4 *>(pair_row + p.ld16 + j + (odd ? 8 : 0)) = odd ? hi : got;
+                            }
+                        } else if (p.c16_vec && col + W <= p.N) {
+                            if (p.dtype16 == (uint32_t)DT_BF16) {
+#pragma unroll
+                                for (uint32_t j = 0; j < W; j += 8)
+                                    *reinterpret_cast<uint4 *>(d16 + j) =
+                                        make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                   pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+                            } else {
+#pragma unroll
+                                for (uint32_t j = 0; j < W; j += 8)
+                                    *reinterpret_cast<uint4 *>(d16 + j) =
+                                        make_uint4(pack_f16(v[j], v[j + 1]), pack_f16(v[j + 2], v[j + 3]),
+                                                   pack_f16(v[j + 4], v[j + 5]), pack_f16(v[j + 6], v[j + 7]));
+                            }
+                        } else {
+#pragma unroll
+                            for (uint32_t j = 0; j < W; ++j)
+                                if (col + j < p.N) d16[j] = f32_to_16(__uint_as_float(v[j]), p.dtype16);
+                        }
+                    }
+                }
+                long long e3 = prof ? clock64() : 0;
+                if (prof) { te_ld += e2 - e1; te_math += e3 - e2; last_e3 = e3; }
                 if (partial) {
                     // always in bounds: the slice holds the whole tile
                     float *d = ws_slice + (uint64_t)(lrow0 + lane) * BN + c * W;
@@ -843,6 +979,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
             // all TMEM reads of this accumulator are done: hand it back to the MMA issuer
+            if (prof && last_e3) { te_store += clock64() - last_e3; last_e3 = 0; }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -901,6 +1038,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
         if (lane == 0) tma_store_wait_all();
+        if (prof && lane == 0) {
+            unsigned long long *o = p.prof + (size_t)blockIdx.x * 16;
+            o[10] = (unsigned long long)te_wait; o[11] = (unsigned long long)te_ld;
+            o[12] = (unsigned long long)te_math; o[13] = (unsigned long long)te_store;
+        }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -1331,6 +1473,13 @@ int tc_gemm_launch(const TcGemm &g) {
     }
     p.C = g.C; p.ldc = g.ldc; p.c_stride = g.c_stride;
     p.c_trans = g.c_trans ? 1u : 0u;
+    p.bias = g.bias; p.act = (uint32_t)g.act; p.c16 = (unsigned short *)g.c16; p.ld16 = g.ld16; p.dtype16 = (uint32_t)g.dtype16;
+    p.bias_vec4 = aligned16(g.bias) ? 1u : 0u;
+    p.c16_vec = (g.c16 && aligned16(g.c16) && g.ld16 % 8 == 0) ? 1u : 0u;
+    if ((g.bias || g.act || g.c16) && (splits > 1 || g.c_trans || g.accumulate)) {
+        set_error("tc_gemm: the fused bias/activation epilogue does not combine with split-K, swapped operands or accumulate");
+        return ST_UNSUPPORTED;
+    }
     p.Cout = (splits > 1) ? g.Cout : nullptr; p.ldc_out = g.ldc_out; p.counters = g.counters;
     if (p.Cout) {
         const uint64_t slabs = (uint64_t)p.m_tiles * p.n_tiles * c.cg * c.ew;
@@ -1382,7 +1531,7 @@ int tc_gemm_launch(const TcGemm &g) {
     if (units > 0xFFFFFFFFull) return ST_UNSUPPORTED;
     uint32_t clusters = (uint32_t)(units < (uint64_t)rt.max_clusters ? units : (uint64_t)rt.max_clusters);
     bool stream_k = false;
-    if (g.allow_stream_k && p.splits == 1 && p.npass == 1 && !p.c_trans && g.counters && c.bn >= 32 && !(p.debug & 31u)) {
+    if (g.allow_stream_k && !g.bias && !g.act && !g.c16 && p.splits == 1 && p.npass == 1 && !p.c_trans && g.counters && c.bn >= 32 && !(p.debug & 31u)) {
         const SkPlan *plan = stream_k_plan(p, c, cfg, (uint32_t)rt.max_clusters, g.stream);
         if (plan && (uint64_t)plan->ws_tiles * c.cg * c.ew <= g.num_counters) {
             p.units = plan->d_units; p.unit_start = plan->d_start; p.ws = g_sk_ws; p.counters = g.counters;

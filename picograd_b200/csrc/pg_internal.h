@@ -47,6 +47,8 @@ struct TcGemm {
     float *C;
     uint64_t ldc, c_stride;    // elements; c_stride between batch elements (or split-K slices)
     int accumulate;            // C += A*B instead of C = A*B
+    // fused epilogue: C = act(A*B + bias[col]) and an optional 16-bit copy of C ([batch][M][ld16])
+    const float *bias; int act; uint16_t *c16; uint64_t ld16; int dtype16;
     int c_trans;               // store the tile transposed: element (row, col) -> C[col*ldc + row]
     // splits > 1 with Cout set: C holds the K-slices and the kernel itself sums them into Cout
     float *Cout;
@@ -84,6 +86,8 @@ struct SimtGemm {
     const void *B; int64_t b_rs, b_cs, b_bs;   // row (k), column (n), batch
     float *C; int64_t ldc, c_bs;
     int accumulate;            // C += instead of C =
+    const float *bias; int act;   // fused epilogue: the chain of column j starts at bias[j]; act applied at the store
+    uint16_t *c16; int64_t ld16; int dtype16;
     cudaStream_t stream;
 };
 int simt_gemm_launch(const SimtGemm &g);
@@ -104,6 +108,8 @@ int gelu_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
 int gelu_grad_launch(const float *x, const float *gy, float *out, uint64_t n, cudaStream_t s);
 int softmax_rows_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
                         uint64_t rows, uint32_t len, cudaStream_t s);
+int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, uint16_t *c16, uint64_t ld16, int dtype16,
+                    uint64_t rows, uint64_t n, cudaStream_t s);
 int fill_f32_launch(float *dst, float v, uint64_t n, cudaStream_t s);
 
 void set_error(const char *fmt, ...);

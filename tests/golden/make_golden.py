@@ -9,8 +9,10 @@ pg_gemm / pg_gemm_ex on small seeded inputs and stores inputs' seeds + outputs. 
 The host CPU matters for one case: on AVX512-FP16 hosts picograd's f16 micro-kernel
 (backend/cpu/hgemm_avx512fp16.c:31-41) resets the accumulators of columns 0..15 of every
 32-column block at each 256-deep K block, so for K > 256 only columns 16..31 (mod 32) of its
-f16 output are an f32 accumulation over all of K.  `f16_valid_cols` records which columns of
-each f16 case are usable as golden values on the host that generated the file.
+f16 output are an f32 accumulation over all of K.  In pg_cpu_gemm_fused_ex the same reset throws
+away the bias row those columns were initialised with, whatever K is.  `<case>_valid_cols`
+records which columns of each f16 case are usable as golden values on the host that generated
+the file.
 """
 import os
 import sys
@@ -35,6 +37,24 @@ CASES = [
     ("f16_40x72x256", wl.F16, 40, 72, 256, 31),
     ("f16_64x96x600", wl.F16, 64, 96, 600, 32),
 ]
+
+
+# pg_cpu_gemm_fused_ex (backend/cpu/gemm.c:718-817): (name, dtype, m, n, k, seed, with_bias, act).
+# f16 cases keep K <= 256 so that the accumulator reset described above cannot touch them.
+FUSED_CASES = [
+    ("fused_f32_13x9x7_bias_none", wl.F32, 13, 9, 7, 40, True, 0),
+    ("fused_f32_37x53x300_bias_relu", wl.F32, 37, 53, 300, 41, True, 1),
+    ("fused_f32_37x53x300_bias_gelu", wl.F32, 37, 53, 300, 42, True, 2),
+    ("fused_f32_24x40x64_nobias_relu", wl.F32, 24, 40, 64, 43, False, 1),
+    ("fused_bf16_40x72x520_bias_relu", wl.BF16, 40, 72, 520, 44, True, 1),
+    ("fused_bf16_40x72x520_bias_gelu", wl.BF16, 40, 72, 520, 45, True, 2),
+    ("fused_f16_40x72x256_bias_relu", wl.F16, 40, 72, 256, 46, True, 1),
+    ("fused_f16_13x48x7_bias_none", wl.F16, 13, 48, 7, 47, True, 0),
+]
+
+
+def make_bias(n, seed):
+    return np.random.default_rng(seed + 1000).uniform(-1, 1, n).astype(np.float32)
 
 
 def make_inputs(dtype, m, n, k, seed):
@@ -62,6 +82,20 @@ def main():
             exact = wl.f16_bits_to_f32(a).astype(np.float64) @ wl.f16_bits_to_f32(b).astype(np.float64)
             good = np.abs(c - exact).max(axis=0) < 1e-3
             out[name + "_valid_cols"] = good
+    for name, dt, m, n, k, seed, with_bias, act in FUSED_CASES:
+        a, b = make_inputs(dt, m, n, k, seed)
+        bias = make_bias(n, seed) if with_bias else None
+        out[name] = ref.gemm_fused_ex(dt, a, b, bias, act)
+        if dt == wl.F16:
+            # the same accumulator reset also drops the bias row the kernel should have started from
+            exact = wl.f16_bits_to_f32(a).astype(np.float64) @ wl.f16_bits_to_f32(b).astype(np.float64)
+            exact = exact + (bias if with_bias else 0.0)
+            if act == 1:
+                exact = np.maximum(exact, 0)
+            out[name + "_valid_cols"] = np.abs(out[name] - exact).max(axis=0) < 1e-3
+    # the f32 entry nn/nn.c:60,85 calls (Linear forward with and without ReLU)
+    a, b = make_inputs(wl.F32, 20, 33, 300, 48)
+    out["fused_f32_plain_entry_relu"] = ref.gemm_fused_ex(wl.F32, a, b, make_bias(33, 48), 1, plain_f32_entry=True)
     # picograd's own dyadic correctness data (benchmarks/bench_gemm_cuda.c:16-65), exact in f32
     s = 64
     d = wl.dyadic(s * s).reshape(s, s)

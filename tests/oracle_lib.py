@@ -26,6 +26,7 @@ class Oracle:
         self.L = L
         L.pgo_gemm_ex.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]
         L.pgo_gemm_ex_panel.argtypes = L.pgo_gemm_ex.argtypes + [_sz] * 4
+        L.pgo_gemm_fused_ex.argtypes = L.pgo_gemm_ex.argtypes + [_vp, C.c_int]
         L.pgo_bmm.argtypes = [C.c_int, _sz, _sz, _sz, _sz, _vp, _vp, _vp]
         L.pgo_matmul_backward.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp]
         L.pgo_softmax_rows.argtypes = [_vp, _vp, _sz, _sz]
@@ -51,6 +52,16 @@ class Oracle:
         else:
             ldc = c.strides[0] // 4
         self.L.pgo_gemm_ex(dtype, m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), ldc)
+        return c
+
+    def gemm_fused_ex(self, dtype, a, b, bias=None, act=0):
+        """C = act(bias + a @ b), picograd's pg_cpu_gemm_fused_ex; bias f32 [n] or None."""
+        m, k = a.shape
+        n = b.shape[1]
+        c = np.zeros((m, n), np.float32)
+        self.L.pgo_gemm_fused_ex(dtype, m, n, k, _ptr(a), max(a.strides[0] // a.itemsize, 1), _ptr(b),
+                                 b.strides[0] // b.itemsize, _ptr(c), n,
+                                 _ptr(bias) if bias is not None else None, act)
         return c
 
     def gemm_ex_panel(self, dtype, a, b, r0, r1, c0, c1):
@@ -133,9 +144,25 @@ class Reference:
         L.pg_gemm.argtypes = [_sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]
         L.pg_gemm_ex.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz]
         L.pg_thread_pool_size.restype = C.c_int
+        L.pg_cpu_gemm_fused.argtypes = L.pg_gemm.argtypes + [_vp, C.c_int]
+        L.pg_cpu_gemm_fused_ex.argtypes = L.pg_gemm_ex.argtypes + [_vp, C.c_int]
 
     def threads(self):
         return int(self.L.pg_thread_pool_size())
+
+    def gemm_fused_ex(self, dtype, a, b, bias=None, act=0, plain_f32_entry=False):
+        """backend/cpu/gemm.c:685-817; plain_f32_entry calls pg_cpu_gemm_fused (what nn/nn.c:60 uses)."""
+        m, k = a.shape
+        n = b.shape[1]
+        c = np.full((m, n), np.nan, np.float32)
+        lda, ldb = max(a.strides[0] // a.itemsize, 1), b.strides[0] // b.itemsize
+        bp = _ptr(bias) if bias is not None else None
+        if plain_f32_entry:
+            assert dtype == F32
+            self.L.pg_cpu_gemm_fused(m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), n, bp, act)
+        else:
+            self.L.pg_cpu_gemm_fused_ex(dtype, m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), n, bp, act)
+        return c
 
     def gemm_ex(self, dtype, a, b, c=None):
         m, k = a.shape

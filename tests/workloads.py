@@ -91,6 +91,10 @@ def dyadic(n):
     return (((i * 37 + 11) % 19).astype(np.float32) - 9.0) / 8.0
 
 
+def seeded_uniform(rows, cols, seed, lo=-1.0, hi=1.0):
+    return np.random.default_rng(seed).uniform(lo, hi, (rows, cols)).astype(np.float32)
+
+
 def tolerance(dtype, k):
     """Normwise relative error bound: 1e-6 for f32, 1e-5*sqrt(K) for f16/bf16."""
     return 1e-6 if dtype == F32 else 1e-5 * float(np.sqrt(max(k, 1)))
