@@ -120,6 +120,17 @@ PG_B200_API int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_
                             const void *a, const void *b, int b_batched,
                             const float *g, float *ga, float *gb);
 
+/* The attention-shaped chain of picograd calls as ONE entry: O = 16bit(softmax_rows(Q * Kt)) * V, i.e.
+ * pg_bmm (ops/matmul.c:340-369) -> pg_softmax over the last axis (ops/activations.c:22-45) -> cast to the
+ * operand dtype -> pg_bmm.  q [batch, seq_q, d], kt [batch, d, seq_k], v [batch, seq_k, d] in `dtype`
+ * (f16/bf16), contiguous, device pointers; o [batch, seq_q, d] f32.  No scaling and no mask: the chain has
+ * none.  For d == 128 and 16-byte aligned operands one kernel does all of it and the f32 scores and the
+ * 16-bit probabilities never reach device memory (P is still rounded to 16 bits after the division by the
+ * row sum, as the chain does, so the result equals the chain's to rounding noise); other shapes run the
+ * chain with the library's own kernels.  pg_b200_last_path() says which ("attn:fused_128x128" / "attn:chain"). */
+PG_B200_API int pg_b200_attention_bmm(int dtype, size_t batch, size_t seq_q, size_t seq_k, size_t d,
+                          const void *q, const void *kt, const void *v, float *o);
+
 /* Harness steps between the GEMMs of the attention-shaped and MLP workloads
  * (ops/activations.c:22-45 softmax rows, :114 GELU, autograd.c:794-801 GELU
  * gradient), so that those workloads stay on the device.  out16 (optional)

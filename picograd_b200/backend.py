@@ -150,6 +150,26 @@ def pg_linear_forward(x, weight, bias=None, relu=False, out16=None):
     return out
 
 
+def pg_attention_bmm(q, kt, v):
+    """softmax-weighted product as picograd's callers chain it: pg_bmm(q, kt) -> pg_softmax(axis -1) ->
+    cast to the operand dtype -> pg_bmm(., v) (ops/matmul.c:340-369, ops/activations.c:22-45), in one call.
+    q [B,Sq,D], kt [B,D,Sk], v [B,Sk,D] f16/bf16 device tensors; returns f32 [B,Sq,D]."""
+    _ready()
+    if q.dim() != 3 or kt.dim() != 3 or v.dim() != 3:
+        raise ValueError("pg_attention_bmm: 3-D operands")
+    bt, sq, d = q.shape
+    if kt.shape[0] != bt or kt.shape[1] != d or v.shape != (bt, kt.shape[2], d) or not (q.dtype == kt.dtype == v.dtype):
+        raise ValueError("pg_attention_bmm: q [B,Sq,D], kt [B,D,Sk], v [B,Sk,D] of one dtype")
+    dt = {torch.float16: PG_DTYPE_F16, torch.bfloat16: PG_DTYPE_BF16}.get(q.dtype)
+    if dt is None:
+        raise TypeError("pg_attention_bmm: float16 or bfloat16")
+    q, kt, v = q.contiguous(), kt.contiguous(), v.contiguous()
+    o = torch.empty((bt, sq, d), dtype=torch.float32, device=q.device)
+    _check(lib.pg_b200_attention_bmm(dt, bt, sq, kt.shape[2], d, q.data_ptr(), kt.data_ptr(), v.data_ptr(), o.data_ptr()),
+           "pg_attention_bmm")
+    return o
+
+
 def pg_gemm_ex_host(dtype, m, n, k, a, lda, b, ldb, c, ldc):
     """pg_gemm_ex with HOST buffers, the way ops/matmul.c:264-271 calls it: a, b, c are CPU
     tensors (pinned or pageable) or numpy arrays; staging copies happen inside the call."""

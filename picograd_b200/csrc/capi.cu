@@ -40,6 +40,8 @@ struct State {
     int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
     int opt_host_pipeline = 1;   // host-pointer pg_gemm_ex: overlap copies and GEMMs block by block
     int opt_fused_splitk = 1;    // split-K slices summed by the GEMM kernel itself (else a second kernel)
+    int opt_fused_attention = 1; // 0: pg_b200_attention_bmm always runs the three-kernel chain
+    DeviceBuf attn_ws;           // S and P of the chain form of pg_b200_attention_bmm
     int opt_stream_k = 0;        // stream-K for a partly filled last wave: correct, but measured 5-20 % slower
                                  // than the plain schedule on B200 (partial waves already run faster), so off
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
@@ -786,6 +788,40 @@ int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t 
     return st;
 }
 
+int pg_b200_attention_bmm(int dtype, size_t batch, size_t seq_q, size_t seq_k, size_t d, const void *q, const void *kt,
+                          const void *v, float *o) {
+    if (!ready()) return g.init_status;
+    if (dtype != DT_F16 && dtype != DT_BF16) { set_error("pg_b200_attention_bmm: f16 or bf16 operands"); return ST_UNSUPPORTED; }
+    if (batch == 0 || seq_q == 0 || d == 0) return ST_OK;
+    if (seq_k == 0) { set_error("pg_b200_attention_bmm: softmax over an empty row"); return ST_UNSUPPORTED; }
+    if (!q || !kt || !v || !o) { set_error("null operand"); return ST_GEMM; }
+    if (g.opt_fused_attention && batch <= 0x7FFFFFu && seq_q <= 0x7FFFFFFFu && seq_k <= 0x7FFFFFFFu) {
+        AttnProblem a = {};
+        a.dtype = dtype; a.batch = (uint32_t)batch; a.sq = (uint32_t)seq_q; a.sk = (uint32_t)seq_k; a.d = (uint32_t)d;
+        a.q = q; a.ldq = d; a.q_stride = seq_q * d;
+        a.kt = kt; a.ldk = seq_k; a.k_stride = d * seq_k;
+        a.v = v; a.ldv = d; a.v_stride = seq_k * d;
+        a.o = o; a.ldo = d; a.o_stride = seq_q * d;
+        a.stream = g.stream; a.dev_status = g.dev_status;
+        const int st = attn_fused_launch(a);
+        if (st != ST_UNSUPPORTED) return st;
+    }
+    // the chain, as picograd's callers would run it: pg_bmm, softmax rows + cast, pg_bmm
+    const size_t s_bytes = align_up(batch * seq_q * seq_k * 4, 256), p_bytes = align_up(batch * seq_q * seq_k * 2, 256);
+    int st = grow(g.attn_ws, s_bytes + p_bytes);
+    if (st != ST_OK) return st;
+    float *S = (float *)g.attn_ws.ptr;
+    uint16_t *P = (uint16_t *)((char *)g.attn_ws.ptr + s_bytes);
+    Problem p1 = {dtype, dtype, 0, 0, batch, seq_q, seq_k, d, q, d, seq_q * d, kt, seq_k, d * seq_k, S, seq_k, seq_q * seq_k, 0};
+    if ((st = run_problem(p1)) != ST_OK) return st;
+    if (seq_k > 0xFFFFFFFFull) return ST_UNSUPPORTED;
+    if ((st = softmax_rows_launch(S, nullptr, P, dtype, batch * seq_q, (uint32_t)seq_k, g.stream)) != ST_OK) return st;
+    Problem p2 = {dtype, dtype, 0, 0, batch, seq_q, d, seq_k, P, seq_k, seq_q * seq_k, v, d, seq_k * d, o, d, seq_q * d, 0};
+    if ((st = run_problem(p2)) != ST_OK) return st;
+    set_last_path("attn:chain");
+    return ST_OK;
+}
+
 int pg_b200_softmax_rows(const float *src, float *out_f32, uint16_t *out16, int dtype16, size_t rows, size_t len) {
     if (!ready()) return g.init_status;
     if (len > 0xFFFFFFFFull) return ST_UNSUPPORTED;
@@ -840,6 +876,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "host_pipeline")) { g.opt_host_pipeline = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "fused_splitk")) { g.opt_fused_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "swap_skinny")) { g.opt_swap_skinny = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "fused_attention")) { g.opt_fused_attention = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);

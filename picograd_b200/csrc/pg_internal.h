@@ -78,6 +78,21 @@ int tc_num_configs();
 const char *tc_config_name(int cfg);
 int tc_config_index(const char *name);   // -1 if unknown
 
+// Q Kt -> softmax -> 16-bit P -> P V in one kernel (attn_tc.cu).  Q [b][sq][d], Kt [b][d][sk], V [b][sk][d]
+// in `dtype` (f16/bf16), O [b][sq][d] f32; leading dimensions and batch strides in elements.
+// ST_UNSUPPORTED when d != 128 or an operand breaks the TMA alignment rules.
+struct AttnProblem {
+    int dtype;
+    uint32_t batch, sq, sk, d;
+    const void *q; uint64_t ldq, q_stride;
+    const void *kt; uint64_t ldk, k_stride;
+    const void *v; uint64_t ldv, v_stride;
+    float *o; uint64_t ldo, o_stride;
+    cudaStream_t stream;
+    uint32_t *dev_status;
+};
+int attn_fused_launch(const AttnProblem &a);
+
 // Generic FFMA fallback: any dtype (per operand), any strides.
 struct SimtGemm {
     int dtype_a, dtype_b;      // DT_*

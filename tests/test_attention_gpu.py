@@ -1,0 +1,95 @@
+"""pg_b200_attention_bmm: the chain pg_bmm -> pg_softmax -> cast -> pg_bmm (ops/matmul.c:340-369,
+ops/activations.c:22-45) as one call, against the CPU oracle running the chain step by step.
+
+The fused kernel rounds P to 16 bits after the division by the row sum, as the chain does, so its O
+differs from the chain's only where a last-bit difference in S or exp() flips a 16-bit rounding of P:
+far inside the tolerance of the second product (1e-5 * sqrt(Sk))."""
+import numpy as np
+import pytest
+import torch
+
+import workloads as wl
+from gpu_util import to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def e2e_tolerance(dt, sk):
+    """End-to-end bound for the whole chain.  Each product alone meets 1e-5 * sqrt(K) on identical input bytes
+    (tests/test_gemm_gpu.py).  End to end, a last-bit difference in a score or in exp() can flip the 16-bit
+    rounding of an element of P by one unit (2^-8 relative for bf16, 2^-11 for f16); a small fraction of the
+    elements does, which adds about a quarter of that unit to the normwise error of O."""
+    eps16 = 2.0 ** -8 if dt == wl.BF16 else 2.0 ** -11
+    return max(wl.tolerance(dt, sk), 0.25 * eps16)
+
+
+def make_qkv(bt, sq, sk, d, dt, seed):
+    rng = np.random.default_rng(seed)
+    conv = wl.to_bf16_bits if dt == wl.BF16 else wl.to_f16_bits
+    s = 1.0 / np.sqrt(np.sqrt(d))        # scores ~ N(0, 1), as in picograd's attention-shaped configuration
+    q = conv((rng.standard_normal((bt, sq, d)) * s).astype(np.float32))
+    kt = conv((rng.standard_normal((bt, d, sk)) * s).astype(np.float32))
+    v = conv(rng.standard_normal((bt, sk, d)).astype(np.float32))
+    return q, kt, v
+
+
+def oracle_chain(oracle, dt, q, kt, v):
+    s = oracle.bmm(dt, q, kt)
+    p = oracle.softmax_rows(s)
+    # IEEE round-to-nearest-even (picograd's own f32->f16 converter mishandles subnormals, core/convert.h:33-44,
+    # and small probabilities are subnormal in f16)
+    p16 = wl.to_bf16_bits(p) if dt == wl.BF16 else wl.to_f16_bits(p)
+    return oracle.bmm(dt, p16, v)
+
+
+@pytest.mark.parametrize("dt", [wl.BF16, wl.F16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(2, 256, 256), (1, 128, 128), (3, 200, 328), (1, 50, 104), (2, 384, 1152), (1, 130, 2048)],
+                         ids=["even", "one-block", "ragged", "tiny", "odd-block-count", "long-row"])
+def test_fused_equals_the_chain_on_the_cpu(pg, oracle, dt, shape):
+    bt, sq, sk = shape
+    q, kt, v = make_qkv(bt, sq, sk, 128, dt, 90)
+    want = oracle_chain(oracle, dt, q, kt, v)
+    got = pg.pg_attention_bmm(to_dev(q, dt), to_dev(kt, dt), to_dev(v, dt))
+    pg.pg_dev_sync()
+    assert pg.last_path() == "attn:fused_128x128"
+    assert wl.relerr(got.cpu().numpy(), want) <= e2e_tolerance(dt, sk)
+
+
+def test_many_units_per_cta_and_both_paths_agree(pg):
+    """More work units than SMs (each CTA loops) and odd counts everywhere; the chain form of the same
+    entry (the library's own three kernels) is the second opinion."""
+    bt, sq, sk = 5, 4096 + 77, 640 + 8
+    q, kt, v = make_qkv(bt, sq, sk, 128, wl.BF16, 91)
+    qd, ktd, vd = to_dev(q, wl.BF16), to_dev(kt, wl.BF16), to_dev(v, wl.BF16)
+    fused = pg.pg_attention_bmm(qd, ktd, vd); pg.pg_dev_sync()
+    assert pg.last_path() == "attn:fused_128x128"
+    pg.set_option("fused_attention", 0)
+    chain = pg.pg_attention_bmm(qd, ktd, vd); pg.pg_dev_sync()
+    pg.set_option("fused_attention", 1)
+    assert pg.last_path() == "attn:chain"
+    assert wl.relerr(fused.cpu().numpy(), chain.cpu().numpy()) <= e2e_tolerance(wl.BF16, sk)
+    # rows of P sum to one: with V all ones every output is 1 up to the 16-bit rounding of P
+    ones = torch.ones_like(vd)
+    o = pg.pg_attention_bmm(qd, ktd, ones); pg.pg_dev_sync()
+    assert (o - 1.0).abs().max().item() < 4e-3
+
+
+@pytest.mark.parametrize("shape", [(2, 96, 160, 64), (2, 96, 333, 128)], ids=["d64", "keys-not-multiple-of-8"])
+def test_shapes_the_fused_kernel_does_not_take_run_the_chain(pg, oracle, shape):
+    bt, sq, sk, d = shape
+    q, kt, v = make_qkv(bt, sq, sk, d, wl.BF16, 92)
+    want = oracle_chain(oracle, wl.BF16, q, kt, v)
+    got = pg.pg_attention_bmm(to_dev(q, wl.BF16), to_dev(kt, wl.BF16), to_dev(v, wl.BF16)); pg.pg_dev_sync()
+    assert pg.last_path() == "attn:chain"
+    assert wl.relerr(got.cpu().numpy(), want) <= e2e_tolerance(wl.BF16, sk)
+
+
+def test_large_scores_do_not_overflow(pg, oracle):
+    """Row maxima far from zero: the subtraction of the maximum happens before the exponential."""
+    bt, sq, sk = 1, 128, 256
+    q, kt, v = make_qkv(bt, sq, sk, 128, wl.BF16, 93)
+    q = wl.to_bf16_bits(wl.bf16_bits_to_f32(q) * 16.0)
+    want = oracle_chain(oracle, wl.BF16, q, kt, v)
+    got = pg.pg_attention_bmm(to_dev(q, wl.BF16), to_dev(kt, wl.BF16), to_dev(v, wl.BF16)); pg.pg_dev_sync()
+    assert np.isfinite(got.cpu().numpy()).all()
+    assert wl.relerr(got.cpu().numpy(), want) <= e2e_tolerance(wl.BF16, sk)
