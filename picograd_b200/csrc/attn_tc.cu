@@ -16,13 +16,19 @@
 // S and the 0.5 GiB write and read of P at picograd's attention-shaped configuration (B=64, Sq=Sk=2048,
 // D=128).  The kernel is bound by the exponentials (two per element of S), not by HBM or the MMAs.
 //
-// Roles (320 threads, one CTA per SM, persistent over (batch, 128-row query block) units):
-//   warp 0      TMA producer: Q (double-buffered) and a ring of 16 KB slots, each a [64 x 128] slice of
-//               Kt or V as an MN-major B operand, in exactly the order the MMA warp consumes them
-//   warp 1      MMA issuer: S = Q Kt_blk into one of two TMEM buffers; O += P V_blk into a third
+// Roles (384 threads, one CTA per SM, persistent over (batch, 128-row query block) units).  The softmax
+// warps keep the schedulers busy, so whatever else runs on them must be a short instruction stream: the two
+// kinds of product have an issuing warp each, and so have their operands.
+//   warp 0      K producer: Q, then the 128 x 128 blocks of Kt into a two-entry ring (TMA, MN-major B operand)
+//   warp 11     V producer: the 128 x 128 blocks of V into a two-entry ring
+//   warp 1      S issuer: S[e] = Q Kt_blk into one of two TMEM buffers (8 MMAs, one commit)
+//   warp 10     PV issuer: O += P[pb] V_blk into a third TMEM buffer
 //   warps 2-5   softmax group 0, warps 6-9 group 1: the groups take alternate S buffers; a thread owns one
-//               query row (TMEM lane), reads its 128 scores with tcgen05.ld, and in pass 2 writes its row
-//               of P into the 128-byte-swizzled K-major layout the MMA reads
+//               query row (TMEM lane), pulls its 128 scores into registers with tcgen05.ld, hands the buffer
+//               straight back, and in pass 2 writes its row of P into the 128-byte-swizzled K-major layout
+//               the MMA reads.  In pass 2 the S products run ahead of the P V products by themselves.
+// Ring entry e of Kt belongs to S buffer e and ring entry pb of V to P tile pb, so "entry free again" is the
+// same event as "product completed" (s_full / p_empty): one commit per product.
 // All waits are bounded mbarrier waits (status word + CTA abort flag), no named barriers.
 
 #include "pg_internal.h"
@@ -34,12 +40,14 @@ constexpr uint32_t AT_ROWS = 128;                 // query rows per unit == TMEM
 constexpr uint32_t AT_KEYS = 128;                 // keys per block
 constexpr uint32_t AT_D = 128;                    // head dimension
 constexpr uint32_t AT_ATOM = 128 * 64 * 2;        // [128 rows x 64 elements] K-major, or [64 k x 128 n] MN-major
-constexpr uint32_t AT_SLOTS = 6;
+constexpr uint32_t AT_ENTRY = 2 * AT_ATOM;        // one ring entry: a 128 x 128 block of Kt or V
+constexpr uint32_t AT_ENTRIES = 4;
+constexpr uint32_t AT_SLOTS = AT_ENTRIES;         // (barrier pairs of the ring)
 constexpr uint32_t AT_Q_BYTES = 2 * AT_ATOM;      // one Q tile (two d-halves)
 constexpr uint32_t AT_P_BYTES = 2 * AT_ATOM;      // one P tile (two key-halves)
 constexpr uint32_t AT_BAR_BYTES = 1024;
-constexpr uint32_t AT_SMEM = 1024 + 2 * AT_Q_BYTES + 2 * AT_P_BYTES + AT_SLOTS * AT_ATOM + AT_BAR_BYTES;
-constexpr uint32_t AT_THREADS = 320;
+constexpr uint32_t AT_SMEM = 1024 + AT_Q_BYTES + 2 * AT_P_BYTES + AT_ENTRIES * AT_ENTRY + AT_BAR_BYTES;
+constexpr uint32_t AT_THREADS = 384;
 constexpr uint32_t AT_TMEM_COLS = 512;            // S0 at 0, S1 at 128, O at 256
 static_assert(AT_SMEM <= 232448, "shared memory budget");
 
@@ -51,6 +59,8 @@ struct AttnParams {
     float *O;
     uint64_t ldo, o_stride;       // elements
     uint32_t *status;
+    unsigned long long *prof;     // timing experiments: 16 cycle counters per CTA (may be null)
+    uint32_t debug;               // timing experiments (results are garbage): 1 = no TMA loads, 16 = no MMAs
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -71,6 +81,86 @@ __device__ __forceinline__ uint32_t at_pack16(float lo, float hi, uint32_t dtype
     else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// Waits for this thread's outstanding tcgen05.ld and ties the wait to the registers just loaded, so that the
+// compiler cannot schedule arithmetic on them above it (loads of the next chunk are issued before the
+// arithmetic of the current one).
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&v)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                   "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                   "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+                   "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+#define AT_F(i) __uint_as_float(v[i])
+// Columns col0 .. col0+31 of a block whose first `valid` columns exist: the others count as -inf.
+__device__ __forceinline__ void at_mask(uint32_t (&v)[32], uint32_t col0, uint32_t valid) {
+#pragma unroll
+    for (uint32_t j = 0; j < 32; ++j)
+        if (col0 + j >= valid) v[j] = __float_as_uint(-INFINITY);
+}
+// Pass 1 pieces on 32 scores of a row: their maximum, and the sum of 2^(s log2 e + nmc).
+__device__ __forceinline__ float at_max32(const uint32_t (&v)[32]) {
+    float a[10];
+#pragma unroll
+    for (uint32_t k = 0; k < 10; ++k) a[k] = fmax3(AT_F(3 * k), AT_F(3 * k + 1), AT_F(3 * k + 2));
+    const float r0 = fmax3(a[0], a[1], a[2]), r1 = fmax3(a[3], a[4], a[5]), r2 = fmax3(a[6], a[7], a[8]);
+    return fmax3(fmax3(r0, r1, r2), fmax3(a[9], AT_F(30), AT_F(31)), -INFINITY);
+}
+__device__ __forceinline__ float at_sum32(const uint32_t (&v)[32], float nmc) {
+    const float LOG2E = 1.4426950408889634f;
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+    for (uint32_t j = 0; j < 32; j += 4) {
+        s0 += ex2_approx(fmaf(AT_F(j), LOG2E, nmc));
+        s1 += ex2_approx(fmaf(AT_F(j + 1), LOG2E, nmc));
+        s2 += ex2_approx(fmaf(AT_F(j + 2), LOG2E, nmc));
+        s3 += ex2_approx(fmaf(AT_F(j + 3), LOG2E, nmc));
+    }
+    return (s0 + s1) + (s2 + s3);
+}
+// Pass 2 on 32 scores: p = 2^(s log2 e + off) with off = -(M log2 e + log2 L), i.e. exp(s - M) / L, rounded to
+// 16 bits and written as four 16-byte pieces of the row's 128-byte line of the swizzled P tile.
+__device__ __forceinline__ void at_probs32(const uint32_t (&v)[32], float off, uint32_t dtype, uint8_t *line,
+                                           uint32_t first_piece, uint32_t row7) {
+    const float LOG2E = 1.4426950408889634f;
+    uint32_t w[16];
+#pragma unroll
+    for (uint32_t j = 0; j < 32; j += 2)
+        w[j >> 1] = at_pack16(ex2_approx(fmaf(AT_F(j), LOG2E, off)), ex2_approx(fmaf(AT_F(j + 1), LOG2E, off)), dtype);
+#pragma unroll
+    for (uint32_t jj = 0; jj < 4; ++jj)
+        *reinterpret_cast<uint4 *>(line + (((first_piece + jj) ^ row7) << 4)) =
+            make_uint4(w[4 * jj], w[4 * jj + 1], w[4 * jj + 2], w[4 * jj + 3]);
+}
+#undef AT_F
+
+#ifndef PG_ATTN_HINT_NS
+#define PG_ATTN_HINT_NS 32
+#endif
+// every hand-over in this kernel is latency-critical: short suspend hint
+__device__ __forceinline__ bool at_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t *status,
+                                        uint32_t err_bit) {
+    return mbar_wait_quick(bar, parity, abort_flag, status, err_bit, PG_ATTN_HINT_NS);
+}
+
+// Timing experiments (debug bit 64): CTA 0 records (tag << 32 | low 32 bits of the clock) into the counter
+// buffer from entry 2400 on, 1400 entries per role (S issuer, softmax group 0, group 1, PV issuer), plain stores.
+__device__ __forceinline__ void at_trace(const AttnParams &p, uint32_t role, uint32_t &n, uint32_t tag) {
+    if ((p.debug & 64u) && p.prof && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && n < 1400)
+        p.prof[2400 + role * 1400 + n++] = ((unsigned long long)tag << 32) | (unsigned long long)(uint32_t)clock64();
+}
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kt,
@@ -79,14 +169,14 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const uint32_t q_base = smem_base;                                   // 2 x 32 KB
-    const uint32_t p_base = q_base + 2 * AT_Q_BYTES;                     // 2 x 32 KB
-    const uint32_t ring_base = p_base + 2 * AT_P_BYTES;                  // AT_SLOTS x 16 KB
-    const uint32_t bar_base = ring_base + AT_SLOTS * AT_ATOM;
+    const uint32_t q_base = smem_base;                                   // 32 KB
+    const uint32_t p_base = q_base + AT_Q_BYTES;                         // 2 x 32 KB
+    const uint32_t ring_base = p_base + 2 * AT_P_BYTES;                  // AT_ENTRIES x 32 KB
+    const uint32_t bar_base = ring_base + AT_ENTRIES * AT_ENTRY;
     uint32_t nb = 0;
     auto take = [&](uint32_t n) { uint32_t b = bar_base + 8u * nb; nb += n; return b; };
-    const uint32_t full0 = take(AT_SLOTS), empty0 = take(AT_SLOTS);
-    const uint32_t q_full0 = take(2), q_empty0 = take(2);
+    const uint32_t kfull0 = take(2), vfull0 = take(2);
+    const uint32_t q_full0 = take(1), q_empty0 = take(1);
     const uint32_t s_full0 = take(2), s_empty0 = take(2);
     const uint32_t p_full0 = take(2), p_empty0 = take(2);
     const uint32_t o_full = take(1), o_empty = take(1);
@@ -95,7 +185,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t abort_off = (take(1) - smem_base);
     volatile uint32_t *tmem_slot_gen = (volatile uint32_t *)(smem_gen + (tmem_slot - smem_base));
     volatile uint32_t *abort_flag = (volatile uint32_t *)(smem_gen + abort_off);
-    static_assert(8 * (2 * AT_SLOTS + 7 * 2 + 2 + 2) <= AT_BAR_BYTES, "barrier block");
+    static_assert(8 * (4 + 5 * 2 + 2 + 2 + 2) <= AT_BAR_BYTES, "barrier block");
 
     const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const uint32_t lane = threadIdx.x & 31;
@@ -107,9 +197,10 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         prefetch_tmap(&map_q);
         prefetch_tmap(&map_kt);
         prefetch_tmap(&map_v);
-        for (uint32_t s = 0; s < AT_SLOTS; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (uint32_t s = 0; s < 2; ++s) { mbar_init(kfull0 + 8 * s, 1); mbar_init(vfull0 + 8 * s, 1); }
+        mbar_init(q_full0, 1);
+        mbar_init(q_empty0, 1);
         for (uint32_t s = 0; s < 2; ++s) {
-            mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1);
             mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 4);
             mbar_init(p_full0 + 8 * s, 4); mbar_init(p_empty0 + 8 * s, 1);
             mbar_init(stat0 + 8 * s, 8);
@@ -127,168 +218,197 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
+    // Use number n (0, 1, 2, ...) of a barrier completes its phase n & 1; "free again after use n - 1" is a
+    // wait for parity (n & 1) ^ 1, which a fresh barrier passes at once.
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        uint32_t slot = 0, slot_phase = 0, n_unit = 0;
+        // ------------------------------ K producer: Q, then the blocks of Kt ------------------------------
+        // K-ring entry e holds the operand of the product into S buffer e, so "entry free" is the very event
+        // "that product has completed" = s_full[e]: no separate empty barrier, no extra commit.
         bool ok = true;
+        uint32_t n_unit = 0;
         const uint64_t pol = l2_policy(0);
-        // one 16 KB slot: rows k0..k0+63 (the MMA's K) by columns n0..n0+127 of an MN-major operand
-        auto load_slot = [&](const CUtensorMap *map, int32_t n0, int32_t k0, int32_t z) -> bool {
-            if (!mbar_wait(empty0 + 8 * slot, slot_phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY)) return false;
-            if (elect_one()) {
-                const uint32_t bar = full0 + 8 * slot, dst = ring_base + slot * AT_ATOM;
-                mbar_arrive_expect_tx(bar, AT_ATOM);
-                tma_load_3d<1>(dst, map, bar, n0, k0, z, pol);
-                tma_load_3d<1>(dst + 8192, map, bar, n0 + 64, k0, z, pol);
-            }
-            __syncwarp();
-            if (++slot == AT_SLOTS) { slot = 0; slot_phase ^= 1; }
-            return true;
-        };
         for (uint32_t u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++n_unit) {
             const int32_t b = (int32_t)(u / p.q_tiles), row0 = (int32_t)((u % p.q_tiles) * AT_ROWS);
-            const uint32_t qb = n_unit & 1, q_phase = (n_unit >> 1) & 1;
-            ok = mbar_wait(q_empty0 + 8 * qb, q_phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
+            // the single Q buffer is free once the last Q Kt product of the previous unit has completed
+            ok = at_wait(q_empty0, (n_unit & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
             if (!ok) break;
             if (elect_one()) {
-                const uint32_t bar = q_full0 + 8 * qb, dst = q_base + qb * AT_Q_BYTES;
-                mbar_arrive_expect_tx(bar, AT_Q_BYTES);
-                tma_load_3d<1>(dst, &map_q, bar, 0, row0, b, pol);
-                tma_load_3d<1>(dst + AT_ATOM, &map_q, bar, 64, row0, b, pol);
+                mbar_arrive_expect_tx(q_full0, AT_Q_BYTES);
+                tma_load_3d<1>(q_base, &map_q, q_full0, 0, row0, b, pol);
+                tma_load_3d<1>(q_base + AT_ATOM, &map_q, q_full0, 64, row0, b, pol);
             }
             __syncwarp();
-            auto load_kt = [&](uint32_t kb) {     // K of this MMA = d: halves 0..63, 64..127; N = keys
-                return load_slot(&map_kt, (int32_t)(kb * AT_KEYS), 0, b) && load_slot(&map_kt, (int32_t)(kb * AT_KEYS), 64, b);
-            };
-            auto load_v = [&](uint32_t kb) {      // K of this MMA = keys: halves of the block; N = d
-                return load_slot(&map_v, 0, (int32_t)(kb * AT_KEYS), b) && load_slot(&map_v, 0, (int32_t)(kb * AT_KEYS + 64), b);
-            };
-            for (uint32_t kb = 0; kb < nkb && ok; ++kb) ok = load_kt(kb);
-            for (uint32_t i = 0; i <= nkb && ok; ++i) {
-                if (i < nkb) ok = load_kt(i);
-                if (ok && i >= 1) ok = load_v(i - 1);
+            for (uint32_t t = 0; t < 2 * nkb && ok; ++t) {
+                const uint32_t e = t & 1, n = n_unit * nkb + (t >> 1);
+                ok = at_wait(s_full0 + 8 * e, (n & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
+                if (!ok) break;
+                if (elect_one()) {
+                    const uint32_t bar = kfull0 + 8 * e, dst = ring_base + e * AT_ENTRY;
+                    const int32_t key0 = (int32_t)((t < nkb ? t : t - nkb) * AT_KEYS);
+                    if (p.debug & 1u) {
+                        mbar_arrive(bar);
+                    } else {    // K of the MMA = d (all 128 rows of Kt), N = the block's keys, two 64-key halves
+                        mbar_arrive_expect_tx(bar, AT_ENTRY);
+                        tma_load_3d<1>(dst, &map_kt, bar, key0, 0, b, pol);
+                        tma_load_3d<1>(dst + AT_ATOM, &map_kt, bar, key0 + 64, 0, b, pol);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 11) {
+        // ------------------------------ V producer ------------------------------
+        // V-ring entry pb holds the operand of the product that reads P tile pb: "entry free" = p_empty[pb].
+        bool ok = true;
+        uint32_t cnt0 = 0, cnt1 = 0;
+        const uint64_t pol = l2_policy(0);
+        for (uint32_t u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            const int32_t b = (int32_t)(u / p.q_tiles);
+            for (uint32_t j = 0; j < nkb && ok; ++j) {
+                const uint32_t pb = (nkb + j) & 1, n = pb ? cnt1 : cnt0;
+                ok = at_wait(p_empty0 + 8 * pb, (n & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
+                if (!ok) break;
+                if (pb) ++cnt1; else ++cnt0;
+                if (elect_one()) {
+                    const uint32_t bar = vfull0 + 8 * pb, dst = ring_base + (2 + pb) * AT_ENTRY;
+                    const int32_t key0 = (int32_t)(j * AT_KEYS);
+                    if (p.debug & 1u) {
+                        mbar_arrive(bar);
+                    } else {    // K of the MMA = the block's keys, N = d, two 64-column halves
+                        mbar_arrive_expect_tx(bar, AT_ENTRY);
+                        tma_load_3d<1>(dst, &map_v, bar, 0, key0, b, pol);
+                        tma_load_3d<1>(dst + AT_ATOM, &map_v, bar, 64, key0, b, pol);
+                    }
+                }
+                __syncwarp();
             }
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        uint32_t slot = 0, slot_phase = 0, n_unit = 0;
-        uint32_t s_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
+        // ------------------------------ S issuer: S[e] = Q Kt_blk ------------------------------
+        // Eight MMAs (k = 16 each) per product: the K-major A operand Q advances 32 bytes per step inside a
+        // 64-element half and 16 KB to the other half; the MN-major B operand advances 16 k-rows = 2048 bytes.
         bool ok = true;
+        uint32_t n_unit = 0, ntr = 0;
+        const bool prof = p.prof != nullptr;
+        long long w_data = 0, w_role = 0, t_all = prof ? clock64() : 0;
         const uint32_t idesc = p.idesc;
-        const uint64_t dq = make_desc(q_base, 0), dp = make_desc(p_base, 0), dr = make_desc(ring_base, 64 * 128);
-        const uint32_t q_hi = (uint32_t)(dq >> 32), p_hi = (uint32_t)(dp >> 32), r_hi = (uint32_t)(dr >> 32);
-        const uint32_t q_lo0 = (uint32_t)dq, p_lo0 = (uint32_t)dp, r_lo0 = (uint32_t)dr;
-        // 4 MMAs (k = 16 each) of one slot: A advances 32 bytes per step inside its 128-byte rows, the
-        // MN-major B advances 16 k-rows = 2048 bytes
-        auto mma_slot = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, bool first) -> bool {
-            if (!mbar_wait(full0 + 8 * slot, slot_phase, abort_flag, p.status, DEV_ERR_WAIT_FULL)) return false;
-            tc_fence_after();
-            const uint32_t b_lo = r_lo0 + slot * (AT_ATOM >> 4);
-            if (elect_one()) {
-#pragma unroll
-                for (uint32_t kk = 0; kk < 4; ++kk)
-                    umma_lohi<1>(d_tmem, a_lo + kk * 2, a_hi, b_lo + kk * 128, r_hi, idesc, (first && kk == 0) ? 0u : 1u);
-                umma_commit<1>(empty0 + 8 * slot);
-            }
-            __syncwarp();
-            if (++slot == AT_SLOTS) { slot = 0; slot_phase ^= 1; }
-            return true;
-        };
+        const uint64_t dq = make_desc(q_base, 0), dr = make_desc(ring_base, 128 * 128);
+        const uint32_t q_hi = (uint32_t)(dq >> 32), r_hi = (uint32_t)(dr >> 32), q_lo = (uint32_t)dq, r_lo0 = (uint32_t)dr;
         for (uint32_t u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++n_unit) {
-            const uint32_t qb = n_unit & 1, q_phase = (n_unit >> 1) & 1;
-            ok = mbar_wait(q_full0 + 8 * qb, q_phase, abort_flag, p.status, DEV_ERR_WAIT_FULL);
-            if (!ok) break;
-            const uint32_t q_lo = q_lo0 + qb * (AT_Q_BYTES >> 4);
-            // S block number t of this unit (0 .. 2 nkb - 1) goes to S buffer t % 2
-            auto s_block = [&](uint32_t t) -> bool {
-                const uint32_t sb = t & 1;
-                if (!mbar_wait(s_empty0 + 8 * sb, (s_cnt[sb] & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY)) return false;
+            ok = at_wait(q_full0, n_unit & 1, abort_flag, p.status, DEV_ERR_WAIT_FULL);
+            for (uint32_t t = 0; t < 2 * nkb && ok; ++t) {
+                const uint32_t e = t & 1, n = n_unit * nkb + (t >> 1);
+                long long c0 = prof ? clock64() : 0;
+                ok = at_wait(kfull0 + 8 * e, n & 1, abort_flag, p.status, DEV_ERR_WAIT_FULL);
+                if (!ok) break;
+                long long c1 = prof ? clock64() : 0;
+                ok = at_wait(s_empty0 + 8 * e, (n & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
+                if (!ok) break;
                 tc_fence_after();
-                ++s_cnt[sb];
-                const uint32_t d_tmem = tmem_base + sb * 128;
-                if (!mma_slot(d_tmem, q_lo, q_hi, true)) return false;
-                if (!mma_slot(d_tmem, q_lo + (AT_ATOM >> 4), q_hi, false)) return false;
-                if (elect_one()) umma_commit<1>(s_full0 + 8 * sb);
-                __syncwarp();
-                return true;
-            };
-            for (uint32_t kb = 0; kb < nkb && ok; ++kb) ok = s_block(kb);
-            for (uint32_t i = 0; i <= nkb && ok; ++i) {
-                if (i < nkb) ok = s_block(nkb + i);
-                if (ok && i >= 1) {
-                    const uint32_t j = i - 1, pb = (nkb + j) & 1;
-                    ok = mbar_wait(p_full0 + 8 * pb, p_cnt[pb] & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
-                    if (!ok) break;
-                    ++p_cnt[pb];
-                    if (j == 0) {   // the previous unit's O must have been read out
-                        ok = mbar_wait(o_empty, (n_unit & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
-                        if (!ok) break;
+                if (prof) { w_data += c1 - c0; w_role += clock64() - c1; }
+                at_trace(p, 0, ntr, 0x100000u | t);
+                if (elect_one()) {
+                    const uint32_t d_tmem = tmem_base + e * 128, b_lo = r_lo0 + e * (AT_ENTRY >> 4);
+                    if (!(p.debug & 16u)) {
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 8; ++kk)
+                            umma_lohi<1>(d_tmem, q_lo + (kk >> 2) * (AT_ATOM >> 4) + (kk & 3) * 2, q_hi, b_lo + kk * 128, r_hi, idesc,
+                                         kk ? 1u : 0u);
                     }
-                    tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + 256, pl = p_lo0 + pb * (AT_P_BYTES >> 4);
-                    ok = mma_slot(d_tmem, pl, p_hi, j == 0) && mma_slot(d_tmem, pl + (AT_ATOM >> 4), p_hi, false);
-                    if (!ok) break;
-                    if (elect_one()) {
-                        umma_commit<1>(p_empty0 + 8 * pb);
-                        if (j == nkb - 1) {
-                            umma_commit<1>(o_full);
-                            umma_commit<1>(q_empty0 + 8 * qb);
-                        }
-                    }
-                    __syncwarp();
+                    umma_commit<1>(s_full0 + 8 * e);
+                    if (t == 2 * nkb - 1) umma_commit<1>(q_empty0);       // Q is not read again in this unit
                 }
+                __syncwarp();
+                at_trace(p, 0, ntr, 0x200000u | t);
             }
         }
-    } else {
+        if (prof && lane == 0) {
+            unsigned long long *o = p.prof + (size_t)blockIdx.x * 16;
+            o[0] = (unsigned long long)(clock64() - t_all); o[1] = (unsigned long long)w_data; o[2] = (unsigned long long)w_role;
+        }
+    } else if (warp == 10) {
+        // ------------------------------ PV issuer: O += P[pb] V_blk ------------------------------
+        bool ok = true;
+        uint32_t n_unit = 0, cnt0 = 0, cnt1 = 0, ntr = 0;
+        const bool prof = p.prof != nullptr;
+        long long w_data = 0, w_role = 0;
+        const uint32_t idesc = p.idesc;
+        const uint64_t dp = make_desc(p_base, 0), dr = make_desc(ring_base + 2 * AT_ENTRY, 128 * 128);
+        const uint32_t p_hi = (uint32_t)(dp >> 32), r_hi = (uint32_t)(dr >> 32), p_lo0 = (uint32_t)dp, r_lo0 = (uint32_t)dr;
+        for (uint32_t u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++n_unit) {
+            for (uint32_t j = 0; j < nkb && ok; ++j) {
+                const uint32_t pb = (nkb + j) & 1, n = pb ? cnt1 : cnt0;
+                long long c0 = prof ? clock64() : 0;
+                ok = at_wait(vfull0 + 8 * pb, n & 1, abort_flag, p.status, DEV_ERR_WAIT_FULL);
+                if (!ok) break;
+                long long c1 = prof ? clock64() : 0;
+                ok = at_wait(p_full0 + 8 * pb, n & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
+                if (!ok) break;
+                // the previous unit's O must have been read out before the first product overwrites it
+                if (j == 0) ok = at_wait(o_empty, (n_unit & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
+                if (!ok) break;
+                if (pb) ++cnt1; else ++cnt0;
+                tc_fence_after();
+                if (prof) { w_data += c1 - c0; w_role += clock64() - c1; }
+                at_trace(p, 3, ntr, 0x300000u | j);
+                if (elect_one()) {
+                    const uint32_t d_tmem = tmem_base + 256, a_lo = p_lo0 + pb * (AT_P_BYTES >> 4), b_lo = r_lo0 + pb * (AT_ENTRY >> 4);
+                    if (!(p.debug & 16u)) {
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 8; ++kk)
+                            umma_lohi<1>(d_tmem, a_lo + (kk >> 2) * (AT_ATOM >> 4) + (kk & 3) * 2, p_hi, b_lo + kk * 128, r_hi, idesc,
+                                         (j | kk) ? 1u : 0u);
+                    }
+                    umma_commit<1>(p_empty0 + 8 * pb);
+                    if (j == nkb - 1) umma_commit<1>(o_full);
+                }
+                __syncwarp();
+                at_trace(p, 3, ntr, 0x400000u | j);
+            }
+        }
+        if (prof && lane == 0) {
+            unsigned long long *o = p.prof + (size_t)blockIdx.x * 16;
+            o[3] = (unsigned long long)w_data; o[4] = (unsigned long long)w_role;
+        }
+    } else if (warp < 10) {
         // ------------------------------ softmax groups ------------------------------
         const uint32_t sw = warp - 2, g = sw >> 2, q = warp & 3;
         const uint32_t row_in_tile = q * 32 + lane;
         const uint32_t t_lane = (q * 32u) << 16;
         const float LOG2E = 1.4426950408889634f;
-        uint32_t s_cnt = 0, p_cnt = 0, n_unit = 0;
+        uint32_t s_cnt = 0, p_cnt = 0, n_unit = 0, ntr = 0;
         bool ok = true;
+        const bool prof = p.prof != nullptr && (sw & 3) == 0;
+        long long x_sfull1 = 0, x_sfull2 = 0, x_pempty = 0, x_stat = 0, x_ofull = 0;
         for (uint32_t u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++n_unit) {
             const uint32_t b = u / p.q_tiles, row0 = (u % p.q_tiles) * AT_ROWS;
             float m = -INFINITY, l = 0.0f;
             // ---- pass 1: row maximum and sum of exp over the blocks of this group ----
             for (uint32_t t = g; t < nkb && ok; t += 2) {
-                ok = mbar_wait(s_full0 + 8 * g, s_cnt & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
+                long long c0 = prof ? clock64() : 0;
+                ok = at_wait(s_full0 + 8 * g, s_cnt & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
                 if (!ok) break;
                 ++s_cnt;
                 tc_fence_after();
+                if (prof) x_sfull1 += clock64() - c0;
+                if ((sw & 3) == 0) at_trace(p, 1 + g, ntr, (0x800000u + g * 0x400000u) | t);
                 const uint32_t valid = p.sk - t * AT_KEYS;          // >= 128 except in a ragged last block
-#pragma unroll 1
-                for (uint32_t c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_base + t_lane + g * 128 + c * 32, v);
-                    tmem_ld_wait();
-                    if (c == 3) {       // every score of the block is in registers or consumed: free the buffer
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(s_empty0 + 8 * g);
-                    }
-                    if (valid < AT_KEYS) {
-#pragma unroll
-                        for (uint32_t j = 0; j < 32; ++j)
-                            if (c * 32 + j >= valid) v[j] = __float_as_uint(-INFINITY);
-                    }
-                    float mx = m;
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
-                    if (mx != -INFINITY) {
-                        const float nmc = -mx * LOG2E;
-                        float a0 = l * ex2_approx(fmaf(m, LOG2E, nmc)), a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-#pragma unroll
-                        for (uint32_t j = 0; j < 32; j += 4) {
-                            a0 += ex2_approx(fmaf(__uint_as_float(v[j]), LOG2E, nmc));
-                            a1 += ex2_approx(fmaf(__uint_as_float(v[j + 1]), LOG2E, nmc));
-                            a2 += ex2_approx(fmaf(__uint_as_float(v[j + 2]), LOG2E, nmc));
-                            a3 += ex2_approx(fmaf(__uint_as_float(v[j + 3]), LOG2E, nmc));
-                        }
-                        l = (a0 + a1) + (a2 + a3);
-                        m = mx;
-                    }
-                }
+                const bool ragged = valid < AT_KEYS;
+                const uint32_t ts = tmem_base + t_lane + g * 128;
+                // all 128 scores of the row into registers, then the buffer goes straight back to the MMA
+                // warp: the next product into it overlaps the arithmetic below
+                uint32_t v0[32], v1[32], v2[32], v3[32];
+                tmem_ld32(ts, v0); tmem_ld32(ts + 32, v1); tmem_ld32(ts + 64, v2); tmem_ld32(ts + 96, v3);
+                tmem_ld_wait_on(v0); tmem_ld_wait_on(v1); tmem_ld_wait_on(v2); tmem_ld_wait_on(v3);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty0 + 8 * g);
+                if (ragged) { at_mask(v0, 0, valid); at_mask(v1, 32, valid); at_mask(v2, 64, valid); at_mask(v3, 96, valid); }
+                const float mx = fmax3(fmax3(at_max32(v0), at_max32(v1), at_max32(v2)), at_max32(v3), m);
+                const float nmc = -mx * LOG2E;          // the first 32 columns of a block always exist: mx is finite
+                l = l * ex2_approx(fmaf(m, LOG2E, nmc)) + ((at_sum32(v0, nmc) + at_sum32(v1, nmc)) + (at_sum32(v2, nmc) + at_sum32(v3, nmc)));
+                m = mx;
+                if ((sw & 3) == 0) at_trace(p, 1 + g, ntr, (0x900000u + g * 0x400000u) | t);
             }
             if (!ok) break;
             // ---- exchange (m, l) with the other group: both groups have a warp on every TMEM lane
@@ -302,9 +422,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(stat0 + 8 * par);
-            ok = mbar_wait(stat0 + 8 * par, (n_unit >> 1) & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
+            long long cs = prof ? clock64() : 0;
+            ok = at_wait(stat0 + 8 * par, (n_unit >> 1) & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
+            if (prof) x_stat += clock64() - cs;
             uint32_t om, ol;
             tmem_ld2(t_stat + (g ^ 1) * 2, om, ol);
             tmem_ld_wait();
@@ -312,57 +434,50 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const float M = fmaxf(m, other_m);
             const float nMc = -M * LOG2E;
             const float L = l * ex2_approx(fmaf(m, LOG2E, nMc)) + other_l * ex2_approx(fmaf(other_m, LOG2E, nMc));
-            const float inv = 1.0f / L;
+            const float off = nMc - lg2_approx(L);      // p = 2^(s log2 e + off) = exp(s - M) / L
             // ---- pass 2: P blocks ----
             for (uint32_t t = nkb + ((nkb + g) & 1); t < 2 * nkb && ok; t += 2) {
                 const uint32_t kb = t - nkb;
-                ok = mbar_wait(s_full0 + 8 * g, s_cnt & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
+                long long c0 = prof ? clock64() : 0;
+                ok = at_wait(s_full0 + 8 * g, s_cnt & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
                 if (!ok) break;
                 ++s_cnt;
-                ok = mbar_wait(p_empty0 + 8 * g, (p_cnt & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
+                long long c1 = prof ? clock64() : 0;
+                ok = at_wait(p_empty0 + 8 * g, (p_cnt & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
                 if (!ok) break;
                 ++p_cnt;
                 tc_fence_after();
+                if (prof) { x_sfull2 += c1 - c0; x_pempty += clock64() - c1; }
+                if ((sw & 3) == 0) at_trace(p, 1 + g, ntr, (0x800000u + g * 0x400000u) | t);
                 const uint32_t valid = p.sk - kb * AT_KEYS;
-                uint8_t *prow = smem_gen + (p_base - smem_base) + g * AT_P_BYTES + row_in_tile * 128;
-#pragma unroll 1
-                for (uint32_t c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_base + t_lane + g * 128 + c * 32, v);
-                    tmem_ld_wait();
-                    if (c == 3) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(s_empty0 + 8 * g);
-                    }
-                    if (valid < AT_KEYS) {
-#pragma unroll
-                        for (uint32_t j = 0; j < 32; ++j)
-                            if (c * 32 + j >= valid) v[j] = __float_as_uint(-INFINITY);
-                    }
-                    uint32_t w[16];
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; j += 2) {
-                        const float p0 = ex2_approx(fmaf(__uint_as_float(v[j]), LOG2E, nMc)) * inv;
-                        const float p1 = ex2_approx(fmaf(__uint_as_float(v[j + 1]), LOG2E, nMc)) * inv;
-                        w[j >> 1] = at_pack16(p0, p1, p.dtype);
-                    }
-                    // keys c*32 .. c*32+31 of this row: key-half (atom) c / 2, 16-byte chunks (c % 2) * 4 .. + 3
-                    uint8_t *dst = prow + (c >> 1) * AT_ATOM;
-#pragma unroll
-                    for (uint32_t jj = 0; jj < 4; ++jj)
-                        *reinterpret_cast<uint4 *>(dst + (((((c & 1) * 4 + jj)) ^ (row_in_tile & 7)) << 4)) =
-                            make_uint4(w[4 * jj], w[4 * jj + 1], w[4 * jj + 2], w[4 * jj + 3]);
-                }
+                const bool ragged = valid < AT_KEYS;
+                const uint32_t ts = tmem_base + t_lane + g * 128;
+                // this row's two 128-byte lines of the P tile: keys 0..63 and 64..127 of the block
+                uint8_t *line0 = smem_gen + (p_base - smem_base) + g * AT_P_BYTES + row_in_tile * 128, *line1 = line0 + AT_ATOM;
+                const uint32_t row7 = row_in_tile & 7;
+                uint32_t v0[32], v1[32], v2[32], v3[32];
+                tmem_ld32(ts, v0); tmem_ld32(ts + 32, v1); tmem_ld32(ts + 64, v2); tmem_ld32(ts + 96, v3);
+                tmem_ld_wait_on(v0); tmem_ld_wait_on(v1); tmem_ld_wait_on(v2); tmem_ld_wait_on(v3);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty0 + 8 * g);
+                if (ragged) { at_mask(v0, 0, valid); at_mask(v1, 32, valid); at_mask(v2, 64, valid); at_mask(v3, 96, valid); }
+                at_probs32(v0, off, p.dtype, line0, 0, row7);
+                at_probs32(v1, off, p.dtype, line0, 4, row7);
+                at_probs32(v2, off, p.dtype, line1, 0, row7);
+                at_probs32(v3, off, p.dtype, line1, 4, row7);
                 fence_proxy_async_smem();      // generic-proxy writes -> visible to the MMA's async-proxy reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full0 + 8 * g);
+                if ((sw & 3) == 0) at_trace(p, 1 + g, ntr, (0x900000u + g * 0x400000u) | t);
             }
             if (!ok) break;
             // ---- O: this group's 64 columns of the finished accumulator ----
+            long long co = prof ? clock64() : 0;
             ok = mbar_wait_patient(o_full, n_unit & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
+            if (prof) x_ofull += clock64() - co;
             const uint32_t row = row0 + row_in_tile;
             float *orow = p.O + (uint64_t)b * p.o_stride + (uint64_t)row * p.ldo + g * 64;
 #pragma unroll 1
@@ -379,6 +494,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(o_empty);
+        }
+        if (prof && lane == 0) {
+            unsigned long long *o = p.prof + (size_t)blockIdx.x * 16 + 6 + g * 5;
+            o[0] = (unsigned long long)x_sfull1; o[1] = (unsigned long long)x_sfull2; o[2] = (unsigned long long)x_pempty;
+            o[3] = (unsigned long long)x_stat; o[4] = (unsigned long long)x_ofull;
         }
     }
 
@@ -440,10 +560,10 @@ int attn_fused_launch(const AttnProblem &a) {
     int st;
     // Q [b][sq][d] as a K-major A operand: boxes of 64 d-elements x 128 rows
     if ((st = encode_3d(&mq, a.dtype, a.q, a.d, a.sq, a.batch, a.ldq, a.q_stride, 64, 128)) != ST_OK) return st;
-    // Kt [b][d][sk]: MN-major B with N = keys (contiguous), K = d: boxes of 64 keys x 64 d-rows
-    if ((st = encode_3d(&mk, a.dtype, a.kt, a.sk, a.d, a.batch, a.ldk, a.k_stride, 64, 64)) != ST_OK) return st;
-    // V [b][sk][d]: MN-major B with N = d (contiguous), K = keys: boxes of 64 d x 64 key-rows
-    if ((st = encode_3d(&mv, a.dtype, a.v, a.d, a.sk, a.batch, a.ldv, a.v_stride, 64, 64)) != ST_OK) return st;
+    // Kt [b][d][sk]: MN-major B with N = keys (contiguous), K = d: boxes of 64 keys x 128 d-rows
+    if ((st = encode_3d(&mk, a.dtype, a.kt, a.sk, a.d, a.batch, a.ldk, a.k_stride, 64, 128)) != ST_OK) return st;
+    // V [b][sk][d]: MN-major B with N = d (contiguous), K = keys: boxes of 64 d x 128 key-rows
+    if ((st = encode_3d(&mv, a.dtype, a.v, a.d, a.sk, a.batch, a.ldv, a.v_stride, 64, 128)) != ST_OK) return st;
 
     AttnParams p = {};
     p.batch = a.batch; p.sq = a.sq; p.sk = a.sk;
@@ -454,6 +574,8 @@ int attn_fused_launch(const AttnProblem &a) {
     p.dtype = (uint32_t)a.dtype;
     p.O = a.o; p.ldo = a.ldo; p.o_stride = a.o_stride;
     p.status = a.dev_status;
+    p.prof = a.prof;
+    p.debug = a.debug;
     const uint64_t units = (uint64_t)p.batch * p.q_tiles;
     if (units > 0xFFFFFFFFull) return ST_UNSUPPORTED;
     const uint32_t sms = (uint32_t)device_sm_count();

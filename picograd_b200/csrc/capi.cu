@@ -803,6 +803,8 @@ int pg_b200_attention_bmm(int dtype, size_t batch, size_t seq_q, size_t seq_k, s
         a.v = v; a.ldv = d; a.v_stride = seq_k * d;
         a.o = o; a.ldo = d; a.o_stride = seq_q * d;
         a.stream = g.stream; a.dev_status = g.dev_status;
+        a.prof = (g.opt_debug & 32) ? g.prof : nullptr;
+        a.debug = (uint32_t)g.opt_debug;
         const int st = attn_fused_launch(a);
         if (st != ST_UNSUPPORTED) return st;
     }

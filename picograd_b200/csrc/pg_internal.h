@@ -90,6 +90,8 @@ struct AttnProblem {
     float *o; uint64_t ldo, o_stride;
     cudaStream_t stream;
     uint32_t *dev_status;
+    unsigned long long *prof;   // 16 cycle counters per CTA, for the timing experiments (may be null)
+    uint32_t debug;             // timing experiments: 1 = no TMA loads, 16 = no MMAs (results are garbage)
 };
 int attn_fused_launch(const AttnProblem &a);
 

@@ -78,6 +78,26 @@ __device__ __forceinline__ uint32_t mbar_spin(uint32_t bar, uint32_t parity, uin
         : "memory");
     return done;
 }
+// The same with a caller-chosen suspend hint.
+__device__ __forceinline__ uint32_t mbar_spin_hint(uint32_t bar, uint32_t parity, uint32_t tries, uint32_t hint_ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b32 n;\n\t"
+        "mov.b32 n, %3;\n"
+        "PG_WAITH_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %4;\n\t"
+        "@p bra PG_WAITH_DONE;\n\t"
+        "sub.u32 n, n, 1;\n\t"
+        "setp.ne.u32 p, n, 0;\n\t"
+        "@p bra PG_WAITH_LOOP;\n\t"
+        "setp.ne.u32 p, n, 0;\n"
+        "PG_WAITH_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(tries), "r"(hint_ns)
+        : "memory");
+    return done;
+}
 // Bounded wait, executed by a whole (converged) warp; the result is the same in every lane.
 // Returns false when the CTA is aborting (this or another wait ran out of time).
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
@@ -100,6 +120,15 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
                                           uint32_t *status, uint32_t err_bit) {
     const uint32_t done = mbar_spin(bar, parity, 1u << 14);
+    if (__all_sync(0xffffffffu, done)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, err_bit);
+}
+// For hand-overs whose latency is on the critical path (a consumer that starts as soon as its producer
+// signals): the hardware may keep a waiting thread suspended for up to the hint before it looks again, so
+// the hint is a few tens of nanoseconds here.
+__device__ __forceinline__ bool mbar_wait_quick(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                uint32_t *status, uint32_t err_bit, uint32_t hint_ns) {
+    const uint32_t done = mbar_spin_hint(bar, parity, 1u << 16, hint_ns);
     if (__all_sync(0xffffffffu, done)) return true;
     return mbar_wait_slow(bar, parity, abort_flag, status, err_bit);
 }
