@@ -318,6 +318,15 @@ def run_other_config(args):
         c = torch.empty((m, n), dtype=torch.float32, device="cuda")
         fn = lambda: pg.pg_gemm_ex(wl.F16, m, n, k, ad, k, bd, n, c, n)
         flops, byts, name, dt = 2.0 * m * n * k, (m * k + k * n) * 2 + m * n * 4, f"pg_gemm_ex f16 {m}x{n}x{k}", "f16"
+    elif cfg == "4-fused":
+        # configuration 4 as one call: the chain pg_bmm -> softmax -> cast -> pg_bmm in one kernel; the f32
+        # scores and the bf16 probabilities never reach HBM, so the algorithmic bytes are Q, Kt, V in and O out
+        q, kt, v = wl.config4()
+        qd, ktd, vd = (to_dev(x, wl.BF16) for x in (q, kt, v))
+        fn = lambda: pg.pg_attention_bmm(qd, ktd, vd)
+        flops = 2 * 2.0 * 64 * 2048 * 2048 * 128
+        byts = 3 * 64 * 2048 * 128 * 2 + 64 * 2048 * 128 * 4
+        name, dt = "pg_attention_bmm (QK^T -> softmax -> PV in one kernel), bf16 [64,2048,128]", "bf16"
     elif cfg == "4":
         q, kt, v = wl.config4()
         qd, ktd, vd = (to_dev(x, wl.BF16) for x in (q, kt, v))
@@ -392,7 +401,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--config", default="2", choices=["1", "2", "3a", "3b", "4", "5", "linear", "linear-unfused"],
+    ap.add_argument("--config", default="2", choices=["1", "2", "3a", "3b", "4", "4-fused", "5", "linear", "linear-unfused"],
                     help="2 (default) is the headline metric; the others time the remaining configurations "
                          "(single GPU, device-resident) and print one JSON line each")
     args = ap.parse_args()

@@ -48,7 +48,7 @@ constexpr uint32_t AT_P_BYTES = 2 * AT_ATOM;      // one P tile (two key-halves)
 constexpr uint32_t AT_BAR_BYTES = 1024;
 constexpr uint32_t AT_SMEM = 1024 + AT_Q_BYTES + 2 * AT_P_BYTES + AT_ENTRIES * AT_ENTRY + AT_BAR_BYTES;
 constexpr uint32_t AT_THREADS = 384;
-constexpr uint32_t AT_TMEM_COLS = 512;            // S0 at 0, S1 at 128, O at 256
+constexpr uint32_t AT_TMEM_COLS = 512;            // S0 at 0, S1 at 128, O at 256, Q at 384, row statistics at 448
 static_assert(AT_SMEM <= 232448, "shared memory budget");
 
 struct AttnParams {
@@ -61,6 +61,7 @@ struct AttnParams {
     uint32_t *status;
     unsigned long long *prof;     // timing experiments: 16 cycle counters per CTA (may be null)
     uint32_t debug;               // timing experiments (results are garbage): 1 = no TMA loads, 16 = no MMAs
+    uint32_t q_tmem;              // Q is copied to tensor memory once per unit and read from there by the MMAs
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -80,6 +81,24 @@ __device__ __forceinline__ uint32_t at_pack16(float lo, float hi, uint32_t dtype
     if (dtype == (uint32_t)DT_BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (128 rows = lanes, 16 K-elements = 8 columns per MMA) read
+// from tensor memory, so that only B crosses the shared-memory port.
+__device__ __forceinline__ void umma_ta(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Shared memory -> tensor memory: 128 rows x 256 bits (16 16-bit elements of each row of a K-major tile) into 8
+// columns; asynchronous, ordered before later tcgen05.mma of the same thread.
+__device__ __forceinline__ void tmem_cp_128x256b(uint32_t taddr, uint32_t s_lo, uint32_t s_hi) {
+    asm volatile(
+        "{\n\t.reg .b64 ds;\n\tmov.b64 ds, {%1, %2};\n\t"
+        "tcgen05.cp.cta_group::1.128x256b [%0], ds;\n\t}"
+        ::"r"(taddr), "r"(s_lo), "r"(s_hi) : "memory");
 }
 // Waits for this thread's outstanding tcgen05.ld and ties the wait to the registers just loaded, so that the
 // compiler cannot schedule arithmetic on them above it (loads of the next chunk are issued before the
@@ -131,14 +150,15 @@ __device__ __forceinline__ float at_sum32(const uint32_t (&v)[32], float nmc) {
     return (s0 + s1) + (s2 + s3);
 }
 // Pass 2 on 32 scores: p = 2^(s log2 e + off) with off = -(M log2 e + log2 L), i.e. exp(s - M) / L, rounded to
-// 16 bits and written as four 16-byte pieces of the row's 128-byte line of the swizzled P tile.
-__device__ __forceinline__ void at_probs32(const uint32_t (&v)[32], float off, uint32_t dtype, uint8_t *line,
-                                           uint32_t first_piece, uint32_t row7) {
+// 16 bits, two per word.
+__device__ __forceinline__ void at_probs32(const uint32_t (&v)[32], float off, uint32_t dtype, uint32_t (&w)[16]) {
     const float LOG2E = 1.4426950408889634f;
-    uint32_t w[16];
 #pragma unroll
     for (uint32_t j = 0; j < 32; j += 2)
         w[j >> 1] = at_pack16(ex2_approx(fmaf(AT_F(j), LOG2E, off)), ex2_approx(fmaf(AT_F(j + 1), LOG2E, off)), dtype);
+}
+// The 32 probabilities as four 16-byte pieces of the row's 128-byte line of the swizzled P tile.
+__device__ __forceinline__ void at_store32(const uint32_t (&w)[16], uint8_t *line, uint32_t first_piece, uint32_t row7) {
 #pragma unroll
     for (uint32_t jj = 0; jj < 4; ++jj)
         *reinterpret_cast<uint4 *>(line + (((first_piece + jj) ^ row7) << 4)) =
@@ -296,6 +316,19 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t q_hi = (uint32_t)(dq >> 32), r_hi = (uint32_t)(dr >> 32), q_lo = (uint32_t)dq, r_lo0 = (uint32_t)dr;
         for (uint32_t u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++n_unit) {
             ok = at_wait(q_full0, n_unit & 1, abort_flag, p.status, DEV_ERR_WAIT_FULL);
+            if (ok && p.q_tmem) {
+                // Q: shared memory -> TMEM columns 384..447 (8 columns per 16 elements of d).  The copies queue
+                // behind the previous unit's last product, which was the last reader of those columns; after
+                // them the shared-memory tile is free for the next unit's Q.
+                tc_fence_after();
+                if (elect_one()) {
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 8; ++kk)
+                        tmem_cp_128x256b(tmem_base + 384 + kk * 8, q_lo + (kk >> 2) * (AT_ATOM >> 4) + (kk & 3) * 2, q_hi);
+                    umma_commit<1>(q_empty0);
+                }
+                __syncwarp();
+            }
             for (uint32_t t = 0; t < 2 * nkb && ok; ++t) {
                 const uint32_t e = t & 1, n = n_unit * nkb + (t >> 1);
                 long long c0 = prof ? clock64() : 0;
@@ -309,14 +342,19 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 at_trace(p, 0, ntr, 0x100000u | t);
                 if (elect_one()) {
                     const uint32_t d_tmem = tmem_base + e * 128, b_lo = r_lo0 + e * (AT_ENTRY >> 4);
-                    if (!(p.debug & 16u)) {
+                    if (p.debug & 16u) {
+                    } else if (p.q_tmem) {
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 8; ++kk)
+                            umma_ta(d_tmem, tmem_base + 384 + kk * 8, b_lo + kk * 128, r_hi, idesc, kk ? 1u : 0u);
+                    } else {
 #pragma unroll
                         for (uint32_t kk = 0; kk < 8; ++kk)
                             umma_lohi<1>(d_tmem, q_lo + (kk >> 2) * (AT_ATOM >> 4) + (kk & 3) * 2, q_hi, b_lo + kk * 128, r_hi, idesc,
                                          kk ? 1u : 0u);
                     }
                     umma_commit<1>(s_full0 + 8 * e);
-                    if (t == 2 * nkb - 1) umma_commit<1>(q_empty0);       // Q is not read again in this unit
+                    if (t == 2 * nkb - 1 && !p.q_tmem) umma_commit<1>(q_empty0);       // Q is not read again in this unit
                 }
                 __syncwarp();
                 at_trace(p, 0, ntr, 0x200000u | t);
@@ -380,6 +418,34 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         bool ok = true;
         const bool prof = p.prof != nullptr && (sw & 3) == 0;
         long long x_sfull1 = 0, x_sfull2 = 0, x_pempty = 0, x_stat = 0, x_ofull = 0;
+        // O of a finished unit: this group's 64 columns of the accumulator, straight from TMEM to global
+        // memory.  It is read out AFTER pass 1 of the following unit (which does not touch O), when its last
+        // P V product has long completed: nobody waits for it, and only pass 2 of that unit needs O free.
+        bool have_prev = false;
+        uint32_t prev_b = 0, prev_row0 = 0, prev_unit = 0;
+        auto drain_o = [&](uint32_t ob, uint32_t orow0, uint32_t ounit) -> bool {
+            long long co = prof ? clock64() : 0;
+            if (!mbar_wait_patient(o_full, ounit & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL)) return false;
+            tc_fence_after();
+            if (prof) x_ofull += clock64() - co;
+            const uint32_t row = orow0 + row_in_tile;
+            float *orow = p.O + (uint64_t)ob * p.o_stride + (uint64_t)row * p.ldo + g * 64;
+#pragma unroll 1
+            for (uint32_t c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + t_lane + 256 + g * 64 + c * 32, v);
+                tmem_ld_wait();
+                if (row < p.sq) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4 *>(orow + c * 32 + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_empty);
+            return true;
+        };
         for (uint32_t u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++n_unit) {
             const uint32_t b = u / p.q_tiles, row0 = (u % p.q_tiles) * AT_ROWS;
             float m = -INFINITY, l = 0.0f;
@@ -411,12 +477,16 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 if ((sw & 3) == 0) at_trace(p, 1 + g, ntr, (0x900000u + g * 0x400000u) | t);
             }
             if (!ok) break;
+            if (have_prev) {
+                ok = drain_o(prev_b, prev_row0, prev_unit);
+                if (!ok) break;
+            }
             // ---- exchange (m, l) with the other group: both groups have a warp on every TMEM lane
             //      quadrant, so a row's two partial results meet in two spare TMEM columns of its lane
-            //      (columns 384.., alternating with the unit so that a fast group cannot overwrite
+            //      (columns 448.., alternating with the unit so that a fast group cannot overwrite
             //      what a slow one has not read yet) ----
             const uint32_t par = n_unit & 1;
-            const uint32_t t_stat = tmem_base + t_lane + 384 + par * 4;
+            const uint32_t t_stat = tmem_base + t_lane + 448 + par * 4;
             tmem_st2(t_stat + g * 2, __float_as_uint(m), __float_as_uint(l));
             tmem_st_wait();
             tc_fence_before();
@@ -442,12 +512,8 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 ok = at_wait(s_full0 + 8 * g, s_cnt & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
                 if (!ok) break;
                 ++s_cnt;
-                long long c1 = prof ? clock64() : 0;
-                ok = at_wait(p_empty0 + 8 * g, (p_cnt & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
-                if (!ok) break;
-                ++p_cnt;
                 tc_fence_after();
-                if (prof) { x_sfull2 += c1 - c0; x_pempty += clock64() - c1; }
+                if (prof) x_sfull2 += clock64() - c0;
                 if ((sw & 3) == 0) at_trace(p, 1 + g, ntr, (0x800000u + g * 0x400000u) | t);
                 const uint32_t valid = p.sk - kb * AT_KEYS;
                 const bool ragged = valid < AT_KEYS;
@@ -462,39 +528,31 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_empty0 + 8 * g);
                 if (ragged) { at_mask(v0, 0, valid); at_mask(v1, 32, valid); at_mask(v2, 64, valid); at_mask(v3, 96, valid); }
-                at_probs32(v0, off, p.dtype, line0, 0, row7);
-                at_probs32(v1, off, p.dtype, line0, 4, row7);
-                at_probs32(v2, off, p.dtype, line1, 0, row7);
-                at_probs32(v3, off, p.dtype, line1, 4, row7);
+                uint32_t w0[16], w1[16], w2[16], w3[16];
+                at_probs32(v0, off, p.dtype, w0);
+                at_probs32(v1, off, p.dtype, w1);
+                at_probs32(v2, off, p.dtype, w2);
+                at_probs32(v3, off, p.dtype, w3);
+                // only now is the P tile needed: the product that read its previous contents has had the whole
+                // of the arithmetic above to complete
+                long long c1 = prof ? clock64() : 0;
+                ok = at_wait(p_empty0 + 8 * g, (p_cnt & 1) ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
+                if (!ok) break;
+                ++p_cnt;
+                if (prof) x_pempty += clock64() - c1;
+                at_store32(w0, line0, 0, row7);
+                at_store32(w1, line0, 4, row7);
+                at_store32(w2, line1, 0, row7);
+                at_store32(w3, line1, 4, row7);
                 fence_proxy_async_smem();      // generic-proxy writes -> visible to the MMA's async-proxy reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full0 + 8 * g);
                 if ((sw & 3) == 0) at_trace(p, 1 + g, ntr, (0x900000u + g * 0x400000u) | t);
             }
             if (!ok) break;
-            // ---- O: this group's 64 columns of the finished accumulator ----
-            long long co = prof ? clock64() : 0;
-            ok = mbar_wait_patient(o_full, n_unit & 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_FULL);
-            if (!ok) break;
-            tc_fence_after();
-            if (prof) x_ofull += clock64() - co;
-            const uint32_t row = row0 + row_in_tile;
-            float *orow = p.O + (uint64_t)b * p.o_stride + (uint64_t)row * p.ldo + g * 64;
-#pragma unroll 1
-            for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + t_lane + 256 + g * 64 + c * 32, v);
-                tmem_ld_wait();
-                if (row < p.sq) {
-#pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j)
-                        *reinterpret_cast<uint4 *>(orow + c * 32 + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty);
+            have_prev = true; prev_b = b; prev_row0 = row0; prev_unit = n_unit;
         }
+        if (ok && have_prev) ok = drain_o(prev_b, prev_row0, prev_unit);
         if (prof && lane == 0) {
             unsigned long long *o = p.prof + (size_t)blockIdx.x * 16 + 6 + g * 5;
             o[0] = (unsigned long long)x_sfull1; o[1] = (unsigned long long)x_sfull2; o[2] = (unsigned long long)x_pempty;
@@ -576,6 +634,7 @@ int attn_fused_launch(const AttnProblem &a) {
     p.status = a.dev_status;
     p.prof = a.prof;
     p.debug = a.debug;
+    p.q_tmem = a.q_tmem ? 1u : 0u;
     const uint64_t units = (uint64_t)p.batch * p.q_tiles;
     if (units > 0xFFFFFFFFull) return ST_UNSUPPORTED;
     const uint32_t sms = (uint32_t)device_sm_count();

@@ -40,6 +40,7 @@ struct State {
     int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
     int opt_host_pipeline = 1;   // host-pointer pg_gemm_ex: overlap copies and GEMMs block by block
     int opt_fused_splitk = 1;    // split-K slices summed by the GEMM kernel itself (else a second kernel)
+    int opt_attn_q_tmem = 1;     // attention kernel: Q copied to tensor memory once per unit and read from there (0: from shared memory)
     int opt_fused_attention = 1; // 0: pg_b200_attention_bmm always runs the three-kernel chain
     DeviceBuf attn_ws;           // S and P of the chain form of pg_b200_attention_bmm
     int opt_stream_k = 0;        // stream-K for a partly filled last wave: correct, but measured 5-20 % slower
@@ -805,6 +806,7 @@ int pg_b200_attention_bmm(int dtype, size_t batch, size_t seq_q, size_t seq_k, s
         a.stream = g.stream; a.dev_status = g.dev_status;
         a.prof = (g.opt_debug & 32) ? g.prof : nullptr;
         a.debug = (uint32_t)g.opt_debug;
+        a.q_tmem = g.opt_attn_q_tmem;
         const int st = attn_fused_launch(a);
         if (st != ST_UNSUPPORTED) return st;
     }
@@ -878,6 +880,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "host_pipeline")) { g.opt_host_pipeline = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "fused_splitk")) { g.opt_fused_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "swap_skinny")) { g.opt_swap_skinny = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "attn_q_tmem")) { g.opt_attn_q_tmem = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "fused_attention")) { g.opt_fused_attention = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }

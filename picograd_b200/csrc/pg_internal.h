@@ -92,6 +92,7 @@ struct AttnProblem {
     uint32_t *dev_status;
     unsigned long long *prof;   // 16 cycle counters per CTA, for the timing experiments (may be null)
     uint32_t debug;             // timing experiments: 1 = no TMA loads, 16 = no MMAs (results are garbage)
+    int q_tmem;                 // keep Q in tensor memory (A operand of the Q Kt products read from there)
 };
 int attn_fused_launch(const AttnProblem &a);
 

@@ -55,6 +55,18 @@ def test_fused_equals_the_chain_on_the_cpu(pg, oracle, dt, shape):
     assert wl.relerr(got.cpu().numpy(), want) <= e2e_tolerance(dt, sk)
 
 
+def test_q_from_shared_memory_and_from_tensor_memory_agree_bit_for_bit(pg):
+    """The Q Kt products read Q from tensor memory by default (copied there once per unit) or from shared memory
+    (option attn_q_tmem = 0): same operands, same MMAs, identical bits."""
+    q, kt, v = make_qkv(3, 400, 776, 128, wl.BF16, 94)
+    qd, ktd, vd = to_dev(q, wl.BF16), to_dev(kt, wl.BF16), to_dev(v, wl.BF16)
+    a = pg.pg_attention_bmm(qd, ktd, vd); pg.pg_dev_sync()
+    pg.set_option("attn_q_tmem", 0)
+    b = pg.pg_attention_bmm(qd, ktd, vd); pg.pg_dev_sync()
+    assert pg.last_path() == "attn:fused_128x128"
+    assert torch.equal(a, b)
+
+
 def test_many_units_per_cta_and_both_paths_agree(pg):
     """More work units than SMs (each CTA loops) and odd counts everywhere; the chain form of the same
     entry (the library's own three kernels) is the second opinion."""

@@ -88,6 +88,21 @@ def test_config4_attention_bmm_full(pg, oracle):
     assert freivalds(o, p16.double(), vd.double()) < wl.tolerance(wl.BF16, 2048) / 10
     p_bits = bits_to_host(p16[11])
     assert wl.relerr(to_host(o[11]), oracle.gemm_ex(wl.BF16, p_bits, v[11])) <= wl.tolerance(wl.BF16, 2048)
+    # the same chain as ONE kernel (scores and probabilities never leave the SM): against the three-kernel
+    # result above, and one batch element against the oracle running the chain on the CPU.  End to end a
+    # last-bit difference in a score can flip the bf16 rounding of a probability, hence the looser bound
+    # (a quarter of a bf16 unit) beside the tolerance of the second product.
+    fused = pg.pg_attention_bmm(qd, ktd, vd); pg.pg_dev_sync()
+    assert pg.last_path() == "attn:fused_128x128"
+    e2e = max(wl.tolerance(wl.BF16, 2048), 0.25 * 2.0 ** -8)
+    assert wl.relerr(to_host(fused), to_host(o)) <= e2e
+    sc = oracle.gemm_ex(wl.BF16, q[37], kt[37])
+    pc = wl.to_bf16_bits(oracle.softmax_rows(sc))
+    assert wl.relerr(to_host(fused[37]), oracle.gemm_ex(wl.BF16, pc, v[37])) <= e2e
+    # rows of P sum to one: with V all ones every output is one up to the rounding of P
+    ones = torch.ones_like(vd)
+    o1 = pg.pg_attention_bmm(qd, ktd, ones); pg.pg_dev_sync()
+    assert (o1 - 1.0).abs().max().item() < 2e-3
 
 
 def test_config5_mlp_step_full(pg, oracle):
