@@ -120,6 +120,15 @@ PG_B200_API int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_
                             const void *a, const void *b, int b_batched,
                             const float *g, float *ga, float *gb);
 
+/* pg_conv2d (ops/conv.c:10-146, ops/conv.h:27-33): NCHW 2-D convolution, f32.  x [n,cin,h,w], wt [cout,cin,kh,kw],
+ * bias [cout] or NULL -> out [n,cout,oh,ow] with oh = (h + 2 padding - kh) / stride + 1 (likewise ow).  Device
+ * pointers.  Same algorithm as picograd: im2col (rows in (ci,ki,kj) order, zeros outside the image) on the
+ * device, one f32 GEMM per batch element through the FFMA kernels (one fused multiply-add chain per output,
+ * zeros included, so results equal picograd's bit for bit), then the bias.  UNSUPPORTED for the shapes
+ * pg_conv2d returns NULL for (stride <= 0, window larger than the padded image). */
+PG_B200_API int pg_b200_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t cout, size_t kh, size_t kw,
+                   int stride, int padding, const float *x, const float *wt, const float *bias, float *out);
+
 /* The attention-shaped chain of picograd calls as ONE entry: O = 16bit(softmax_rows(Q * Kt)) * V, i.e.
  * pg_bmm (ops/matmul.c:340-369) -> pg_softmax over the last axis (ops/activations.c:22-45) -> cast to the
  * operand dtype -> pg_bmm.  q [batch, seq_q, d], kt [batch, d, seq_k], v [batch, seq_k, d] in `dtype`

@@ -324,6 +324,56 @@ void pgo_matmul_backward(int dtype, size_t m, size_t n, size_t k,
     }
 }
 
+/* ops/conv.c:10-146 (pg_conv2d): NCHW, per batch element an im2col matrix (K = cin*kh*kw rows in
+ * (ci, ki, kj) order, one column per output pixel, zeros where the window leaves the image), then
+ * pg_cpu_gemm(cout, columns, K, w, K, col, ...) and `+= bias[co]` over the finished rows (:127-133).
+ * The chunking into 1024 columns (:43-58) does not change any element's arithmetic: each output is one
+ * fused multiply-add chain over the K rows, zeros included, followed by one addition of the bias. */
+typedef struct {
+    size_t cin, h, w, cout, kh, kw, oh, ow; int stride, pad;
+    const float *x, *wt, *bias; float *out;
+} conv_ctx;
+
+static void conv_range(void *vctx, size_t begin, size_t end)
+{
+    const conv_ctx *c = (const conv_ctx *)vctx;
+    for (size_t o = begin; o < end; o++) {               /* o = (n * cout + co) */
+        size_t n = o / c->cout, co = o % c->cout;
+        const float *xb = c->x + n * c->cin * c->h * c->w;
+        const float *wr = c->wt + co * c->cin * c->kh * c->kw;
+        float *orow = c->out + o * c->oh * c->ow;
+        for (size_t oh = 0; oh < c->oh; oh++)
+            for (size_t ow = 0; ow < c->ow; ow++) {
+                float acc = 0.0f;
+                size_t k = 0;
+                for (size_t ci = 0; ci < c->cin; ci++)
+                    for (size_t ki = 0; ki < c->kh; ki++)
+                        for (size_t kj = 0; kj < c->kw; kj++, k++) {
+                            long ih = (long)oh * c->stride - c->pad + (long)ki;
+                            long iw = (long)ow * c->stride - c->pad + (long)kj;
+                            float v = 0.0f;
+                            if (ih >= 0 && ih < (long)c->h && iw >= 0 && iw < (long)c->w)
+                                v = xb[(ci * c->h + (size_t)ih) * c->w + (size_t)iw];
+                            acc = __builtin_fmaf(wr[k], v, acc);
+                        }
+                if (c->bias) acc += c->bias[co];
+                orow[oh * c->ow + ow] = acc;
+            }
+    }
+}
+
+int pgo_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t cout, size_t kh, size_t kw,
+               int stride, int pad, const float *x, const float *wt, const float *bias, float *out)
+{
+    if (stride <= 0) return -1;
+    long vh = (long)h + 2L * pad - (long)kh, vw = (long)w + 2L * pad - (long)kw;   /* conv.h:19-25 */
+    if (vh < 0 || vw < 0) return -1;
+    conv_ctx c = {cin, h, w, cout, kh, kw, (size_t)(vh / stride) + 1, (size_t)(vw / stride) + 1,
+                  stride, pad, x, wt, bias, out};
+    pgo_parallel_for(n * cout, conv_range, &c);
+    return 0;
+}
+
 /* ---- harness steps between the GEMMs ------------------------------------ */
 
 typedef struct { float *out; const float *a; const float *b; size_t len; } ew_ctx;

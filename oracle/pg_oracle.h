@@ -65,6 +65,10 @@ void pgo_matmul_backward(int dtype, size_t m, size_t n, size_t k,
 
 /* Row softmax over the last axis and erf-GELU, the two harness steps between
  * the GEMMs of the attention-shaped and MLP workloads. */
+/* pg_conv2d (ops/conv.c:10-146): x [n,cin,h,w], wt [cout,cin,kh,kw], bias [cout] or NULL ->
+ * out [n,cout,oh,ow], oh = (h + 2 pad - kh) / stride + 1.  Returns -1 for shapes pg_conv2d rejects. */
+int pgo_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t cout, size_t kh, size_t kw,
+               int stride, int pad, const float *x, const float *wt, const float *bias, float *out);
 void pgo_softmax_rows(float *out, const float *src, size_t rows, size_t len);
 void pgo_gelu(float *out, const float *src, size_t n);
 void pgo_gelu_grad(float *out, const float *x, const float *gy, size_t n);

@@ -150,6 +150,28 @@ def pg_linear_forward(x, weight, bias=None, relu=False, out16=None):
     return out
 
 
+def pg_conv2d(x, w, b=None, stride=1, padding=0):
+    """pg_conv2d (ops/conv.c:10-146): x [N,Cin,H,W], w [Cout,Cin,kh,kw], b [Cout] or None, f32 device tensors;
+    returns [N,Cout,OH,OW].  Raises where picograd returns NULL."""
+    _ready()
+    if x.dim() != 4 or w.dim() != 4 or x.shape[1] != w.shape[1]:
+        raise ValueError("pg_conv2d: x [N,Cin,H,W] and w [Cout,Cin,kh,kw]")
+    if b is not None and (b.dim() != 1 or b.shape[0] != w.shape[0]):
+        raise ValueError("pg_conv2d: bias [Cout]")
+    if x.dtype != torch.float32 or w.dtype != torch.float32:
+        raise TypeError("pg_conv2d: float32")
+    n, cin, h, wd = x.shape
+    cout, _, kh, kw = w.shape
+    if stride <= 0 or h + 2 * padding < kh or wd + 2 * padding < kw:
+        raise ValueError("pg_conv2d: empty output")
+    oh, ow = (h + 2 * padding - kh) // stride + 1, (wd + 2 * padding - kw) // stride + 1
+    x, w = x.contiguous(), w.contiguous()
+    out = torch.empty((n, cout, oh, ow), dtype=torch.float32, device=x.device)
+    _check(lib.pg_b200_conv2d(n, cin, h, wd, cout, kh, kw, stride, padding, x.data_ptr(), w.data_ptr(),
+                              b.contiguous().data_ptr() if b is not None else None, out.data_ptr()), "pg_conv2d")
+    return out
+
+
 def pg_attention_bmm(q, kt, v):
     """softmax-weighted product as picograd's callers chain it: pg_bmm(q, kt) -> pg_softmax(axis -1) ->
     cast to the operand dtype -> pg_bmm(., v) (ops/matmul.c:340-369, ops/activations.c:22-45), in one call.

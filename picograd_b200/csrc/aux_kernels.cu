@@ -216,6 +216,44 @@ int gelu_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
+// im2col of picograd's pg_conv2d (ops/conv.c:92-113): col[b][row][j], row = (ci*kh + ki)*kw + kj, j = oh*OW + ow,
+// zero where the window leaves the image.  One thread per element of col, j fastest (coalesced writes; reads
+// run along a row of the image).
+__global__ void im2col_kernel(const float *__restrict__ x, float *__restrict__ col, uint32_t cin, uint32_t h, uint32_t w,
+                              uint32_t kh, uint32_t kw, uint32_t oh, uint32_t ow, int stride, int pad, uint64_t total) {
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t ncols = (uint64_t)oh * ow, krows = (uint64_t)cin * kh * kw;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const uint64_t j = i % ncols, t = i / ncols, row = t % krows, b = t / krows;
+        const uint32_t o_h = (uint32_t)(j / ow), o_w = (uint32_t)(j % ow);
+        const uint32_t kj = (uint32_t)(row % kw), ki = (uint32_t)((row / kw) % kh), ci = (uint32_t)(row / ((uint64_t)kw * kh));
+        const long ih = (long)o_h * stride - pad + (long)ki, iw = (long)o_w * stride - pad + (long)kj;
+        float v = 0.0f;
+        if (ih >= 0 && ih < (long)h && iw >= 0 && iw < (long)w) v = x[((b * cin + ci) * h + (uint64_t)ih) * w + (uint64_t)iw];
+        col[i] = v;
+    }
+}
+int im2col_launch(const float *x, float *col, uint32_t batch, uint32_t cin, uint32_t h, uint32_t w, uint32_t kh, uint32_t kw,
+                  uint32_t oh, uint32_t ow, int stride, int pad, cudaStream_t s) {
+    const uint64_t total = (uint64_t)batch * cin * kh * kw * oh * ow;
+    if (!total) return ST_OK;
+    im2col_kernel<<<grid_for(total, 256), 256, 0, s>>>(x, col, cin, h, w, kh, kw, oh, ow, stride, pad, total);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+// out[r][j] += bias[r % cout] over rows of `n` elements: the bias step of pg_conv2d (ops/conv.c:127-133)
+__global__ void bias_rows_kernel(float *__restrict__ out, const float *__restrict__ bias, uint32_t cout, uint64_t n, uint64_t total) {
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+        out[i] += bias[(i / n) % cout];
+}
+int bias_rows_launch(float *out, const float *bias, uint32_t cout, uint64_t rows, uint64_t n, cudaStream_t s) {
+    if (!rows || !n) return ST_OK;
+    bias_rows_kernel<<<grid_for(rows * n, 256), 256, 0, s>>>(out, bias, cout, n, rows * n);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+
 // Bias and activation over a finished C (rows x n, leading dimension ldc), for the products whose
 // tensor-core route cannot apply them in its own epilogue (K-slices, swapped operands): picograd's
 // act_apply (backend/cpu/gemm.c:632-636) after the bias row of gemm.c:729-735.

@@ -789,6 +789,44 @@ int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t 
     return st;
 }
 
+int pg_b200_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t cout, size_t kh, size_t kw, int stride, int padding,
+                   const float *x, const float *wt, const float *bias, float *out) {
+    if (!ready()) return g.init_status;
+    if (stride <= 0 || padding < 0) { set_error("pg_conv2d: stride must be positive"); return ST_UNSUPPORTED; }
+    const long vh = (long)h + 2L * padding - (long)kh, vw = (long)w + 2L * padding - (long)kw;   // ops/conv.h:19-25
+    if (vh < 0 || vw < 0 || cin == 0 || kh == 0 || kw == 0) { set_error("pg_conv2d: empty output"); return ST_UNSUPPORTED; }
+    if (n == 0 || cout == 0) return ST_OK;
+    if (!x || !wt || !out) { set_error("null operand"); return ST_GEMM; }
+    const size_t oh = (size_t)(vh / stride) + 1, ow = (size_t)(vw / stride) + 1;
+    const size_t K = cin * kh * kw, ncols = oh * ow;
+    if (K > 0x7FFFFFFFull || ncols > 0x7FFFFFFFull || cout > 0x7FFFFFFFull || h > 0xFFFFFFFFull || w > 0xFFFFFFFFull) return ST_UNSUPPORTED;
+    // batch elements per pass: the im2col matrices of one pass stay within 512 MiB of scratch
+    const size_t per = K * ncols * 4;
+    size_t nb = per ? (512ull << 20) / per : n;
+    if (nb < 1) nb = 1;
+    if (nb > n) nb = n;
+    if (nb > 65535) nb = 65535;
+    int st = grow(g.attn_ws, align_up(nb * per, 256));
+    if (st != ST_OK) return st;
+    float *col = (float *)g.attn_ws.ptr;
+    for (size_t b0 = 0; b0 < n; b0 += nb) {
+        const size_t cur = n - b0 < nb ? n - b0 : nb;
+        st = im2col_launch(x + b0 * cin * h * w, col, (uint32_t)cur, (uint32_t)cin, (uint32_t)h, (uint32_t)w, (uint32_t)kh,
+                           (uint32_t)kw, (uint32_t)oh, (uint32_t)ow, stride, padding, g.stream);
+        if (st != ST_OK) return st;
+        // out[b] (cout x ncols) = W (cout x K, shared by the batch) * col[b] (K x ncols): f32, one chain per element
+        Problem p = {DT_F32, DT_F32, 0, 0, cur, cout, ncols, K, wt, K, 0, col, ncols, K * ncols,
+                     out + b0 * cout * ncols, ncols, cout * ncols, 0};
+        if ((st = run_problem(p)) != ST_OK) return st;
+    }
+    if (bias) {
+        st = bias_rows_launch(out, bias, (uint32_t)cout, n * cout, ncols, g.stream);
+        if (st != ST_OK) return st;
+    }
+    set_last_path("conv:im2col+simt");
+    return ST_OK;
+}
+
 int pg_b200_attention_bmm(int dtype, size_t batch, size_t seq_q, size_t seq_k, size_t d, const void *q, const void *kt,
                           const void *v, float *o) {
     if (!ready()) return g.init_status;

@@ -53,6 +53,24 @@ FUSED_CASES = [
 ]
 
 
+# pg_conv2d (ops/conv.c:10-146): (name, N, Cin, H, W, Cout, kh, kw, stride, padding, with_bias, seed)
+CONV_CASES = [
+    ("conv_2x3x7x7_k3_s1_p1_bias", 2, 3, 7, 7, 2, 3, 3, 1, 1, True, 60),       # the shape of tests/test_nn_layers.c:87-92
+    ("conv_1x4x19x23_k5x3_s2_p2_bias", 1, 4, 19, 23, 6, 5, 3, 2, 2, True, 61),
+    ("conv_3x2x40x40_k3_s1_p0_nobias", 3, 2, 40, 40, 5, 3, 3, 1, 0, False, 62),  # 1444 output pixels: two column chunks
+    ("conv_2x8x9x9_k1_s1_p0_bias", 2, 8, 9, 9, 4, 1, 1, 1, 0, True, 63),
+]
+
+
+def make_conv_inputs(case):
+    _, n, cin, h, w, cout, kh, kw, _, _, with_bias, seed = case
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-1, 1, (n, cin, h, w)).astype(np.float32)
+    wt = rng.uniform(-1, 1, (cout, cin, kh, kw)).astype(np.float32)
+    b = rng.uniform(-1, 1, cout).astype(np.float32) if with_bias else None
+    return x, wt, b
+
+
 def make_bias(n, seed):
     return np.random.default_rng(seed + 1000).uniform(-1, 1, n).astype(np.float32)
 
@@ -96,6 +114,9 @@ def main():
     # the f32 entry nn/nn.c:60,85 calls (Linear forward with and without ReLU)
     a, b = make_inputs(wl.F32, 20, 33, 300, 48)
     out["fused_f32_plain_entry_relu"] = ref.gemm_fused_ex(wl.F32, a, b, make_bias(33, 48), 1, plain_f32_entry=True)
+    for case in CONV_CASES:
+        x, wt, b = make_conv_inputs(case)
+        out[case[0]] = ref.conv2d(x, wt, b, case[8], case[9])
     # picograd's own dyadic correctness data (benchmarks/bench_gemm_cuda.c:16-65), exact in f32
     s = 64
     d = wl.dyadic(s * s).reshape(s, s)

@@ -30,6 +30,7 @@ class Oracle:
         L.pgo_bmm.argtypes = [C.c_int, _sz, _sz, _sz, _sz, _vp, _vp, _vp]
         L.pgo_matmul_backward.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp]
         L.pgo_softmax_rows.argtypes = [_vp, _vp, _sz, _sz]
+        L.pgo_conv2d.argtypes = [_sz] * 7 + [C.c_int, C.c_int, _vp, _vp, _vp, _vp]
         L.pgo_gelu.argtypes = [_vp, _vp, _sz]
         L.pgo_gelu_grad.argtypes = [_vp, _vp, _vp, _sz]
         for n in ("pgo_f32_to_bf16_n", "pgo_f32_to_f16_n", "pgo_bf16_to_f32_n", "pgo_f16_to_f32_n"):
@@ -97,6 +98,17 @@ class Oracle:
                                    _ptr(ga) if want_a else None, _ptr(gb) if want_b else None)
         return ga, gb
 
+    def conv2d(self, x, w, bias=None, stride=1, padding=0):
+        """pg_conv2d: x [N,Cin,H,W], w [Cout,Cin,kh,kw] f32 -> [N,Cout,OH,OW]."""
+        n, cin, h, wd = x.shape
+        cout, _, kh, kw = w.shape
+        oh, ow = (h + 2 * padding - kh) // stride + 1, (wd + 2 * padding - kw) // stride + 1
+        out = np.empty((n, cout, oh, ow), np.float32)
+        st = self.L.pgo_conv2d(n, cin, h, wd, cout, kh, kw, stride, padding, _ptr(x), _ptr(w),
+                               _ptr(bias) if bias is not None else None, _ptr(out))
+        assert st == 0
+        return out
+
     def softmax_rows(self, x):
         out = np.empty_like(x)
         self.L.pgo_softmax_rows(_ptr(out), _ptr(x), x.size // x.shape[-1], x.shape[-1])
@@ -135,6 +147,15 @@ class Oracle:
         return out
 
 
+class _PgTensor(C.Structure):
+    """Head of picograd's pg_tensor (core/tensor.h:21-36), enough to reach the data pointer."""
+    _fields_ = [("ndim", _sz), ("shape", _sz * 8), ("stride", _sz * 8), ("numel", _sz), ("data", _vp)]
+
+
+class _ConvCfg(C.Structure):
+    _fields_ = [("stride", C.c_int), ("padding", C.c_int)]       # ops/conv.h:7-10
+
+
 class Reference:
     """The unmodified picograd CPU library (backend/backend.h:103-136)."""
 
@@ -163,6 +184,30 @@ class Reference:
         else:
             self.L.pg_cpu_gemm_fused_ex(dtype, m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), n, bp, act)
         return c
+
+    def conv2d(self, x, w, bias=None, stride=1, padding=0):
+        """pg_conv2d (ops/conv.c:10-146) on picograd's own tensors."""
+        L = self.L
+        L.pg_tensor_from_data.restype = C.POINTER(_PgTensor)
+        L.pg_tensor_from_data.argtypes = [_sz, C.POINTER(_sz), _vp]
+        L.pg_conv2d.restype = C.POINTER(_PgTensor)
+        L.pg_conv2d.argtypes = [C.POINTER(_PgTensor)] * 3 + [_ConvCfg]
+        L.pg_tensor_free.argtypes = [C.POINTER(_PgTensor)]
+
+        def mk(a):
+            a = np.ascontiguousarray(a, np.float32)
+            return L.pg_tensor_from_data(a.ndim, (_sz * a.ndim)(*a.shape), _ptr(a))
+
+        tx, tw = mk(x), mk(w)
+        tb = mk(bias) if bias is not None else None
+        y = L.pg_conv2d(tx, tw, tb, _ConvCfg(stride, padding))
+        assert y, "pg_conv2d returned NULL"
+        t = y.contents
+        shape = tuple(t.shape[i] for i in range(t.ndim))
+        out = np.ctypeslib.as_array(C.cast(t.data, C.POINTER(C.c_float)), shape=(t.numel,)).reshape(shape).copy()
+        for h in (y, tx, tw) + ((tb,) if tb is not None else ()):
+            L.pg_tensor_free(h)
+        return out
 
     def gemm_ex(self, dtype, a, b, c=None):
         m, k = a.shape
