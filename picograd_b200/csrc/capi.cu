@@ -43,6 +43,7 @@ struct State {
     int opt_attn_q_tmem = 1;     // attention kernel: Q copied to tensor memory once per unit and read from there (0: from shared memory)
     int opt_fused_attention = 1; // 0: pg_b200_attention_bmm always runs the three-kernel chain
     DeviceBuf attn_ws;           // S and P of the chain form of pg_b200_attention_bmm
+    int opt_cluster_splitk = 1;  // K-slices of a skinny product as one cluster (reduction through distributed shared memory)
     int opt_stream_k = 0;        // stream-K for a partly filled last wave: correct, but measured 5-20 % slower
                                  // than the plain schedule on B200 (partial waves already run faster), so off
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
@@ -246,6 +247,7 @@ static int run_tc(const Problem &p) {
     t.stages = g.opt_stages; t.debug = g.opt_debug; t.l2_hints = g.opt_l2_hints; t.group_m = g.opt_group_m;
     t.stream = g.stream; t.dev_status = g.dev_status; t.prof = g.prof;
     t.allow_stream_k = g.opt_stream_k;
+    t.cluster_splitk = g.opt_cluster_splitk;
     t.counters = g.counters; t.num_counters = g.num_counters;
 
     // a batch-shared operand (stride 0) with batch > 1 cannot be a TMA dimension of stride 0
@@ -920,6 +922,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "swap_skinny")) { g.opt_swap_skinny = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "attn_q_tmem")) { g.opt_attn_q_tmem = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "fused_attention")) { g.opt_fused_attention = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "cluster_splitk")) { g.opt_cluster_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);

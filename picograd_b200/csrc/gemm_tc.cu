@@ -67,7 +67,7 @@ struct Cfg {
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
     static_assert(SUB_BYTES % 1024 == 0, "tiles must keep the 1024-byte swizzle alignment");
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
-    static_assert(STAGING ? BN >= 32 : true, "the TMA-store epilogue works on 32-column chunks");
+    static_assert(STAGING ? BN >= 16 : true, "staging area: TMA-store chunks (BN >= 32) or the cluster reduction (BN <= 32)");
 };
 
 struct TcParams {
@@ -87,6 +87,8 @@ struct TcParams {
                                   // stores, 4 = no TMEM reads, 8 = alternate accumulators, 16 = no MMAs
     uint32_t l2_hints;            // 2 bits each for A loads, B loads, C stores: 0 normal, 1 evict_first, 2 evict_last
     uint32_t c_trans;             // element (row, col) of the tile goes to C[col*ldc + row] (swapped operands)
+    uint32_t cluster_k;           // > 1: the K-slices of a tile are the CTAs of one cluster of this size; their partial
+                                  // tiles meet in the leader's shared memory and the leader writes Cout (BN <= 32)
     // fused epilogue (picograd pg_cpu_gemm_fused_ex): C = act(A*B + bias[col]); optional 16-bit copy of C
     const float *bias;
     uint32_t act;                 // 0 none, 1 relu, 2 gelu (erf form)
@@ -298,6 +300,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // timing experiments: wall-clock nanoseconds at which this CTA started / set up / ended (counters 14, 15, 7)
+    if ((p.debug & 32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 14] = globaltimer_ns();
 
     const uint32_t stage_base = smem_base;
     const uint32_t epi_base = smem_base + STAGES * C_::STAGE_BYTES;
@@ -308,6 +312,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto tmem_empty_bar = [&](uint32_t s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
     const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
     const uint32_t abort_off = (bar_base - smem_base) + 8u * (2 * STAGES + 4) + 8u;
+    const uint32_t red_bar = bar_base + 8u * (2 * STAGES + 4) + 16u;   // cluster reduction: partial tiles have landed
     volatile uint32_t *tmem_slot_gen = (volatile uint32_t *)(smem_gen + (tmem_slot - smem_base));
     volatile uint32_t *abort_flag = (volatile uint32_t *)(smem_gen + abort_off);
 
@@ -337,6 +342,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(tmem_full_bar(s), 1);
             mbar_init(tmem_empty_bar(s), EPI_WARPS * CG);
         }
+        mbar_init(red_bar, p.cluster_k > 1 ? (p.cluster_k - 1) * EPI_WARPS * 32 : 1);
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -344,9 +350,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_relinquish<CG>();
     }
     tc_fence_before();
-    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    // (a cluster of K-slices: every CTA must be running and its barriers initialised before a peer touches them)
+    if (CG == 2 || p.cluster_k > 1) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
+    if ((p.debug & 32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 7] = globaltimer_ns();
 
     // Each role loop below is executed by its whole warp with warp-uniform state; the instructions
     // that must come from one thread (TMA, tcgen05.mma, tcgen05.commit, barrier arrives) sit under
@@ -529,7 +537,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t acc = 0, acc_phase = 0;
         uint32_t buf = 0;
         bool ok = true;
-        const bool fused = p.splits > 1 && p.Cout != nullptr;
+        const bool cluster_mode = CG == 1 && BN <= 32 && STAGING && p.cluster_k > 1;
+        const bool fused = p.splits > 1 && p.Cout != nullptr && !cluster_mode;
         const uint64_t pol_c = l2_policy((int)((p.l2_hints >> 4) & 3u));
         const bool prof = (p.debug & 32u) != 0 && ew == 0;
         long long te_wait = 0, te_ld = 0, te_math = 0, te_store = 0, last_e3 = 0;
@@ -559,8 +568,64 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             constexpr uint32_t TILE_ELEMS = BM_CTA * CG * BN;
             const uint32_t lrow0 = cta_rank * BM_CTA + q * 32;              // tile-local first row of this warp
             float *ws_slice = partial ? p.ws + (uint64_t)(w.ws_slice0 + w.split) * TILE_ELEMS : nullptr;
+            if constexpr (CG == 1 && BN <= 32 && STAGING) {
+                if (cluster_mode) {
+                    // Split-K inside a cluster: CTA r of the cluster holds K-slice r of this tile (one chunk of
+                    // W = BN columns per warp).  Slices 1.. write their 32 x W partial sums into the leader's
+                    // staging area through distributed shared memory and arrive on its barrier; the leader adds
+                    // them to its own registers in slice order and writes C.  No global round trip, no atomics.
+                    static_assert(CHUNKS == 1, "one chunk per warp");
+                    const uint32_t rank = cluster_ctarank();
+                    uint32_t v[32];
+                    if constexpr (W == 32) tmem_ld32(taddr, v); else tmem_ld16(taddr, v);
+                    tmem_ld_wait();
+                    constexpr uint32_t SLOT = 32 * W * 4;                 // one warp's partial of one slice
+                    if (rank != 0) {
+                        const uint32_t dst = mapa(epi_base + ((rank - 1) * 4 + q) * SLOT + lane * (W * 4), 0);
+#pragma unroll
+                        for (uint32_t j = 0; j < W / 4; ++j) st_cluster_v4(dst + 16 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        mbar_arrive_release_cluster(mapa(red_bar, 0));
+                    } else {
+                        const uint64_t t0 = globaltimer_ns();
+                        bool landed = true;
+                        while (!__all_sync(0xffffffffu, mbar_try_acquire_cluster(red_bar, 0))) {
+                            uint32_t give_up = *abort_flag;
+                            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) give_up = 1;
+                            if (__any_sync(0xffffffffu, give_up)) {
+                                if (lane == 0) { *abort_flag = 1; atomicOr(p.status, DEV_ERR_WAIT_TMEM_FULL); }
+                                landed = false;
+                                break;
+                            }
+                        }
+                        if (landed && !(p.debug & 2u)) {
+                            for (uint32_t r = 1; r < p.cluster_k; ++r) {
+                                const uint4 *src = reinterpret_cast<const uint4 *>(smem_gen + (epi_base - smem_base) + ((r - 1) * 4 + q) * SLOT + lane * (W * 4));
+#pragma unroll
+                                for (uint32_t j = 0; j < W / 4; ++j) {
+                                    const uint4 t4 = src[j];
+                                    v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + __uint_as_float(t4.x));
+                                    v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + __uint_as_float(t4.y));
+                                    v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + __uint_as_float(t4.z));
+                                    v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + __uint_as_float(t4.w));
+                                }
+                            }
+                            if (row < p.M) {
+                                float *out = p.Cout + (uint64_t)w.batch * p.M * p.ldc_out;
+#pragma unroll
+                                for (uint32_t j = 0; j < W; ++j) {
+                                    if (col0 + j < p.N) {
+                                        float *d = p.c_trans ? out + (uint64_t)(col0 + j) * p.ldc_out + row : out + (uint64_t)row * p.ldc_out + col0 + j;
+                                        *d = p.accumulate ? *d + __uint_as_float(v[j]) : __uint_as_float(v[j]);
+                                    }
+                                }
+                            }
+                        }
+                        if (!landed) ok = false;
+                    }
+                }
+            }
 #pragma unroll 1
-            for (uint32_t c = half; c < CHUNKS; c += CSTEP) {
+            for (uint32_t c = half; c < CHUNKS && !cluster_mode; c += CSTEP) {
                 const uint32_t col = col0 + c * W;
                 if (col >= p.N || row0 >= p.M) break;   // nothing of this warp's slab is inside C
                 if (p.debug & 4u) break;
@@ -774,6 +839,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after();
         tmem_dealloc<CG>(tmem_base, C_::TMEM_COLS);
     }
+    if ((p.debug & 32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 15] = globaltimer_ns();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -832,8 +898,8 @@ static const TcConfig g_cfgs[] = {
     PG_TC_CFG("1cta_128x256_k128", 1, 256, 2, true, 4, 2, false),
     PG_TC_CFG("2cta_256x256_s7", 2, 256, 1, false, 4, 2, false),
     PG_TC_CFG("2cta_256x256_e8", 2, 256, 1, true, 8, 2, false),   // store-bound shapes (small K): 8 epilogue warps
-    PG_TC_CFG("1cta_128x16_t", 1, 16, 1, false, 4, 2, false),     // swapped operands for M <= 16
-    PG_TC_CFG("1cta_128x32_t", 1, 32, 1, false, 4, 2, false),     // swapped operands for M <= 32
+    PG_TC_CFG("1cta_128x16_t", 1, 16, 1, true, 4, 2, false),      // swapped operands for M <= 16 (staging area = cluster reduction)
+    PG_TC_CFG("1cta_128x32_t", 1, 32, 1, true, 4, 2, false),      // swapped operands for M <= 32
 };
 constexpr int NUM_CFGS = sizeof(g_cfgs) / sizeof(g_cfgs[0]);
 
@@ -1195,6 +1261,12 @@ int tc_gemm_launch(const TcGemm &g) {
     }
     p.C = g.C; p.ldc = g.ldc; p.c_stride = g.c_stride;
     p.c_trans = g.c_trans ? 1u : 0u;
+    // K-slices as the CTAs of a cluster, reduced through distributed shared memory: narrow tiles whose partial
+    // sums of all slices fit in the leader's 32 KB staging area (128 x BN x 4 bytes per slice beyond the first)
+    p.cluster_k = 0;
+    if (g.cluster_splitk && c.cg == 1 && c.staging && c.bn <= 32 && g.Cout && g.batch == 1 && splits >= 2 && splits <= 8 &&
+        (splits - 1) * BM_CTA * c.bn * 4 <= c.ew * 2 * EPI_BUF_BYTES && !(g.debug & 5))
+        p.cluster_k = splits;
     p.bias = g.bias; p.act = (uint32_t)g.act; p.c16 = (unsigned short *)g.c16; p.ld16 = g.ld16; p.dtype16 = (uint32_t)g.dtype16;
     p.bias_vec4 = aligned16(g.bias) ? 1u : 0u;
     p.c16_vec = (g.c16 && aligned16(g.c16) && g.ld16 % 8 == 0) ? 1u : 0u;
@@ -1203,7 +1275,7 @@ int tc_gemm_launch(const TcGemm &g) {
         return ST_UNSUPPORTED;
     }
     p.Cout = (splits > 1) ? g.Cout : nullptr; p.ldc_out = g.ldc_out; p.counters = g.counters;
-    if (p.Cout) {
+    if (p.Cout && !p.cluster_k) {
         const uint64_t slabs = (uint64_t)p.m_tiles * p.n_tiles * c.cg * c.ew;
         if (!g.counters || slabs > g.num_counters) {
             set_error("tc_gemm: %llu slab counters needed for the fused split-K reduction, %u available",
@@ -1262,6 +1334,7 @@ int tc_gemm_launch(const TcGemm &g) {
         }
     }
 
+    if (p.cluster_k) clusters = (uint32_t)units;      // one unit per CTA; consecutive CTAs = the slices of one tile
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(clusters * c.cg, 1, 1);
     lc.blockDim = dim3(c.threads, 1, 1);
@@ -1269,7 +1342,7 @@ int tc_gemm_launch(const TcGemm &g) {
     lc.stream = g.stream;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = (unsigned)c.cg;
+    at[0].val.clusterDim.x = p.cluster_k ? p.cluster_k : (unsigned)c.cg;
     at[0].val.clusterDim.y = 1;
     at[0].val.clusterDim.z = 1;
     lc.attrs = at;
@@ -1283,7 +1356,7 @@ int tc_gemm_launch(const TcGemm &g) {
     }
     note_launch();
     set_last_path("tc:%s%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
-                  p.Cout ? ":fused" : "", stream_k ? ":streamk" : "");
+                  p.cluster_k ? ":cluster" : (p.Cout ? ":fused" : ""), stream_k ? ":streamk" : "");
     return ST_OK;
 }
 

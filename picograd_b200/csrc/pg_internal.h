@@ -55,6 +55,7 @@ struct TcGemm {
     uint64_t ldc_out;
     uint32_t *counters;        // zeroed device words, one per (tile, CTA, epilogue warp)
     uint32_t num_counters;
+    int cluster_splitk;        // may run the K-slices of a narrow tile as one cluster, summed through distributed shared memory
     int allow_stream_k;        // may deal the K blocks of a partly filled last wave out to all clusters
     uint32_t splits;           // >1: split-K, slice s goes to C + s*c_stride (batch must be 1)
     int force_cfg;             // -1 = choose; else index into the config table

@@ -53,6 +53,24 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive on a barrier of another CTA of the cluster, publishing this thread's earlier writes to that CTA's
+// shared memory (release at cluster scope); bar is a shared::cluster address.
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// One try of a wait whose completion makes other CTAs' writes to this CTA's shared memory visible.
+__device__ __forceinline__ uint32_t mbar_try_acquire_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 // Upper bound, in nanoseconds, that the hardware may keep a waiting thread suspended inside one
 // try_wait before it returns "not yet" (a hint; the wait still ends as soon as the phase completes).
 constexpr uint32_t g_suspend_hint_ns = PG_SUSPEND_HINT_NS;
