@@ -89,46 +89,57 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
         if (a_k_contig) { a_kk[r] = idx % SK; a_mm[r] = idx / SK; } else { a_mm[r] = idx % TILE; a_kk[r] = idx / TILE; }
         if (b_n_contig) { b_nn[r] = idx % TILE; b_kk[r] = idx / TILE; } else { b_kk[r] = idx % SK; b_nn[r] = idx / SK; }
     }
-    float ra[PER], rb[PER];
-    auto fetch = [&](uint32_t k0) {
+    // D K-slabs are kept in flight in registers: the loads of slab i + D are issued while slab i is being
+    // multiplied, so a load has D slabs of arithmetic to arrive (a 64-wide tile leaves one CTA of 8 warps per
+    // SM on small products: nothing else hides the latency of L2).
+    constexpr int D = TILE == 64 ? 4 : 1;
+    float ra[D][PER], rb[D][PER];
+    auto fetch = [&](float (&qa)[PER], float (&qb)[PER], uint32_t k0) {
 #pragma unroll
         for (int r = 0; r < PER; ++r) {
             const long long gm = m0 + a_mm[r], gka = (long long)k0 + a_kk[r];
-            ra[r] = (gm < p.M && gka < p.K) ? load_as_f32(p.A, a_off + gm * p.a_rs + gka * p.a_cs, p.dtype_a) : 0.0f;
+            qa[r] = (gm < p.M && gka < p.K) ? load_as_f32(p.A, a_off + gm * p.a_rs + gka * p.a_cs, p.dtype_a) : 0.0f;
             const long long gn = n0 + b_nn[r], gkb = (long long)k0 + b_kk[r];
-            rb[r] = (gn < p.N && gkb < p.K) ? load_as_f32(p.B, b_off + gkb * p.b_rs + gn * p.b_cs, p.dtype_b) : 0.0f;
+            qb[r] = (gn < p.N && gkb < p.K) ? load_as_f32(p.B, b_off + gkb * p.b_rs + gn * p.b_cs, p.dtype_b) : 0.0f;
         }
     };
 
-    if (p.K) fetch(0);
-    for (uint32_t k0 = 0; k0 < p.K; k0 += SK) {
 #pragma unroll
-        for (int r = 0; r < PER; ++r) {
-            As[a_kk[r]][a_mm[r]] = ra[r];
-            Bs[b_kk[r]][b_nn[r]] = rb[r];
-        }
-        __syncthreads();
-        if (k0 + SK < p.K) fetch(k0 + SK);
-        // stop at the true K so that the chain of each element is exactly its K fused multiply-adds
-        const int kmax = (p.K - k0) < (uint32_t)SK ? (int)(p.K - k0) : SK;
-#pragma unroll 4
-        for (int kk = 0; kk < kmax; ++kk) {
-            // a thread's T rows (columns) are groups of four, 64 apart: the 16 threads of a half-warp
-            // then read 256 contiguous bytes per 16-byte load — no shared-memory bank conflict
-            float a[T], b[T];
+    for (int d = 0; d < D; ++d)
+        if ((uint32_t)(d * SK) < p.K) fetch(ra[d], rb[d], d * SK);
+    for (uint32_t kbase = 0; kbase < p.K; kbase += D * SK) {
 #pragma unroll
-            for (int i = 0; i < T; i += 4) {
-                const float4 va = *reinterpret_cast<const float4 *>(&As[kk][ty * 4 + i * 16]);
-                a[i] = va.x; a[i + 1] = va.y; a[i + 2] = va.z; a[i + 3] = va.w;
-                const float4 vb = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4 + i * 16]);
-                b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
+        for (int d = 0; d < D; ++d) {
+            const uint32_t k0 = kbase + d * SK;
+            if (k0 >= p.K) break;
+#pragma unroll
+            for (int r = 0; r < PER; ++r) {
+                As[a_kk[r]][a_mm[r]] = ra[d][r];
+                Bs[b_kk[r]][b_nn[r]] = rb[d][r];
             }
+            __syncthreads();
+            if (k0 + D * SK < p.K) fetch(ra[d], rb[d], k0 + D * SK);
+            // stop at the true K so that the chain of each element is exactly its K fused multiply-adds
+            const int kmax = (p.K - k0) < (uint32_t)SK ? (int)(p.K - k0) : SK;
+#pragma unroll 4
+            for (int kk = 0; kk < kmax; ++kk) {
+                // a thread's T rows (columns) are groups of four, 64 apart: the 16 threads of a half-warp
+                // then read 256 contiguous bytes per 16-byte load — no shared-memory bank conflict
+                float a[T], b[T];
 #pragma unroll
-            for (int i = 0; i < T; ++i)
+                for (int i = 0; i < T; i += 4) {
+                    const float4 va = *reinterpret_cast<const float4 *>(&As[kk][ty * 4 + i * 16]);
+                    a[i] = va.x; a[i + 1] = va.y; a[i + 2] = va.z; a[i + 3] = va.w;
+                    const float4 vb = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4 + i * 16]);
+                    b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
+                }
 #pragma unroll
-                for (int j = 0; j < T; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+                for (int i = 0; i < T; ++i)
+#pragma unroll
+                    for (int j = 0; j < T; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
 
     float *Cb = p.C + (long long)bz * p.c_bs;
