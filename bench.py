@@ -272,7 +272,7 @@ def run_ours(args, rank, world):
                          "frac": tflops / world / burst,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this
                          # size, from the ncu capture summarised in profiles/tc_gemm_kernel_bf16_8192.md
-                         "traffic": 1.388e9 if world == 1 else None, "algorithmic_bytes": 536870912 // 1,
+                         "traffic": 1.305e9 if world == 1 else None, "algorithmic_bytes": 536870912 // 1,
                          "peak_source": f"{src} burst bf16 (kernel timed alone, back to back)",
                          "frac_of_sustained": tflops / world / sustained},
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": int((M * K + K * n_loc) * 2),

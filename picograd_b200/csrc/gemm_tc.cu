@@ -1255,6 +1255,9 @@ int tc_gemm_launch(const TcGemm &g) {
         for (uint32_t gm = 1; gm <= 32 && gm <= p.m_tiles; ++gm) {
             double cols = (double)slots / gm;
             double cost = gm * (double)bm + cols * (double)c.bn;
+            // a group height that does not divide the M tiles leaves a flatter last group, whose waves touch more
+            // columns of B (measured at 8192^3: 9 rows -> 1.11 GB of DRAM reads, 8 rows -> 1.04 GB, and 1.3 % faster)
+            if (p.m_tiles % gm) cost *= 1.05;
             if (cost < best_cost) { best_cost = cost; best = gm; }
         }
         p.group_m = best;
