@@ -161,12 +161,13 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
 
 // ---------------------------------------------------------------------------------------------
 // f32 x f32, both operands row-major with unit column stride and 16-byte aligned rows (the shape of
-// pg_gemm): 128 x 128 tile, K slabs of 16, 16-byte global loads, double-buffered shared memory (one
+// pg_gemm): 128 x 128 tile (64 x 64 for small products, which then fill more SMs), K slabs of 16, 16-byte global loads, double-buffered shared memory (one
 // barrier per slab), 8 x 8 outputs per thread.  Same arithmetic as above: one fmaf chain per element,
 // k ascending (zero-filled slab tails add exact zeros).
 // ---------------------------------------------------------------------------------------------
+template <int TILE>
 __global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
-    constexpr int TILE = 128, LD = TILE + 4;
+    constexpr int LD = TILE + 4, T = TILE / 16, NV = TILE / 64;     // NV 16-byte vectors of each operand per thread and slab
     __shared__ __align__(16) float As[2][SK][LD];
     __shared__ __align__(16) float Bs[2][SK][LD];
     const int tid = threadIdx.x;
@@ -176,106 +177,127 @@ __global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
     const float *A = reinterpret_cast<const float *>(p.A) + (long long)bz * p.a_bs;
     const float *B = reinterpret_cast<const float *>(p.B) + (long long)bz * p.b_bs;
 
-    float acc[8][8];
+    float acc[T][T];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < T; ++j) {
         const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
         const float b0 = (p.bias && gn < p.N) ? p.bias[gn] : 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i][j] = b0;
+        for (int i = 0; i < T; ++i) acc[i][j] = b0;
     }
 
-    // staging roles: A as 2 x float4 along k (rows a_r, a_r + 64), B as 2 x float4 along n (k rows b_k, b_k + 8)
+    // staging roles: A as float4 along k (rows a_r, a_r + 64), B as float4 along n (k rows b_k, b_k + BKS)
+    constexpr int BROW = TILE / 4;                 // float4 per k-row of B
+    constexpr int BKS = 256 / BROW;                // k-rows of B covered by one pass of the CTA
     const int a_r = tid >> 2, a_kq = (tid & 3) * 4;
-    const int b_k = tid >> 5, b_nq = (tid & 31) * 4;
-    float4 ra[2], rb[2];
-    auto fetch = [&](uint32_t k0) {
+    const int b_k = tid / BROW, b_nq = (tid % BROW) * 4;
+    // R register sets: the loads of slab s + R are issued while slab s is multiplied and slab s + 1 already sits
+    // in the other shared-memory buffer.  R = 2 measured slower than R = 1 on the 64-wide tile (29.2 vs 25.0 us
+    // at 512^3), so one set it is.
+    constexpr int R = 1;
+    float4 ra[R][NV], rb[R][NV];
+    auto fetch = [&](float4 (&qa)[NV], float4 (&qb)[NV], uint32_t k0) {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const long long gm = m0 + a_r + 64 * i, gk = (long long)k0 + a_kq;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (gm < p.M) {
+            if (gm < p.M && gk < p.K) {
                 const float *src = A + gm * p.a_rs + gk;
                 if (gk + 3 < p.K) v = *reinterpret_cast<const float4 *>(src);
                 else {
-                    if (gk + 0 < p.K) v.x = src[0];
+                    v.x = src[0];
                     if (gk + 1 < p.K) v.y = src[1];
                     if (gk + 2 < p.K) v.z = src[2];
                 }
             }
-            ra[i] = v;
-            const long long gkb = (long long)k0 + b_k + 8 * i, gn = n0 + b_nq;
+            qa[i] = v;
+            const long long gkb = (long long)k0 + b_k + BKS * i, gn = n0 + b_nq;
             float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (gkb < p.K) {
+            if (gkb < p.K && gn < p.N) {
                 const float *src = B + gkb * p.b_rs + gn;
                 if (gn + 3 < p.N) w = *reinterpret_cast<const float4 *>(src);
                 else {
-                    if (gn + 0 < p.N) w.x = src[0];
+                    w.x = src[0];
                     if (gn + 1 < p.N) w.y = src[1];
                     if (gn + 2 < p.N) w.z = src[2];
                 }
             }
-            rb[i] = w;
+            qb[i] = w;
         }
     };
-    auto stash = [&](int buf) {
+    auto stash = [&](const float4 (&qa)[NV], const float4 (&qb)[NV], int buf) {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            As[buf][a_kq + 0][a_r + 64 * i] = ra[i].x;
-            As[buf][a_kq + 1][a_r + 64 * i] = ra[i].y;
-            As[buf][a_kq + 2][a_r + 64 * i] = ra[i].z;
-            As[buf][a_kq + 3][a_r + 64 * i] = ra[i].w;
-            *reinterpret_cast<float4 *>(&Bs[buf][b_k + 8 * i][b_nq]) = rb[i];
+        for (int i = 0; i < NV; ++i) {
+            As[buf][a_kq + 0][a_r + 64 * i] = qa[i].x;
+            As[buf][a_kq + 1][a_r + 64 * i] = qa[i].y;
+            As[buf][a_kq + 2][a_r + 64 * i] = qa[i].z;
+            As[buf][a_kq + 3][a_r + 64 * i] = qa[i].w;
+            *reinterpret_cast<float4 *>(&Bs[buf][b_k + BKS * i][b_nq]) = qb[i];
         }
     };
-
-    int buf = 0;
-    if (p.K) { fetch(0); stash(0); }
-    __syncthreads();
-    for (uint32_t k0 = 0; k0 < p.K; k0 += SK) {
-        const bool more = k0 + SK < p.K;
-        if (more) fetch(k0 + SK);
+    auto multiply = [&](int buf) {
 #pragma unroll
         for (int kk = 0; kk < SK; ++kk) {
-            float a[8], b[8];
+            float a[T], b[T];
 #pragma unroll
-            for (int i = 0; i < 8; i += 4) {
+            for (int i = 0; i < T; i += 4) {
                 const float4 va = *reinterpret_cast<const float4 *>(&As[buf][kk][ty * 4 + i * 16]);
                 a[i] = va.x; a[i + 1] = va.y; a[i + 2] = va.z; a[i + 3] = va.w;
                 const float4 vb = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4 + i * 16]);
                 b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < T; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < T; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
         }
-        if (more) stash(buf ^ 1);
-        __syncthreads();
-        buf ^= 1;
+    };
+
+    // slab s is multiplied out of shared buffer s % 2; register set (s + 1) % R holds slab s + 1 on entry to
+    // iteration s, is stored to the other buffer and refilled with slab s + 1 + R
+    if (p.K) {
+        fetch(ra[0], rb[0], 0);
+        stash(ra[0], rb[0], 0);
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            if ((uint32_t)((r + 1) * SK) < p.K) fetch(ra[(r + 1) % R], rb[(r + 1) % R], (r + 1) * SK);
+    }
+    __syncthreads();
+    for (uint32_t k0 = 0; k0 < p.K; k0 += R * SK) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint32_t ks = k0 + r * SK;                 // slab s = ks / SK, s % R == r
+            if (ks >= p.K) break;
+            const int buf = (ks / SK) & 1, set = (r + 1) % R;
+            const bool more = ks + SK < p.K;
+            if (more) stash(ra[set], rb[set], buf ^ 1);
+            if (ks + (1 + R) * SK < p.K) fetch(ra[set], rb[set], ks + (1 + R) * SK);
+            multiply(buf);
+            __syncthreads();
+        }
     }
 
     float *Cb = p.C + (long long)bz * p.c_bs;
     const bool vec = (p.ldc % 4 == 0) && (((uintptr_t)Cb & 15) == 0) && !p.accumulate;
     if (p.act) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < T; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[i][j] = simt_act(acc[i][j], p.act);
+            for (int j = 0; j < T; ++j) acc[i][j] = simt_act(acc[i][j], p.act);
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < T; ++i) {
         const long long gm = m0 + ty * 4 + (i / 4) * 64 + (i % 4);
         if (gm >= p.M) continue;
         if (p.c16) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < T; ++j) {
                 const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
                 if (gn < p.N) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn] = simt_to16(acc[i][j], p.dtype16);
             }
         }
 #pragma unroll
-        for (int jh = 0; jh < 2; ++jh) {
+        for (int jh = 0; jh < T / 4; ++jh) {
             const long long gn = n0 + tx * 4 + jh * 64;
             float *dst = Cb + gm * p.ldc + gn;
             if (vec && gn + 3 < p.N) {
@@ -314,10 +336,11 @@ int simt_gemm_launch(const SimtGemm &g) {
         if (q.c16) q.c16 = p.c16 + (long long)done * p.c16_bs;
         dim3 grid((g.N + tile - 1) / tile, (g.M + tile - 1) / tile, nb);
         if (grid.y > 65535u) { set_error("simt gemm: M too large for one launch"); return ST_UNSUPPORTED; }
-        const bool nn_f32 = big && g.dtype_a == DT_F32 && g.dtype_b == DT_F32 && g.a_cs == 1 && g.b_cs == 1 &&
+        const bool nn_f32 = g.dtype_a == DT_F32 && g.dtype_b == DT_F32 && g.a_cs == 1 && g.b_cs == 1 &&
                             g.a_rs % 4 == 0 && g.b_rs % 4 == 0 && g.a_bs % 4 == 0 && g.b_bs % 4 == 0 &&
                             (((uintptr_t)g.A | (uintptr_t)g.B) & 15) == 0;
-        if (nn_f32) sgemm_nn_kernel<<<grid, 256, 0, g.stream>>>(q);
+        if (nn_f32 && big) sgemm_nn_kernel<128><<<grid, 256, 0, g.stream>>>(q);
+        else if (nn_f32) sgemm_nn_kernel<64><<<grid, 256, 0, g.stream>>>(q);
         else if (big) simt_gemm_kernel<128><<<grid, 256, 0, g.stream>>>(q);
         else simt_gemm_kernel<64><<<grid, 256, 0, g.stream>>>(q);
         cudaError_t e = cudaGetLastError();
