@@ -113,6 +113,12 @@ PG_B200_API int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int 
                          const void *b, size_t ldb, size_t stride_b,
                          float *c, size_t ldc, size_t stride_c, int accumulate);
 
+/* permute_copy of pg_tensordot (ops/matmul.c:21-42): dst (contiguous, dimension d of size shape[perm[d]])
+ * receives src (contiguous, `shape`) with its dimensions reordered; dtype gives the element size.  Device
+ * pointers, ndim <= 8 (picograd's PG_MAX_NDIM).  pg_tensordot is this on both operands, then pg_matmul. */
+PG_B200_API int pg_b200_permute_copy(int dtype, size_t ndim, const size_t *shape, const size_t *perm,
+                         const void *src, void *dst);
+
 /* bwd_matmul (autograd/autograd.c:561-706) for a [batch,m,k] x [batch,k,n]
  * (or shared [k,n] when b_batched == 0) product: ga += g * B^T, gb += A^T * g.
  * a, b in `dtype`; g, ga, gb f32; ga / gb may be NULL. Device pointers. */

@@ -294,6 +294,22 @@ def pg_bmm(a, b, dtype=None):
     return out
 
 
+def _permute_copy(t, perm):
+    """permute_copy (ops/matmul.c:21-42) with the library's own kernel: a new contiguous tensor whose dimension d
+    is dimension perm[d] of t."""
+    _ready()
+    import ctypes
+    t = t.contiguous()
+    if list(perm) == list(range(t.dim())):
+        return t
+    nd = t.dim()
+    out = torch.empty([t.shape[d] for d in perm], dtype=t.dtype, device=t.device)
+    arr = ctypes.c_size_t * nd
+    _check(lib.pg_b200_permute_copy(_TORCH2PG[t.dtype], nd, arr(*t.shape), arr(*perm), t.data_ptr(), out.data_ptr()),
+           "pg_b200_permute_copy")
+    return out
+
+
 def pg_tensordot(a, b, axes_a, axes_b, dtype=None):
     """pg_tensordot (ops/matmul.c:407-490): contract axes_a of a with axes_b of b — permute to
     (free, contracted) x (contracted, free), reshape to 2-D, matmul, reshape back."""
@@ -312,13 +328,20 @@ def pg_tensordot(a, b, axes_a, axes_b, dtype=None):
     kdim = 1
     for d in axes_a:
         kdim *= a.shape[d]
-    ra = a.permute(pa).contiguous().reshape(-1, kdim)
-    rb = b.permute(pb).contiguous().reshape(kdim, -1)
+    ra = _permute_copy(a, pa).reshape(-1, kdim)
+    rb = _permute_copy(b, pb).reshape(kdim, -1)
     rc = pg_matmul(ra, rb, dtype=dtype)
     if rc is None:
         return None
     fshape = free_a + free_b
     return rc.reshape(fshape if fshape else [1])
+
+
+def _zeros_f32(shape, device):
+    """A zeroed f32 gradient (pg_backward zeroes them, autograd.c:2490-2492), filled by the library's kernel."""
+    t = torch.empty(tuple(shape), dtype=torch.float32, device=device)
+    _check(lib.pg_b200_fill_f32(t.data_ptr(), 0.0, t.numel()), "pg_b200_fill_f32")
+    return t
 
 
 def pg_matmul_backward(a, b, g, need_a=True, need_b=True, ga=None, gb=None, dtype=None):
@@ -335,9 +358,9 @@ def pg_matmul_backward(a, b, g, need_a=True, need_b=True, ga=None, gb=None, dtyp
         batch *= d
     b_batched = b.dim() > 2
     if need_a and ga is None:
-        ga = torch.zeros(a.shape, dtype=torch.float32, device=a.device)
+        ga = _zeros_f32(a.shape, a.device)
     if need_b and gb is None:
-        gb = torch.zeros(b.shape, dtype=torch.float32, device=a.device)
+        gb = _zeros_f32(b.shape, a.device)
     _check(lib.pg_b200_matmul_backward(dt, batch, m, n, k, a.data_ptr(), b.data_ptr(), int(b_batched),
                                        g.data_ptr(), ga.data_ptr() if need_a else None,
                                        gb.data_ptr() if need_b else None), "pg_b200_matmul_backward")

@@ -216,6 +216,55 @@ int gelu_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
+// permute_copy of picograd's pg_tensordot (ops/matmul.c:21-42): dst, contiguous with shape out_shape, takes
+// element (c0, .., c_{nd-1}) from src offset sum(c_d * src_stride[d]) (the strides of the source dimension that
+// lands in position d).  One thread per destination element: writes coalesced, reads strided; when the last
+// dimension keeps its place the reads run along it too.
+struct PermuteParams {
+    uint32_t ndim;
+    uint64_t out_shape[8];
+    uint64_t src_stride[8];
+    uint64_t total;
+};
+template <typename T>
+__global__ void permute_copy_kernel(const T *__restrict__ src, T *__restrict__ dst, const PermuteParams p) {
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += step) {
+        uint64_t rest = i, off = 0;
+#pragma unroll
+        for (int d = 7; d >= 0; --d) {
+            if (d < (int)p.ndim) {
+                const uint64_t c = rest % p.out_shape[d];
+                rest /= p.out_shape[d];
+                off += c * p.src_stride[d];
+            }
+        }
+        dst[i] = src[off];
+    }
+}
+int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t ndim, const uint64_t *shape, const uint32_t *perm,
+                        cudaStream_t s) {
+    if (ndim == 0 || ndim > 8 || (elem_size != 2 && elem_size != 4)) return ST_UNSUPPORTED;
+    PermuteParams p = {};
+    p.ndim = ndim;
+    uint64_t stride[8], run = 1;
+    for (int d = (int)ndim - 1; d >= 0; --d) { stride[d] = run; run *= shape[d]; }
+    uint32_t seen = 0;
+    p.total = 1;
+    for (uint32_t d = 0; d < ndim; ++d) {
+        if (perm[d] >= ndim || (seen >> perm[d]) & 1u) return ST_UNSUPPORTED;
+        seen |= 1u << perm[d];
+        p.out_shape[d] = shape[perm[d]];
+        p.src_stride[d] = stride[perm[d]];
+        p.total *= shape[perm[d]];
+    }
+    if (!p.total) return ST_OK;
+    if (elem_size == 4) permute_copy_kernel<uint32_t><<<grid_for(p.total, 256), 256, 0, s>>>((const uint32_t *)src, (uint32_t *)dst, p);
+    else permute_copy_kernel<uint16_t><<<grid_for(p.total, 256), 256, 0, s>>>((const uint16_t *)src, (uint16_t *)dst, p);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+
 // im2col of picograd's pg_conv2d (ops/conv.c:92-113): col[b][row][j], row = (ci*kh + ki)*kw + kj, j = oh*OW + ow,
 // zero where the window leaves the image.  One thread per element of col, j fastest (coalesced writes; reads
 // run along a row of the image).

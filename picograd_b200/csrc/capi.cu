@@ -791,6 +791,16 @@ int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t 
     return st;
 }
 
+int pg_b200_permute_copy(int dtype, size_t ndim, const size_t *shape, const size_t *perm, const void *src, void *dst) {
+    if (!ready()) return g.init_status;
+    if (ndim == 0 || ndim > 8 || !shape || !perm) { set_error("pg_b200_permute_copy: 1 to 8 dimensions"); return ST_UNSUPPORTED; }
+    uint64_t sh[8]; uint32_t pm[8];
+    for (size_t d = 0; d < ndim; ++d) { sh[d] = shape[d]; pm[d] = (uint32_t)perm[d]; }
+    const int st = permute_copy_launch(src, dst, esize(dtype), (uint32_t)ndim, sh, pm, g.stream);
+    if (st == ST_UNSUPPORTED) set_error("pg_b200_permute_copy: perm is not a permutation of 0..ndim-1");
+    return st;
+}
+
 int pg_b200_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t cout, size_t kh, size_t kw, int stride, int padding,
                    const float *x, const float *wt, const float *bias, float *out) {
     if (!ready()) return g.init_status;

@@ -132,6 +132,8 @@ int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, uint16_t
 int im2col_launch(const float *x, float *col, uint32_t batch, uint32_t cin, uint32_t h, uint32_t w, uint32_t kh, uint32_t kw,
                   uint32_t oh, uint32_t ow, int stride, int pad, cudaStream_t s);
 int bias_rows_launch(float *out, const float *bias, uint32_t cout, uint64_t rows, uint64_t n, cudaStream_t s);
+int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t ndim, const uint64_t *shape, const uint32_t *perm,
+                        cudaStream_t s);
 int fill_f32_launch(float *dst, float v, uint64_t n, cudaStream_t s);
 
 void set_error(const char *fmt, ...);

@@ -341,6 +341,20 @@ def test_tensordot(pg):
     assert np.all(np.abs(to_host(y) - ref) <= 1e-4 * (1 + np.abs(ref)))
 
 
+@pytest.mark.parametrize("shape,perm", [((3, 4, 5), (2, 0, 1)), ((7, 33), (1, 0)), ((2, 3, 4, 5, 6), (4, 0, 3, 1, 2)),
+                                        ((5, 1, 9), (1, 2, 0)), ((64, 130), (0, 1))])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_permute_copy_is_the_librarys_own_kernel(pg, shape, perm, dt):
+    """permute_copy of pg_tensordot (ops/matmul.c:21-42): bytes moved, nothing computed -> equality."""
+    from picograd_b200 import backend
+    x = torch.arange(int(np.prod(shape)), device="cuda", dtype=torch.float32).reshape(shape).to(dt)
+    n0 = pg.launch_count()
+    y = backend._permute_copy(x, list(perm)); pg.pg_dev_sync()
+    if list(perm) != list(range(len(shape))):
+        assert pg.launch_count() == n0 + 1
+    assert y.is_contiguous() and torch.equal(y, x.permute(perm))
+
+
 def test_config4_attention_shaped_bmm(pg, oracle):
     """Reduced config 4 (batch 4, seq 256, d 128).  Each GEMM is checked on identical input bytes:
     P = bf16(softmax(S)) is produced once (on the device) and fed to both sides."""
