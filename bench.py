@@ -362,9 +362,13 @@ def run_other_config(args):
 
         dy = torch.ones((8192, 4096), dtype=torch.float32, device="cuda")     # loss = sum(y): its gradient, made once
 
+        h = torch.empty((8192, 16384), dtype=torch.float32, device="cuda")
+        a16 = torch.empty((8192, 16384), dtype=torch.bfloat16, device="cuda")
+
         def fn():
-            h = pg.pg_matmul(xd, w1d)
-            a16 = ops.gelu(h, out16=torch.bfloat16, want_f32=False)[1]
+            # first layer in one kernel: h = x W1 in f32 (the backward pass reads it) and a16 = bf16(gelu(h))
+            pg.pg_gemm_fused_ex(wl.BF16, 8192, 16384, 4096, xd, 4096, w1d, 16384, h, 16384, None,
+                                pg.PG_ACT_GELU | pg.PG_ACT_COPY_ONLY, a16, 16384)
             y = pg.pg_matmul(a16, w2d)
             da, dw2 = pg.pg_matmul_backward(a16, w2d, dy)
             dh = ops.gelu_grad(h, da)

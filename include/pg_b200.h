@@ -72,6 +72,10 @@ PG_B200_API int pg_b200_gemm_ex(int dtype, size_t m, size_t n, size_t k, const v
 #define PG_B200_ACT_NONE 0
 #define PG_B200_ACT_RELU 1
 #define PG_B200_ACT_GELU 2   /* 0.5 x (1 + erf(x / sqrt 2)) */
+/* OR-ed into `act` of pg_b200_gemm_fused_out16: the activation goes into the 16-bit copy only and C keeps
+ * bias + A*B — what a training step wants from the first layer of an MLP: the pre-activation in f32 for the
+ * backward pass (autograd.c:794-801 reads it) and the activated value in 16 bits for the next GEMM. */
+#define PG_B200_ACT_COPY_ONLY 0x100
 
 /* pg_cpu_gemm_fused_ex (gemm.c:806-817): C = act(bias[j] + A*B), bias of n floats or NULL.
  * In picograd each row of C starts as the bias row and the micro-kernels accumulate onto it, so

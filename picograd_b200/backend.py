@@ -108,6 +108,9 @@ def pg_bgemm(m, n, k, a, lda, b, ldb, c, ldc):
 PG_ACT_NONE, PG_ACT_RELU, PG_ACT_GELU = 0, 1, 2   # backend/cpu/gemm.h:37-39
 
 
+PG_ACT_COPY_ONLY = 0x100   # with c16: the activation goes into the 16-bit copy only, C keeps bias + A*B
+
+
 def pg_gemm_fused_ex(dtype, m, n, k, a, lda, b, ldb, c, ldc, bias=None, act=PG_ACT_NONE, c16=None, ldc16=0):
     """pg_cpu_gemm_fused_ex (backend/cpu/gemm.c:806-817): C = act(bias[j] + A*B), bias an f32
     tensor of n elements or None, applied in the GEMM kernel's epilogue.  Device tensors, or host

@@ -306,23 +306,24 @@ int bias_rows_launch(float *out, const float *bias, uint32_t cout, uint64_t rows
 // Bias and activation over a finished C (rows x n, leading dimension ldc), for the products whose
 // tensor-core route cannot apply them in its own epilogue (K-slices, swapped operands): picograd's
 // act_apply (backend/cpu/gemm.c:632-636) after the bias row of gemm.c:729-735.
-__global__ void bias_act_kernel(float *__restrict__ c, uint64_t ldc, const float *__restrict__ bias, int act,
+__global__ void bias_act_kernel(float *__restrict__ c, uint64_t ldc, const float *__restrict__ bias, int act, int copy_only,
                                 uint16_t *__restrict__ c16, uint64_t ld16, int dtype16, uint64_t rows, uint64_t n) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * n; i += stride) {
         const uint64_t r = i / n, j = i - r * n;
         float x = c[r * ldc + j];
         if (bias) x += bias[j];
-        if (act == 1) x = x > 0.0f ? x : 0.0f;
-        else if (act == 2) x = 0.5f * x * (1.0f + erff(x * 0.70710678118f));
-        c[r * ldc + j] = x;
-        if (c16) c16[r * ld16 + j] = to16(x, dtype16);
+        float y = x;
+        if (act == 1) y = x > 0.0f ? x : 0.0f;
+        else if (act == 2) y = 0.5f * x * (1.0f + erff(x * 0.70710678118f));
+        c[r * ldc + j] = copy_only ? x : y;
+        if (c16) c16[r * ld16 + j] = to16(y, dtype16);
     }
 }
-int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, uint16_t *c16, uint64_t ld16, int dtype16,
-                    uint64_t rows, uint64_t n, cudaStream_t s) {
+int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, int act_copy_only, uint16_t *c16, uint64_t ld16,
+                    int dtype16, uint64_t rows, uint64_t n, cudaStream_t s) {
     if (!rows || !n) return ST_OK;
-    bias_act_kernel<<<grid_for(rows * n, 256), 256, 0, s>>>(c, ldc, bias, act, c16, ld16, dtype16, rows, n);
+    bias_act_kernel<<<grid_for(rows * n, 256), 256, 0, s>>>(c, ldc, bias, act, act_copy_only, c16, ld16, dtype16, rows, n);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }

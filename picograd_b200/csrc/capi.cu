@@ -200,6 +200,7 @@ struct Problem {
     uint16_t *c16 = nullptr;
     size_t ld16 = 0;
     int dtype16 = DT_BF16;
+    int act_copy_only = 0;       // the activation goes into c16 only; C keeps bias + A*B
     bool has_epilogue() const { return bias != nullptr || act != 0 || c16 != nullptr; }
 };
 
@@ -214,6 +215,7 @@ static int run_simt(const Problem &p) {
     s.C = p.c; s.ldc = (int64_t)p.ldc; s.c_bs = (int64_t)p.stride_c;
     s.accumulate = p.accumulate;
     s.bias = p.bias; s.act = p.act; s.c16 = p.c16; s.ld16 = (int64_t)p.ld16; s.dtype16 = p.dtype16;
+    s.act_copy_only = p.act_copy_only;
     s.stream = g.stream;
     int st = simt_gemm_launch(s);
     if (st == ST_OK) set_last_path("simt");
@@ -405,7 +407,7 @@ static int run_tc(const Problem &p) {
     // Bias and activation ride in the kernel's epilogue when every tile holds finished sums; K-slices
     // and the swapped route finish C first and one elementwise pass follows.
     const bool epi_in_kernel = p.has_epilogue() && splits == 1 && !swap;
-    if (epi_in_kernel) { t.bias = p.bias; t.act = p.act; t.c16 = p.c16; t.ld16 = p.ld16; t.dtype16 = p.dtype16; }
+    if (epi_in_kernel) { t.bias = p.bias; t.act = p.act; t.c16 = p.c16; t.ld16 = p.ld16; t.dtype16 = p.dtype16; t.act_copy_only = p.act_copy_only; }
     if (swap) {
         // A' = B (its N runs along the tile rows), B' = A, tile stored transposed into the same C
         TcOperand opa = t.A;
@@ -429,7 +431,7 @@ static int run_tc(const Problem &p) {
         if (st != ST_OK) return st;
     }
     if (p.has_epilogue() && !epi_in_kernel) {
-        st = bias_act_launch(p.c, p.ldc, p.bias, p.act, p.c16, p.ld16, p.dtype16, p.m, p.n, g.stream);
+        st = bias_act_launch(p.c, p.ldc, p.bias, p.act, p.act_copy_only, p.c16, p.ld16, p.dtype16, p.m, p.n, g.stream);
         if (st != ST_OK) return st;
     }
     return ST_OK;
@@ -592,7 +594,10 @@ static int gemm_ex_any(int dtype, size_t m, size_t n, size_t k, const void *a, s
                        size_t ld16 = 0, int dtype16 = DT_BF16) {
     if (!ready()) return g.init_status;
     if (dtype != DT_F32 && dtype != DT_F16 && dtype != DT_BF16) { set_error("bad dtype %d", dtype); return ST_UNSUPPORTED; }
+    const int copy_only = (act & 0x100) ? 1 : 0;      // PG_B200_ACT_COPY_ONLY
+    act &= ~0x100;
     if (act < 0 || act > 2) { set_error("bad activation %d", act); return ST_UNSUPPORTED; }
+    if (copy_only && !c16) { set_error("PG_B200_ACT_COPY_ONLY needs the 16-bit output"); return ST_UNSUPPORTED; }
     if (c16 && dtype16 != DT_F16 && dtype16 != DT_BF16) { set_error("bad 16-bit output dtype %d", dtype16); return ST_UNSUPPORTED; }
     if (m == 0 || n == 0) return ST_OK;
     const bool da = is_device_ptr(a), db = is_device_ptr(b), dc = is_device_ptr(c);
@@ -602,7 +607,7 @@ static int gemm_ex_any(int dtype, size_t m, size_t n, size_t k, const void *a, s
             return ST_UNSUPPORTED;
         }
         Problem p = {dtype, dtype, 0, 0, 1, m, n, k, a, lda, 0, b, ldb, 0, c, ldc, 0, 0};
-        p.bias = bias; p.act = act; p.c16 = c16; p.ld16 = ld16; p.dtype16 = dtype16;
+        p.bias = bias; p.act = act; p.c16 = c16; p.ld16 = ld16; p.dtype16 = dtype16; p.act_copy_only = copy_only;
         return run_problem(p);
     }
     if (!da && !db && !dc) {

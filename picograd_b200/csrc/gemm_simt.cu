@@ -30,6 +30,7 @@ struct SimtParams {
     // bias row, the micro-kernels accumulate onto it, the activation runs over the finished row
     const float *bias; int act;
     unsigned short *c16; long long ld16, c16_bs; int dtype16;
+    int act_copy_only;          // the activation goes into the 16-bit copy only
 };
 
 __device__ __forceinline__ float simt_act(float x, int act) {
@@ -152,8 +153,8 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
             const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
             if (gn >= p.N) continue;
             float *dst = Cb + gm * p.ldc + gn;
-            const float r = simt_act(acc[i][j], p.act);
-            *dst = p.accumulate ? (*dst + r) : r;
+            const float r = simt_act(acc[i][j], p.act), rc = p.act_copy_only ? acc[i][j] : r;
+            *dst = p.accumulate ? (*dst + rc) : rc;
             if (p.c16) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn] = simt_to16(r, p.dtype16);
         }
     }
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
 
     float *Cb = p.C + (long long)bz * p.c_bs;
     const bool vec = (p.ldc % 4 == 0) && (((uintptr_t)Cb & 15) == 0) && !p.accumulate;
-    if (p.act) {
+    if (p.act && !p.act_copy_only) {
 #pragma unroll
         for (int i = 0; i < T; ++i)
 #pragma unroll
@@ -293,7 +294,8 @@ __global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
 #pragma unroll
             for (int j = 0; j < T; ++j) {
                 const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
-                if (gn < p.N) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn] = simt_to16(acc[i][j], p.dtype16);
+                const float y = p.act_copy_only ? simt_act(acc[i][j], p.act) : acc[i][j];
+                if (gn < p.N) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn] = simt_to16(y, p.dtype16);
             }
         }
 #pragma unroll
@@ -320,7 +322,7 @@ int simt_gemm_launch(const SimtGemm &g) {
     p.C = g.C; p.ldc = g.ldc; p.c_bs = g.c_bs;
     p.dtype_a = g.dtype_a; p.dtype_b = g.dtype_b; p.accumulate = g.accumulate;
     p.bias = g.bias; p.act = g.act; p.c16 = (unsigned short *)g.c16; p.ld16 = g.ld16;
-    p.c16_bs = (long long)g.M * g.ld16; p.dtype16 = g.dtype16;
+    p.c16_bs = (long long)g.M * g.ld16; p.dtype16 = g.dtype16; p.act_copy_only = g.act_copy_only;
     // grid.z is limited to 65535: launch the batch in slices
     const bool big = (uint64_t)g.M * g.N >= (uint64_t)512 * 512 * 4;
     const int tile = big ? 128 : 64;

@@ -92,6 +92,7 @@ struct TcParams {
     // fused epilogue (picograd pg_cpu_gemm_fused_ex): C = act(A*B + bias[col]); optional 16-bit copy of C
     const float *bias;
     uint32_t act;                 // 0 none, 1 relu, 2 gelu (erf form)
+    uint32_t act_copy_only;       // the activation goes into the 16-bit copy only; C keeps bias + A*B
     unsigned short *c16;
     uint64_t ld16;
     uint32_t dtype16;
@@ -645,12 +646,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (uint32_t j = 0; j < W; ++j)
                             v[j] = __float_as_uint(__uint_as_float(v[j]) + __shfl_sync(0xffffffffu, bias_cur, j));
                     }
+                    // u: what the 16-bit copy receives.  Normally C gets the same; with act_copy_only C keeps the
+                    // value before the activation (a training step needs it for the backward pass) and only the
+                    // copy is activated.
+                    uint32_t u[32];
+#pragma unroll
+                    for (uint32_t j = 0; j < W; ++j) u[j] = v[j];
                     if (p.act == 1) {
 #pragma unroll
-                        for (uint32_t j = 0; j < W; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
+                        for (uint32_t j = 0; j < W; ++j) u[j] = __float_as_uint(fmaxf(__uint_as_float(u[j]), 0.0f));
                     } else if (p.act == 2) {
 #pragma unroll
-                        for (uint32_t j = 0; j < W; ++j) v[j] = __float_as_uint(gelu_erf(__uint_as_float(v[j])));
+                        for (uint32_t j = 0; j < W; ++j) u[j] = __float_as_uint(gelu_erf(__uint_as_float(u[j])));
+                    }
+                    if (!p.act_copy_only) {
+#pragma unroll
+                        for (uint32_t j = 0; j < W; ++j) v[j] = u[j];
                     }
                     if (p.c16 && row < p.M) {
                         unsigned short *d16 = p.c16 + (uint64_t)zc * p.M * p.ld16 + (uint64_t)row * p.ld16 + col;
@@ -664,15 +675,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (uint32_t j = 0; j < W; j += 16) {
                                 uint4 lo, hi;           // pieces j/8 and j/8 + 1 of this lane's row
                                 if (p.dtype16 == (uint32_t)DT_BF16) {
-                                    lo = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                                    pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
-                                    hi = make_uint4(pack_bf16(v[j + 8], v[j + 9]), pack_bf16(v[j + 10], v[j + 11]),
-                                                    pack_bf16(v[j + 12], v[j + 13]), pack_bf16(v[j + 14], v[j + 15]));
+                                    lo = make_uint4(pack_bf16(u[j], u[j + 1]), pack_bf16(u[j + 2], u[j + 3]),
+                                                    pack_bf16(u[j + 4], u[j + 5]), pack_bf16(u[j + 6], u[j + 7]));
+                                    hi = make_uint4(pack_bf16(u[j + 8], u[j + 9]), pack_bf16(u[j + 10], u[j + 11]),
+                                                    pack_bf16(u[j + 12], u[j + 13]), pack_bf16(u[j + 14], u[j + 15]));
                                 } else {
-                                    lo = make_uint4(pack_f16(v[j], v[j + 1]), pack_f16(v[j + 2], v[j + 3]),
-                                                    pack_f16(v[j + 4], v[j + 5]), pack_f16(v[j + 6], v[j + 7]));
-                                    hi = make_uint4(pack_f16(v[j + 8], v[j + 9]), pack_f16(v[j + 10], v[j + 11]),
-                                                    pack_f16(v[j + 12], v[j + 13]), pack_f16(v[j + 14], v[j + 15]));
+                                    lo = make_uint4(pack_f16(u[j], u[j + 1]), pack_f16(u[j + 2], u[j + 3]),
+                                                    pack_f16(u[j + 4], u[j + 5]), pack_f16(u[j + 6], u[j + 7]));
+                                    hi = make_uint4(pack_f16(u[j + 8], u[j + 9]), pack_f16(u[j + 10], u[j + 11]),
+                                                    pack_f16(u[j + 12], u[j + 13]), pack_f16(u[j + 14], u[j + 15]));
                                 }
                                 uint4 give = odd ? lo : hi, got;
                                 got.x = __shfl_xor_sync(0xffffffffu, give.x, 1);
@@ -689,19 +700,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                                 for (uint32_t j = 0; j < W; j += 8)
                                     *reinterpret_cast<uint4 *>(d16 + j) =
-                                        make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                                   pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+                                        make_uint4(pack_bf16(u[j], u[j + 1]), pack_bf16(u[j + 2], u[j + 3]),
+                                                   pack_bf16(u[j + 4], u[j + 5]), pack_bf16(u[j + 6], u[j + 7]));
                             } else {
 #pragma unroll
                                 for (uint32_t j = 0; j < W; j += 8)
                                     *reinterpret_cast<uint4 *>(d16 + j) =
-                                        make_uint4(pack_f16(v[j], v[j + 1]), pack_f16(v[j + 2], v[j + 3]),
-                                                   pack_f16(v[j + 4], v[j + 5]), pack_f16(v[j + 6], v[j + 7]));
+                                        make_uint4(pack_f16(u[j], u[j + 1]), pack_f16(u[j + 2], u[j + 3]),
+                                                   pack_f16(u[j + 4], u[j + 5]), pack_f16(u[j + 6], u[j + 7]));
                             }
                         } else {
 #pragma unroll
                             for (uint32_t j = 0; j < W; ++j)
-                                if (col + j < p.N) d16[j] = f32_to_16(__uint_as_float(v[j]), p.dtype16);
+                                if (col + j < p.N) d16[j] = f32_to_16(__uint_as_float(u[j]), p.dtype16);
                         }
                     }
                 }
@@ -1270,6 +1281,7 @@ int tc_gemm_launch(const TcGemm &g) {
     if (g.cluster_splitk && c.cg == 1 && c.staging && c.bn <= 32 && g.Cout && g.batch == 1 && splits >= 2 && splits <= 8 &&
         (splits - 1) * BM_CTA * c.bn * 4 <= c.ew * 2 * EPI_BUF_BYTES && !(g.debug & 5))
         p.cluster_k = splits;
+    p.act_copy_only = g.act_copy_only ? 1u : 0u;
     p.bias = g.bias; p.act = (uint32_t)g.act; p.c16 = (unsigned short *)g.c16; p.ld16 = g.ld16; p.dtype16 = (uint32_t)g.dtype16;
     p.bias_vec4 = aligned16(g.bias) ? 1u : 0u;
     p.c16_vec = (g.c16 && aligned16(g.c16) && g.ld16 % 8 == 0) ? 1u : 0u;

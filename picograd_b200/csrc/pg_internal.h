@@ -49,6 +49,7 @@ struct TcGemm {
     int accumulate;            // C += A*B instead of C = A*B
     // fused epilogue: C = act(A*B + bias[col]) and an optional 16-bit copy of C ([batch][M][ld16])
     const float *bias; int act; uint16_t *c16; uint64_t ld16; int dtype16;
+    int act_copy_only;         // activation applied to the 16-bit copy only
     int c_trans;               // store the tile transposed: element (row, col) -> C[col*ldc + row]
     // splits > 1 with Cout set: C holds the K-slices and the kernel itself sums them into Cout
     float *Cout;
@@ -107,6 +108,7 @@ struct SimtGemm {
     int accumulate;            // C += instead of C =
     const float *bias; int act;   // fused epilogue: the chain of column j starts at bias[j]; act applied at the store
     uint16_t *c16; int64_t ld16; int dtype16;
+    int act_copy_only;         // activation applied to the 16-bit copy only
     cudaStream_t stream;
 };
 int simt_gemm_launch(const SimtGemm &g);
@@ -127,8 +129,8 @@ int gelu_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
 int gelu_grad_launch(const float *x, const float *gy, float *out, uint64_t n, cudaStream_t s);
 int softmax_rows_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
                         uint64_t rows, uint32_t len, cudaStream_t s);
-int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, uint16_t *c16, uint64_t ld16, int dtype16,
-                    uint64_t rows, uint64_t n, cudaStream_t s);
+int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, int act_copy_only, uint16_t *c16, uint64_t ld16,
+                    int dtype16, uint64_t rows, uint64_t n, cudaStream_t s);
 int im2col_launch(const float *x, float *col, uint32_t batch, uint32_t cin, uint32_t h, uint32_t w, uint32_t kh, uint32_t kw,
                   uint32_t oh, uint32_t ow, int stride, int pad, cudaStream_t s);
 int bias_rows_launch(float *out, const float *bias, uint32_t cout, uint64_t rows, uint64_t n, cudaStream_t s);

@@ -129,6 +129,23 @@ def test_16bit_copy_of_c(pg, oracle, dt16, shape, path):
     assert np.array_equal(bits_to_host(c16), conv(got))
 
 
+@pytest.mark.parametrize("shape,path", [((256, 512, 512), 1), ((130, 77, 304), 1), ((130, 77, 300), 2), ((1100, 1200, 64), 2),
+                                        ((16, 4096, 1024), 0)], ids=["tc-vec", "tc-ragged", "ffma64", "ffma128", "skinny-post-pass"])
+def test_activation_on_the_16bit_copy_only(pg, oracle, shape, path):
+    """PG_ACT_COPY_ONLY: C keeps bias + A*B (the pre-activation a backward pass reads), the 16-bit copy gets
+    the activation of it: the first layer of a training MLP in one kernel."""
+    m, n, k = shape
+    a, b = wl.to_bf16_bits(wl.seeded_uniform(m, k, 65)), wl.to_bf16_bits(wl.seeded_uniform(k, n, 66))
+    bias = np.random.default_rng(67).uniform(-1, 1, n).astype(np.float32)
+    pg.set_option("path", path)
+    got, c16 = fused_dev(pg, wl.BF16, a, b, bias, pg.PG_ACT_GELU | pg.PG_ACT_COPY_ONLY, want16=torch.bfloat16)
+    pre = oracle.gemm_fused_ex(wl.BF16, a, b, bias, 0)
+    assert wl.relerr(got, pre) <= wl.tolerance(wl.BF16, k)
+    want16 = oracle.gelu(got)                                 # activation of what C actually holds
+    got16 = wl.bf16_bits_to_f32(bits_to_host(c16))
+    assert np.abs(got16 - want16).max() <= 2.0 ** -8 * max(1.0, np.abs(want16).max())   # one bf16 rounding
+
+
 def test_skinny_and_split_k_routes_apply_the_epilogue_after_the_sum(pg, oracle):
     """K-slices and the swapped-operand route finish C first; one elementwise pass follows."""
     for (m, n, k) in [(16, 4096, 4096), (128, 128, 8192)]:
