@@ -150,6 +150,13 @@ PG_B200_API int pg_b200_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t 
 PG_B200_API int pg_b200_attention_bmm(int dtype, size_t batch, size_t seq_q, size_t seq_k, size_t d,
                           const void *q, const void *kt, const void *v, float *o);
 
+/* The same with accumulate == 0: ga = g * B^T, gb = A^T * g (overwrite).  For gradients that were just created:
+ * picograd zeroes them (autograd.c:2490-2492) and adds; overwriting saves the zero fill and the read of the
+ * old values, with the same result. */
+PG_B200_API int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size_t k,
+                               const void *a, const void *b, int b_batched,
+                               const float *g, float *ga, float *gb, int accumulate);
+
 /* Harness steps between the GEMMs of the attention-shaped and MLP workloads
  * (ops/activations.c:22-45 softmax rows, :114 GELU, autograd.c:794-801 GELU
  * gradient), so that those workloads stay on the device.  out16 (optional)

@@ -360,11 +360,16 @@ def pg_matmul_backward(a, b, g, need_a=True, need_b=True, ga=None, gb=None, dtyp
     for d in a.shape[:-2]:
         batch *= d
     b_batched = b.dim() > 2
-    if need_a and ga is None:
-        ga = _zeros_f32(a.shape, a.device)
-    if need_b and gb is None:
-        gb = _zeros_f32(b.shape, a.device)
-    _check(lib.pg_b200_matmul_backward(dt, batch, m, n, k, a.data_ptr(), b.data_ptr(), int(b_batched),
-                                       g.data_ptr(), ga.data_ptr() if need_a else None,
-                                       gb.data_ptr() if need_b else None), "pg_b200_matmul_backward")
+    # Gradients created here would be zero (pg_backward zeroes them, autograd.c:2490-2492): the products then
+    # overwrite instead of adding to zeros; gradients passed in are accumulated into, as in picograd.
+    fresh_a, fresh_b = need_a and ga is None, need_b and gb is None
+    overwrite = (fresh_a or not need_a) and (fresh_b or not need_b)
+    if fresh_a:
+        ga = torch.empty(a.shape, dtype=torch.float32, device=a.device) if overwrite else _zeros_f32(a.shape, a.device)
+    if fresh_b:
+        gb = torch.empty(b.shape, dtype=torch.float32, device=a.device) if overwrite else _zeros_f32(b.shape, a.device)
+    _check(lib.pg_b200_matmul_backward_ex(dt, batch, m, n, k, a.data_ptr(), b.data_ptr(), int(b_batched),
+                                          g.data_ptr(), ga.data_ptr() if need_a else None,
+                                          gb.data_ptr() if need_b else None, 0 if overwrite else 1),
+           "pg_b200_matmul_backward")
     return ga, gb

@@ -751,7 +751,13 @@ int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int trans_b, siz
 
 int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t k, const void *a, const void *b,
                             int b_batched, const float *gr, float *ga, float *gb) {
+    return pg_b200_matmul_backward_ex(dtype, batch, m, n, k, a, b, b_batched, gr, ga, gb, 1);
+}
+
+int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size_t k, const void *a, const void *b,
+                               int b_batched, const float *gr, float *ga, float *gb, int accumulate) {
     if (!ready()) return g.init_status;
+    const int acc = accumulate ? 1 : 0;
     if (batch == 0 || m == 0 || n == 0 || k == 0) return ST_OK;
     int st = ST_OK;
     // The f32 gradient meets the tensor cores as exact bf16 pieces; both products read the same
@@ -774,7 +780,7 @@ int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t 
     if (ga) {
         // ga[batch][m][k] += g[batch][m][n] * B^T : the product's "A" is g (m x n), its "B" is B (stored
         // k x n) read transposed.  A B shared by the batch folds the batch into the rows of g and ga.
-        Problem p = {DT_F32, dtype, 0, 1, batch, m, k, n, gr, n, m * n, b, n, k * n, ga, k, m * k, 1};
+        Problem p = {DT_F32, dtype, 0, 1, batch, m, k, n, gr, n, m * n, b, n, k * n, ga, k, m * k, acc};
         if (!b_batched) { p.batch = 1; p.m = batch * m; p.stride_a = p.stride_b = p.stride_c = 0; }
         if (pieces && p.batch == 1) { p.a_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; }
         st = run_problem(p);
@@ -783,12 +789,12 @@ int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t 
     if (gb) {
         if (b_batched && batch > 1) {
             // gb[batch][k][n] += A^T[batch][k][m] * g[batch][m][n]
-            Problem p = {dtype, DT_F32, 1, 0, batch, k, n, m, a, k, m * k, gr, n, m * n, gb, n, k * n, 1};
+            Problem p = {dtype, DT_F32, 1, 0, batch, k, n, m, a, k, m * k, gr, n, m * n, gb, n, k * n, acc};
             st = run_problem(p);
         } else {
             // B shared by the batch (or no batch): gb[k][n] += sum_b A[b]^T g[b]  ==  one product with the
             // batch folded into the contraction: A as [(batch*m)][k], g as [(batch*m)][n]
-            Problem p = {dtype, DT_F32, 1, 0, 1, k, n, batch * m, a, k, 0, gr, n, 0, gb, n, 0, 1};
+            Problem p = {dtype, DT_F32, 1, 0, 1, k, n, batch * m, a, k, 0, gr, n, 0, gb, n, 0, acc};
             if (pieces) { p.b_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; }
             st = run_problem(p);
         }
