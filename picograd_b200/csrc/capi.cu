@@ -44,6 +44,7 @@ struct State {
     int opt_fused_attention = 1; // 0: pg_b200_attention_bmm always runs the three-kernel chain
     DeviceBuf attn_ws;           // S and P of the chain form of pg_b200_attention_bmm
     int opt_cluster_splitk = 1;  // K-slices of a skinny product as one cluster (reduction through distributed shared memory)
+    int opt_host_blk = 0;        // slab size of the staged host-pointer pipeline (0 = 2048)
     int opt_stream_k = 0;        // stream-K for a partly filled last wave: correct, but measured 5-20 % slower
                                  // than the plain schedule on B200 (partial waves already run faster), so off
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
@@ -201,6 +202,7 @@ struct Problem {
     size_t ld16 = 0;
     int dtype16 = DT_BF16;
     int act_copy_only = 0;       // the activation goes into c16 only; C keeps bias + A*B
+    int no_split_k = 0;          // every element keeps the K order of the unsplit product (staged pieces of a large one)
     bool has_epilogue() const { return bias != nullptr || act != 0 || c16 != nullptr; }
 };
 
@@ -296,7 +298,7 @@ static int run_tc(const Problem &p) {
     // split-K for shapes that would leave most SMs idle
     uint32_t splits = 1;
     const uint32_t k_blocks = (uint32_t)((p.k + 63) / 64);
-    if (p.batch == 1 && npa == 1 && npb == 1) {
+    if (p.batch == 1 && npa == 1 && npb == 1 && !p.no_split_k) {
         if (g.opt_splits > 0) {
             splits = (uint32_t)g.opt_splits;
         } else {
@@ -535,52 +537,60 @@ static int gemm_ex_host_pipelined(int dtype, size_t m, size_t n, size_t k, const
     char *da = (char *)g.stage_a.ptr, *db = (char *)g.stage_b.ptr;
     float *dc = (float *)g.stage_c.ptr;
     cudaError_t e = cudaSuccess;
-    // slabs in, alternating A row slabs and B column slabs; order[] remembers when each one lands
-    size_t when_a[16], when_b[16], tick = 0;
-    for (size_t t = 0; t < (gm > gn ? gm : gn) && e == cudaSuccess; ++t) {
-        if (t < gm) {
-            const size_t r0 = t * bm, rh = (m - r0 < bm) ? m - r0 : bm;
-            e = cudaMemcpy2DAsync(da + r0 * k8 * es, k8 * es, (const char *)a + r0 * lda * es, lda * es, k * es, rh,
-                                  cudaMemcpyHostToDevice, g_pipe.in);
-            if (e == cudaSuccess) e = cudaEventRecord(g_pipe.ev_a[t], g_pipe.in);
-            when_a[t] = tick++;
-        }
-        if (t < gn && e == cudaSuccess) {
-            const size_t c0 = t * bn, cw = (n - c0 < bn) ? n - c0 : bn;
-            e = cudaMemcpy2DAsync(db + c0 * es, n8 * es, (const char *)b + c0 * es, ldb * es, cw * es, k,
-                                  cudaMemcpyHostToDevice, g_pipe.in);
-            if (e == cudaSuccess) e = cudaEventRecord(g_pipe.ev_b[t], g_pipe.in);
-            when_b[t] = tick++;
-        }
-    }
-    if (e != cudaSuccess) { set_error("H2D staging failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_COPY; }
-    // blocks of C in the order in which their slabs become available
-    for (size_t step = 0; step < tick; ++step) {
-        for (size_t i = 0; i < gm; ++i)
-            for (size_t j = 0; j < gn; ++j) {
-                const size_t avail = when_a[i] > when_b[j] ? when_a[i] : when_b[j];
-                if (avail != step) continue;
-                const size_t r0 = i * bm, rh = (m - r0 < bm) ? m - r0 : bm;
-                const size_t c0 = j * bn, cw = (n - c0 < bn) ? n - c0 : bn;
-                cudaStreamWaitEvent(g.stream, g_pipe.ev_a[i], 0);
-                cudaStreamWaitEvent(g.stream, g_pipe.ev_b[j], 0);
-                Problem p = {dtype, dtype, 0, 0, 1, rh, cw, k, da + r0 * k8 * es, k8, 0, db + c0 * es, n8, 0,
-                             dc + r0 * n4 + c0, n4, 0, 0};
-                p.bias = dev_bias ? dev_bias + c0 : nullptr; p.act = act;
-                st = run_problem(p);
-                if (st != ST_OK) { cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream); return st; }
-                cudaEvent_t done = g_pipe.ev_c[i * gn + j];
-                cudaEventRecord(done, g.stream);
-                cudaStreamWaitEvent(g_pipe.out, done, 0);
-                e = cudaMemcpy2DAsync(c + r0 * ldc + c0, ldc * 4, dc + r0 * n4 + c0, n4 * 4, cw * 4, rh,
-                                      cudaMemcpyDeviceToHost, g_pipe.out);
-                if (e != cudaSuccess) {
-                    set_error("D2H staging failed: %s", cudaGetErrorString(e));
-                    cudaGetLastError();
-                    cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream);
-                    return ST_COPY;
-                }
+    // Slabs in, alternating A row slabs and B column slabs.  When a slab has landed, everything it completes is
+    // ONE product: row slab i of A with all column slabs of B that are there (a strip of C, i blocks wide), column
+    // slab j of B with all row slabs of A that are there (a strip j + 1 blocks high).  The strips grow as the
+    // operands arrive, so the products stay large enough to fill the GPU while the copies out start after the
+    // first two slabs and then run beside the copies in (PCIe is full duplex).
+    size_t na = 0, nb = 0, strips = 0;       // slabs of A / B sent so far
+    for (size_t t = 0; t < (gm > gn ? gm : gn); ++t) {
+        for (int which = 0; which < 2; ++which) {
+            size_t r0, rh, c0, cw;
+            if (which == 0) {
+                if (t >= gm) continue;
+                r0 = t * bm; rh = (m - r0 < bm) ? m - r0 : bm;
+                e = cudaMemcpy2DAsync(da + r0 * k8 * es, k8 * es, (const char *)a + r0 * lda * es, lda * es, k * es, rh,
+                                      cudaMemcpyHostToDevice, g_pipe.in);
+                if (e == cudaSuccess) e = cudaEventRecord(g_pipe.ev_a[t], g_pipe.in);
+                ++na;
+                c0 = 0; cw = nb * bn < n ? nb * bn : n;              // the strip this slab completes
+            } else {
+                if (t >= gn) continue;
+                c0 = t * bn; cw = (n - c0 < bn) ? n - c0 : bn;
+                e = cudaMemcpy2DAsync(db + c0 * es, n8 * es, (const char *)b + c0 * es, ldb * es, cw * es, k,
+                                      cudaMemcpyHostToDevice, g_pipe.in);
+                if (e == cudaSuccess) e = cudaEventRecord(g_pipe.ev_b[t], g_pipe.in);
+                ++nb;
+                r0 = 0; rh = na * bm < m ? na * bm : m;
             }
+            if (e != cudaSuccess) {
+                set_error("H2D staging failed: %s", cudaGetErrorString(e));
+                cudaGetLastError();
+                cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g_pipe.out);
+                return ST_COPY;
+            }
+            if (rh == 0 || cw == 0) continue;                        // the very first slab completes nothing
+            // the copy stream is in order: the newest event of each operand implies the earlier ones
+            cudaStreamWaitEvent(g.stream, g_pipe.ev_a[na - 1], 0);
+            cudaStreamWaitEvent(g.stream, g_pipe.ev_b[nb - 1], 0);
+            Problem p = {dtype, dtype, 0, 0, 1, rh, cw, k, da + r0 * k8 * es, k8, 0, db + c0 * es, n8, 0,
+                         dc + r0 * n4 + c0, n4, 0, 0};
+            p.bias = dev_bias ? dev_bias + c0 : nullptr; p.act = act;
+            p.no_split_k = 1;        // same K order per element as the product in one piece: same bits
+            st = run_problem(p);
+            if (st != ST_OK) { cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g_pipe.out); return st; }
+            cudaEvent_t done = g_pipe.ev_c[strips++];
+            cudaEventRecord(done, g.stream);
+            cudaStreamWaitEvent(g_pipe.out, done, 0);
+            e = cudaMemcpy2DAsync(c + r0 * ldc + c0, ldc * 4, dc + r0 * n4 + c0, n4 * 4, cw * 4, rh,
+                                  cudaMemcpyDeviceToHost, g_pipe.out);
+            if (e != cudaSuccess) {
+                set_error("D2H staging failed: %s", cudaGetErrorString(e));
+                cudaGetLastError();
+                cudaStreamSynchronize(g_pipe.in); cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g_pipe.out);
+                return ST_COPY;
+            }
+        }
     }
     e = cudaStreamSynchronize(g_pipe.out);
     if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
@@ -623,7 +633,8 @@ static int gemm_ex_any(int dtype, size_t m, size_t n, size_t k, const void *a, s
             dev_bias = (const float *)g.stage_bias.ptr;
         }
         // pipeline only products whose copies dominate and that cut into at least 2 x 2 blocks
-        const size_t blk = 2048;
+        // slabs of 1024 rows / columns (2048 for products beyond 16 slabs a side)
+        const size_t blk = (size_t)(g.opt_host_blk > 0 ? g.opt_host_blk : 2048);
         if (g.opt_host_pipeline && k > 0 && m >= 2 * blk && n >= 2 * blk && (m + blk - 1) / blk <= 16 &&
             (n + blk - 1) / blk <= 16 && host_pipe_ready((m + blk - 1) / blk, (n + blk - 1) / blk))
             return gemm_ex_host_pipelined(dtype, m, n, k, a, lda, b, ldb, c, ldc, blk, blk, dev_bias, act);
@@ -944,6 +955,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "attn_q_tmem")) { g.opt_attn_q_tmem = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "fused_attention")) { g.opt_fused_attention = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "cluster_splitk")) { g.opt_cluster_splitk = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);
