@@ -117,6 +117,14 @@ PG_B200_API int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int 
                          const void *b, size_t ldb, size_t stride_b,
                          float *c, size_t ldc, size_t stride_c, int accumulate);
 
+/* pg_addmm (ops/matmul.c:371-405): c = beta * input + alpha * (a * b).  a [m,k], b [k,n] in `dtype`; c f32 [m,n];
+ * input f32 read at input[i * in_row_stride + j * in_col_stride] (strides in elements, 0 = broadcast along that
+ * dimension, so [m,n], [n], [m,1] and scalars all fit).  The product is pg_matmul's; the tail is one kernel that
+ * rounds after every step as picograd's separate scale and add passes do (same bits for f32).  Device pointers. */
+PG_B200_API int pg_b200_addmm(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+                  float *c, size_t ldc, const float *input, size_t in_row_stride, size_t in_col_stride,
+                  float alpha, float beta);
+
 /* permute_copy of pg_tensordot (ops/matmul.c:21-42): dst (contiguous, dimension d of size shape[perm[d]])
  * receives src (contiguous, `shape`) with its dimensions reordered; dtype gives the element size.  Device
  * pointers, ndim <= 8 (picograd's PG_MAX_NDIM).  pg_tensordot is this on both operands, then pg_matmul. */

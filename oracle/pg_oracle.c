@@ -324,6 +324,26 @@ void pgo_matmul_backward(int dtype, size_t m, size_t n, size_t k,
     }
 }
 
+/* ops/matmul.c:371-405 (pg_addmm): tmp = pg_matmul(m1, m2); tmp *= alpha (if alpha != 1); with beta == 0 that is
+ * the result; else base = 0 + broadcast(input) ; base *= beta (if beta != 1); result = base + tmp -- separate
+ * f32 operations, each rounded.  input is read through (row, column) element strides, 0 for a broadcast one. */
+void pgo_addmm(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+               float *c, size_t ldc, const float *input, size_t in_rs, size_t in_cs, float alpha, float beta)
+{
+    pgo_gemm_ex(dtype, m, n, k, a, lda, b, ldb, c, ldc);
+    for (size_t i = 0; i < m; i++)
+        for (size_t j = 0; j < n; j++) {
+            volatile float t = c[i * ldc + j];
+            if (alpha != 1.0f) t = t * alpha;
+            if (beta != 0.0f) {
+                volatile float base = 0.0f + input[i * in_rs + j * in_cs];
+                if (beta != 1.0f) base = base * beta;
+                t = base + t;
+            }
+            c[i * ldc + j] = t;
+        }
+}
+
 /* ops/conv.c:10-146 (pg_conv2d): NCHW, per batch element an im2col matrix (K = cin*kh*kw rows in
  * (ci, ki, kj) order, one column per output pixel, zeros where the window leaves the image), then
  * pg_cpu_gemm(cout, columns, K, w, K, col, ...) and `+= bias[co]` over the finished rows (:127-133).

@@ -65,6 +65,10 @@ void pgo_matmul_backward(int dtype, size_t m, size_t n, size_t k,
 
 /* Row softmax over the last axis and erf-GELU, the two harness steps between
  * the GEMMs of the attention-shaped and MLP workloads. */
+/* pg_addmm (ops/matmul.c:371-405): c = beta * input + alpha * (a * b), input read through element strides
+ * (0 = broadcast along that dimension), every step a separate rounded f32 operation as in picograd. */
+void pgo_addmm(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+               float *c, size_t ldc, const float *input, size_t in_rs, size_t in_cs, float alpha, float beta);
 /* pg_conv2d (ops/conv.c:10-146): x [n,cin,h,w], wt [cout,cin,kh,kw], bias [cout] or NULL ->
  * out [n,cout,oh,ow], oh = (h + 2 pad - kh) / stride + 1.  Returns -1 for shapes pg_conv2d rejects. */
 int pgo_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t cout, size_t kh, size_t kw,

@@ -297,6 +297,28 @@ def pg_bmm(a, b, dtype=None):
     return out
 
 
+def pg_addmm(inp, m1, m2, alpha=1.0, beta=1.0):
+    """pg_addmm (ops/matmul.c:371-405): beta * inp + alpha * (m1 @ m2); m1 [m,k], m2 [k,n] of one dtype, inp f32
+    broadcastable to [m,n].  Returns f32 [m,n], or None where picograd returns NULL."""
+    _ready()
+    if inp is None or m1 is None or m2 is None or m1.dim() != 2 or m2.dim() != 2:
+        return None
+    if m1.shape[1] != m2.shape[0] or m1.dtype != m2.dtype:
+        return None
+    m, k = m1.shape
+    n = m2.shape[1]
+    shape = [1] * (2 - inp.dim()) + list(inp.shape) if inp.dim() <= 2 else None
+    if shape is None or shape[0] not in (1, m) or shape[1] not in (1, n) or inp.dtype != torch.float32:
+        return None
+    inp, m1, m2 = inp.contiguous(), m1.contiguous(), m2.contiguous()
+    rs = 0 if shape[0] == 1 else shape[1]
+    cs = 0 if shape[1] == 1 else 1
+    out = torch.empty((m, n), dtype=torch.float32, device=m1.device)
+    _check(lib.pg_b200_addmm(_TORCH2PG[m1.dtype], m, n, k, m1.data_ptr(), k, m2.data_ptr(), n, out.data_ptr(), n,
+                             inp.data_ptr(), rs, cs, float(alpha), float(beta)), "pg_addmm")
+    return out
+
+
 def _permute_copy(t, perm):
     """permute_copy (ops/matmul.c:21-42) with the library's own kernel: a new contiguous tensor whose dimension d
     is dimension perm[d] of t."""

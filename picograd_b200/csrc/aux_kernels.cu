@@ -265,6 +265,31 @@ int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t n
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
+// The element-wise tail of pg_addmm (ops/matmul.c:383-404): c = (0 + input) * beta + c * alpha with every step a
+// separate rounded f32 operation (no contraction into an FMA), input read through (row, column) element strides.
+__global__ void addmm_finish_kernel(float *__restrict__ c, uint64_t ldc, const float *__restrict__ input, uint64_t in_rs,
+                                    uint64_t in_cs, float alpha, float beta, uint64_t rows, uint64_t n) {
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * n; i += step) {
+        const uint64_t r = i / n, j = i - r * n;
+        float t = c[r * ldc + j];
+        if (alpha != 1.0f) t = __fmul_rn(t, alpha);
+        if (beta != 0.0f) {
+            float base = __fadd_rn(0.0f, input[r * in_rs + j * in_cs]);
+            if (beta != 1.0f) base = __fmul_rn(base, beta);
+            t = __fadd_rn(base, t);
+        }
+        c[r * ldc + j] = t;
+    }
+}
+int addmm_finish_launch(float *c, uint64_t ldc, const float *input, uint64_t in_rs, uint64_t in_cs, float alpha, float beta,
+                        uint64_t rows, uint64_t n, cudaStream_t s) {
+    if (!rows || !n || (alpha == 1.0f && beta == 0.0f)) return ST_OK;
+    addmm_finish_kernel<<<grid_for(rows * n, 256), 256, 0, s>>>(c, ldc, input, in_rs, in_cs, alpha, beta, rows, n);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+
 // im2col of picograd's pg_conv2d (ops/conv.c:92-113): col[b][row][j], row = (ci*kh + ki)*kw + kj, j = oh*OW + ow,
 // zero where the window leaves the image.  One thread per element of col, j fastest (coalesced writes; reads
 // run along a row of the image).

@@ -813,6 +813,18 @@ int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size
     return st;
 }
 
+int pg_b200_addmm(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb, float *c,
+                  size_t ldc, const float *input, size_t in_row_stride, size_t in_col_stride, float alpha, float beta) {
+    if (!ready()) return g.init_status;
+    if (dtype != DT_F32 && dtype != DT_F16 && dtype != DT_BF16) { set_error("bad dtype %d", dtype); return ST_UNSUPPORTED; }
+    if (m == 0 || n == 0) return ST_OK;
+    if (beta != 0.0f && !input) { set_error("pg_addmm: beta != 0 needs the input"); return ST_GEMM; }
+    Problem p = {dtype, dtype, 0, 0, 1, m, n, k, a, lda, 0, b, ldb, 0, c, ldc, 0, 0};
+    int st = run_problem(p);
+    if (st != ST_OK) return st;
+    return addmm_finish_launch(c, ldc, input, in_row_stride, in_col_stride, alpha, beta, m, n, g.stream);
+}
+
 int pg_b200_permute_copy(int dtype, size_t ndim, const size_t *shape, const size_t *perm, const void *src, void *dst) {
     if (!ready()) return g.init_status;
     if (ndim == 0 || ndim > 8 || !shape || !perm) { set_error("pg_b200_permute_copy: 1 to 8 dimensions"); return ST_UNSUPPORTED; }

@@ -136,6 +136,8 @@ int im2col_launch(const float *x, float *col, uint32_t batch, uint32_t cin, uint
 int bias_rows_launch(float *out, const float *bias, uint32_t cout, uint64_t rows, uint64_t n, cudaStream_t s);
 int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t ndim, const uint64_t *shape, const uint32_t *perm,
                         cudaStream_t s);
+int addmm_finish_launch(float *c, uint64_t ldc, const float *input, uint64_t in_rs, uint64_t in_cs, float alpha, float beta,
+                        uint64_t rows, uint64_t n, cudaStream_t s);
 int fill_f32_launch(float *dst, float v, uint64_t n, cudaStream_t s);
 
 void set_error(const char *fmt, ...);

@@ -71,6 +71,24 @@ def make_conv_inputs(case):
     return x, wt, b
 
 
+# pg_addmm (ops/matmul.c:371-405), f32: (name, m, n, k, input shape, alpha, beta, seed)
+ADDMM_CASES = [
+    ("addmm_3x5x4_full_2_0.5", 3, 5, 4, (3, 5), 2.0, 0.5, 80),                 # tests/test_ops.c:442-448
+    ("addmm_37x53x129_rowvec_1_1", 37, 53, 129, (53,), 1.0, 1.0, 81),
+    ("addmm_24x40x300_colvec_-0.75_3", 24, 40, 300, (24, 1), -0.75, 3.0, 82),
+    ("addmm_16x16x64_beta0", 16, 16, 64, (16, 16), 1.5, 0.0, 83),
+]
+
+
+def make_addmm_inputs(case):
+    _, m, n, k, ishape, _, _, seed = case
+    rng = np.random.default_rng(seed)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    inp = rng.uniform(-1, 1, ishape).astype(np.float32)
+    return inp, a, b
+
+
 def make_bias(n, seed):
     return np.random.default_rng(seed + 1000).uniform(-1, 1, n).astype(np.float32)
 
@@ -114,6 +132,9 @@ def main():
     # the f32 entry nn/nn.c:60,85 calls (Linear forward with and without ReLU)
     a, b = make_inputs(wl.F32, 20, 33, 300, 48)
     out["fused_f32_plain_entry_relu"] = ref.gemm_fused_ex(wl.F32, a, b, make_bias(33, 48), 1, plain_f32_entry=True)
+    for case in ADDMM_CASES:
+        inp, a, b = make_addmm_inputs(case)
+        out[case[0]] = ref.addmm(inp, a, b, case[5], case[6])
     for case in CONV_CASES:
         x, wt, b = make_conv_inputs(case)
         out[case[0]] = ref.conv2d(x, wt, b, case[8], case[9])

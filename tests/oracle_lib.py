@@ -30,6 +30,7 @@ class Oracle:
         L.pgo_bmm.argtypes = [C.c_int, _sz, _sz, _sz, _sz, _vp, _vp, _vp]
         L.pgo_matmul_backward.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp]
         L.pgo_softmax_rows.argtypes = [_vp, _vp, _sz, _sz]
+        L.pgo_addmm.argtypes = [C.c_int, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _sz, C.c_float, C.c_float]
         L.pgo_conv2d.argtypes = [_sz] * 7 + [C.c_int, C.c_int, _vp, _vp, _vp, _vp]
         L.pgo_gelu.argtypes = [_vp, _vp, _sz]
         L.pgo_gelu_grad.argtypes = [_vp, _vp, _vp, _sz]
@@ -97,6 +98,18 @@ class Oracle:
         self.L.pgo_matmul_backward(dtype, m, n, k, _ptr(a), _ptr(b), _ptr(g),
                                    _ptr(ga) if want_a else None, _ptr(gb) if want_b else None)
         return ga, gb
+
+    def addmm(self, dtype, inp, a, b, alpha, beta):
+        """pg_addmm: beta * inp + alpha * (a @ b); inp f32 of shape [m,n], [1,n], [n], [m,1] or [1,1]."""
+        m, k = a.shape
+        n = b.shape[1]
+        inp2 = np.ascontiguousarray(inp, np.float32).reshape((1,) * (2 - inp.ndim) + inp.shape) if inp.ndim < 2 else np.ascontiguousarray(inp, np.float32)
+        rs = 0 if inp2.shape[0] == 1 else inp2.shape[1]
+        cs = 0 if inp2.shape[1] == 1 else 1
+        c = np.zeros((m, n), np.float32)
+        self.L.pgo_addmm(dtype, m, n, k, _ptr(a), a.strides[0] // a.itemsize, _ptr(b), b.strides[0] // b.itemsize, _ptr(c), n,
+                         _ptr(inp2), rs, cs, alpha, beta)
+        return c
 
     def conv2d(self, x, w, bias=None, stride=1, padding=0):
         """pg_conv2d: x [N,Cin,H,W], w [Cout,Cin,kh,kw] f32 -> [N,Cout,OH,OW]."""
@@ -184,6 +197,28 @@ class Reference:
         else:
             self.L.pg_cpu_gemm_fused_ex(dtype, m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), n, bp, act)
         return c
+
+    def addmm(self, inp, a, b, alpha, beta):
+        """pg_addmm (ops/matmul.c:371-405) on picograd's own f32 tensors."""
+        L = self.L
+        L.pg_tensor_from_data.restype = C.POINTER(_PgTensor)
+        L.pg_tensor_from_data.argtypes = [_sz, C.POINTER(_sz), _vp]
+        L.pg_addmm.restype = C.POINTER(_PgTensor)
+        L.pg_addmm.argtypes = [C.POINTER(_PgTensor)] * 3 + [C.c_float, C.c_float]
+        L.pg_tensor_free.argtypes = [C.POINTER(_PgTensor)]
+
+        def mk(x):
+            x = np.ascontiguousarray(x, np.float32)
+            return L.pg_tensor_from_data(x.ndim, (_sz * x.ndim)(*x.shape), _ptr(x))
+
+        ti, ta, tb = mk(inp), mk(a), mk(b)
+        y = L.pg_addmm(ti, ta, tb, alpha, beta)
+        assert y, "pg_addmm returned NULL"
+        t = y.contents
+        out = np.ctypeslib.as_array(C.cast(t.data, C.POINTER(C.c_float)), shape=(t.numel,)).reshape(t.shape[0], t.shape[1]).copy()
+        for h in (y, ti, ta, tb):
+            L.pg_tensor_free(h)
+        return out
 
     def conv2d(self, x, w, bias=None, stride=1, padding=0):
         """pg_conv2d (ops/conv.c:10-146) on picograd's own tensors."""

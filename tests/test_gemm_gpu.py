@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import workloads as wl
-from golden.make_golden import CASES, make_inputs
+from golden.make_golden import ADDMM_CASES, CASES, make_addmm_inputs, make_inputs
 from gpu_util import bits_to_host, gemm_dev, to_dev, to_host
 
 pytestmark = pytest.mark.gpu
@@ -353,6 +353,24 @@ def test_permute_copy_is_the_librarys_own_kernel(pg, shape, perm, dt):
     if list(perm) != list(range(len(shape))):
         assert pg.launch_count() == n0 + 1
     assert y.is_contiguous() and torch.equal(y, x.permute(perm))
+
+
+@pytest.mark.parametrize("case", ADDMM_CASES, ids=[c[0] for c in ADDMM_CASES])
+def test_addmm_against_reference_outputs(pg, case):
+    """pg_addmm (ops/matmul.c:371-405): the f32 product is the bit-exact FFMA one and the tail rounds after every
+    step like picograd's separate passes -> equality with the compiled reference."""
+    inp, a, b = make_addmm_inputs(case)
+    y = pg.pg_addmm(to_dev(inp, wl.F32), to_dev(a, wl.F32), to_dev(b, wl.F32), case[5], case[6]); pg.pg_dev_sync()
+    assert np.array_equal(to_host(y), np.load(GOLDEN)[case[0]])
+
+
+def test_addmm_bf16_on_tensor_cores(pg, oracle):
+    rng = np.random.default_rng(84)
+    a = wl.to_bf16_bits(rng.uniform(-1, 1, (300, 512)).astype(np.float32))
+    b = wl.to_bf16_bits(rng.uniform(-1, 1, (512, 264)).astype(np.float32))
+    inp = rng.uniform(-1, 1, (264,)).astype(np.float32)
+    y = pg.pg_addmm(to_dev(inp, wl.F32), to_dev(a, wl.BF16), to_dev(b, wl.BF16), 0.5, 2.0); pg.pg_dev_sync()
+    assert wl.relerr(to_host(y), oracle.addmm(wl.BF16, inp, a, b, 0.5, 2.0)) <= wl.tolerance(wl.BF16, 512)
 
 
 def test_config4_attention_shaped_bmm(pg, oracle):
