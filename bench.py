@@ -396,6 +396,31 @@ def run_other_config(args):
     if byts:
         line["algorithmic_GBps"] = byts / ms / 1e6
         line["frac_of_measured_hbm"] = byts / ms / 1e6 / hbm_peak
+    if cfg in ("1", "3b"):
+        # launch-bound shapes: the same step replayed from a CUDA graph (20 launches per replay) — device time
+        # without the CPU side of the calls
+        from picograd_b200 import _lib
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            _lib.lib.pg_b200_set_stream(side.cuda_stream)
+            fn(); side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    fn()
+            graph.replay(); side.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(side)
+            for _ in range(10):
+                graph.replay()
+            g1.record(side); side.synchronize()
+        _lib.lib.pg_b200_set_stream(None)
+        gms = g0.elapsed_time(g1) / 200
+        line["graph_replay_ms_per_step"] = gms
+        if byts:
+            line["graph_replay_GBps"] = byts / gms / 1e6
+            line["graph_replay_frac_of_measured_hbm"] = byts / gms / 1e6 / hbm_peak
+        line["graph_replay_TFLOPs"] = flops / gms / 1e9
     print(json.dumps(line), flush=True)
 
 

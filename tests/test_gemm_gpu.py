@@ -373,6 +373,38 @@ def test_addmm_bf16_on_tensor_cores(pg, oracle):
     assert wl.relerr(to_host(y), oracle.addmm(wl.BF16, inp, a, b, 0.5, 2.0)) <= wl.tolerance(wl.BF16, 512)
 
 
+def test_launches_can_be_captured_in_a_cuda_graph(pg, oracle):
+    """Launch-bound loops (decode-like GEMMs) replay from a CUDA graph: after a warm-up call has sized the
+    library's scratch, a call enqueues kernels only (the tensor maps travel by value as kernel parameters)."""
+    from picograd_b200 import _lib
+    m, n, k = 16, 1024, 2048
+    rng = np.random.default_rng(85)
+    a = wl.to_bf16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    bs = [wl.to_bf16_bits(rng.uniform(-1, 1, (k, n)).astype(np.float32)) for _ in range(3)]
+    ad, bds = to_dev(a, wl.BF16), [to_dev(b, wl.BF16) for b in bs]
+    outs = [torch.zeros((m, n), dtype=torch.float32, device="cuda") for _ in bs]
+    bias = torch.from_numpy(rng.uniform(-1, 1, n).astype(np.float32)).cuda()
+    side = torch.cuda.Stream()
+    try:
+        with torch.cuda.stream(side):
+            _lib.lib.pg_b200_set_stream(side.cuda_stream)
+            pg.pg_gemm_fused_ex(wl.BF16, m, n, k, ad, k, bds[0], n, outs[0], n, bias, pg.PG_ACT_RELU)      # warm-up
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for bd, out in zip(bds, outs):
+                    pg.pg_gemm_fused_ex(wl.BF16, m, n, k, ad, k, bd, n, out, n, bias, pg.PG_ACT_RELU)
+            for out in outs:
+                out.zero_()
+            graph.replay(); side.synchronize()
+    finally:
+        _lib.lib.pg_b200_set_stream(None)
+    pg.pg_dev_sync()
+    for b, out in zip(bs, outs):
+        want = oracle.gemm_fused_ex(wl.BF16, a, b, bias.cpu().numpy(), 1)
+        assert wl.relerr(to_host(out), want) <= wl.tolerance(wl.BF16, k)
+
+
 def test_config4_attention_shaped_bmm(pg, oracle):
     """Reduced config 4 (batch 4, seq 256, d 128).  Each GEMM is checked on identical input bytes:
     P = bf16(softmax(S)) is produced once (on the device) and fed to both sides."""
