@@ -206,6 +206,43 @@ def test_edge_shape_sweep(pg, oracle, path):
             assert wl.relerr(got, want) <= wl.tolerance(wl.BF16, k), shp
 
 
+def test_random_shapes_whatever_path_the_library_picks(pg, oracle):
+    """Sixty seeded random problems: dtype, sizes, leading dimensions (aligned or not), bias / activation on or
+    off.  Whatever route the library takes (tensor cores, split-K, cluster, swapped, re-pitched, FFMA), the
+    result is within the path's tolerance and nothing is written outside the n columns of C."""
+    rng = np.random.default_rng(2024)
+    routes = set()
+    for it in range(60):
+        dt = [wl.F32, wl.F16, wl.BF16][rng.integers(3)]
+        m = int(rng.choice([1, 3, 16, 31, 64, 130, 257, 600, 1500]))
+        n = int(rng.choice([1, 5, 32, 100, 128, 264, 513, 1100]))
+        k = int(rng.choice([1, 7, 64, 65, 200, 512, 1111, 2304]))
+        aligned = bool(rng.integers(2))
+        lda = (k + 7) // 8 * 8 if aligned else k + int(rng.integers(0, 4))
+        ldb = (n + 7) // 8 * 8 if aligned else n + int(rng.integers(0, 4))
+        ldc = n + int(rng.integers(0, 5))
+        a32 = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+        b32 = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+        conv = {wl.F32: lambda x: x, wl.F16: wl.to_f16_bits, wl.BF16: wl.to_bf16_bits}[dt]
+        a, b = conv(a32), conv(b32)
+        act = int(rng.integers(3))
+        bias = rng.uniform(-1, 1, n).astype(np.float32) if rng.integers(2) else None
+        abuf = np.zeros((m, lda), a.dtype); abuf[:, :k] = a
+        bbuf = np.zeros((k, ldb), b.dtype); bbuf[:, :n] = b
+        ad, bd = to_dev(abuf, dt), to_dev(bbuf, dt)
+        c = torch.full((m, ldc), float(0xAB), dtype=torch.float32, device="cuda")
+        bt = torch.from_numpy(bias).cuda() if bias is not None else None
+        pg.pg_gemm_fused_ex(dt, m, n, k, ad, lda, bd, ldb, c, ldc, bt, act)
+        pg.pg_dev_sync()
+        routes.add(pg.last_path().split(":")[0] + (":" + pg.last_path().split(":")[-1] if ":" in pg.last_path() else ""))
+        out = c.cpu().numpy()
+        assert np.all(out[:, n:] == np.float32(0xAB)), (it, dt, m, n, k, pg.last_path())
+        want = oracle.gemm_fused_ex(dt, a, b, bias, act)
+        tol = max(wl.tolerance(dt, k), 2e-6)            # GELU's erf differs in the last bits between libm and the GPU
+        assert wl.relerr(out[:, :n], want) <= tol, (it, dt, m, n, k, lda, ldb, act, pg.last_path())
+    assert "simt" in routes and any(r.startswith("tc") for r in routes), routes
+
+
 def test_unaligned_operands_fall_to_ffma_not_to_garbage(pg, oracle):
     a, b = wl.config2(100, 90, 77)
     got = gemm_dev(pg, wl.BF16, a, b)          # ld = 77 / 90: breaks the 16-byte stride rule of TMA
