@@ -959,6 +959,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "f32_parts")) { if (value != 2 && value != 3) return ST_UNSUPPORTED; g.opt_f32_parts = value; return ST_OK; }
     if (!strcmp(name, "f32_tensor_cores")) { g.opt_f32_tc = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "stages")) { g.opt_stages = value; return ST_OK; }
+    if (!strcmp(name, "l2_promotion")) { if (value < 0 || value > 3) return ST_UNSUPPORTED; g_l2_promotion = value; return ST_OK; }
     if (!strcmp(name, "l2_hints")) { g.opt_l2_hints = value; return ST_OK; }
     if (!strcmp(name, "group_m")) { g.opt_group_m = value; return ST_OK; }
     if (!strcmp(name, "host_pipeline")) { g.opt_host_pipeline = value ? 1 : 0; return ST_OK; }

@@ -941,6 +941,10 @@ bool tc_gemm_supported(const TcGemm &g) {
     return true;
 }
 
+// L2 promotion of the operand loads (CUtensorMapL2promotion: 0 none, 1 64 B, 2 128 B, 3 256 B); a tuning hook.
+// Measured at 8192^3, three interleaved rounds on one GPU: none 1536.1-1537.5, 64 B 1535.0-1536.2, 128 B
+// 1534.8-1536.9, 256 B 1531.5-1533.9 TFLOP/s.
+int g_l2_promotion = (int)CU_TENSOR_MAP_L2_PROMOTION_NONE;
 static int encode_operand(CUtensorMap *map, const TcOperand &o, int dtype, uint32_t mn_extent, uint32_t K,
                           uint32_t z, uint32_t mn_box_rows) {
     EncodeTiledFn enc = get_encode_tiled();
@@ -958,7 +962,7 @@ static int encode_operand(CUtensorMap *map, const TcOperand &o, int dtype, uint3
     strides[0] = o.ld * 2;
     strides[1] = (z > 1 ? o.z_stride : o.ld * dims[1]) * 2;   // a single slice gets a harmless stride
     CUresult r = enc(map, dt, 3, const_cast<void *>(o.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     CU_TENSOR_MAP_SWIZZLE_128B, (CUtensorMapL2promotion)g_l2_promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled(operand) failed: %d", (int)r);
         return ST_GEMM;

@@ -76,6 +76,7 @@ int tc_gemm_launch(const TcGemm &g);
 // true if operands satisfy the TMA rules (16-byte aligned bases and strides)
 bool tc_gemm_supported(const TcGemm &g);
 int wait_timeout_selftest_launch(uint32_t *status, unsigned limit_ms, cudaStream_t stream);
+extern int g_l2_promotion;   // CUtensorMapL2promotion of the operand tensor maps
 int tc_num_configs();
 const char *tc_config_name(int cfg);
 int tc_config_index(const char *name);   // -1 if unknown
