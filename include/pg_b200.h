@@ -192,7 +192,11 @@ PG_B200_API int pg_b200_fill_f32(float *dst, float value, size_t n);
  *     library, until the process exits.  All calls share it: calls whose kernels overlap on the GPU
  *     (other streams, other threads) race; calls on one stream are ordered.
  *   - The first call on a device resolves the array's device address and sets kernel attributes;
- *     make that call before any stream capture begins.
+ *     make that call before any stream capture begins.  It is also the call at which the driver
+ *     loads this library's kernels and the array into device memory (lazy module loading): a
+ *     one-time reservation of the array plus a few MiB of code, so make it at start-up, before your
+ *     arena takes the remaining memory.  Later calls leave free device memory unchanged.
+ *   - One caller thread, like the rest of this library (the per-device set-up is not locked).
  *   - The call synchronises its stream before returning, so a kernel-side failure is returned as
  *     PG_ERR_GEMM by the call itself. */
 #define PG_B200_STATIC_SCRATCH_BYTES (16u << 20)

@@ -159,8 +159,8 @@ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
 // 0.5 x (1 + erf(x / sqrt 2)), picograd's act_apply (backend/cpu/gemm.c:632-636), with
 // erf(a) = sign(a) (1 - 2^(t Q(t))), t = min(|a|, 4): one piece, no branch, 13 instructions, so the
 // epilogue warps take few issue slots from the MMA and producer warps they share schedulers with.
-// Coefficients and their check (erf to 8e-8 absolute, GELU to 5e-7 at |x| = 6) come from
-// fit_erf_coefficients.py.
+// Q is a weighted least-squares fit of log2(erfc(t)) / t on [0, 4.05]; tests/test_erf_coefficients.py refits it
+// and checks these numbers (erf to 8e-8 absolute, GELU to 5e-7 at |x| = 6).
 __device__ __forceinline__ float erf_nodiv(float a) {
     const float t = fminf(fabsf(a), 4.0f);
     float r = fmaf(-4.477160110e-05f, t, 4.406937805e-04f);

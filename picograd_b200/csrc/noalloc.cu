@@ -5,13 +5,17 @@
 // the device-wide synchronisation cudaMalloc and cudaFree imply, a plugin whose host forbids
 // allocation after start-up.  The regular entry points grow a scratch buffer with cudaMalloc when a
 // shape needs split-K; this one keeps the K-slices in a fixed array that is part of the library
-// image, so it allocates nothing: no cudaMalloc, cudaFree, cudaMallocHost or allocating library call
-// on any path, first call included.
+// image, so it calls no cudaMalloc, cudaFree, cudaMallocHost or allocating library routine on any
+// path.  What the first call on a device does cost: with CUDA's lazy module loading that call is when
+// the driver places this library's kernels and the array itself in device memory (a one-time
+// reservation the driver makes, not an allocator call), so it belongs at start-up, before an arena
+// takes the remaining memory; every later call leaves free memory untouched.
 //
 // The price: the array is PG_B200_STATIC_SCRATCH_BYTES (16 MiB) of device memory on every GPU that
 // loads the library, held until the process exits, and it is shared by all calls — two calls whose
 // kernels overlap on the GPU (different streams, different host threads) race on it.  Calls on one
-// stream are ordered and safe.
+// stream are ordered and safe.  Like the rest of the library it expects one caller thread: the
+// per-device set-up below is not guarded against two threads running it at once.
 
 #include "../../include/pg_b200.h"
 #include "pg_internal.h"
@@ -57,8 +61,8 @@ static int setup_current_device(StaticScratch **out) {
             cudaGetLastError();
             return ST_GEMM;
         }
+        s.status = (uint32_t *)p_status;      // slices last: it is the "set-up done" mark
         s.slices = (float *)p_slices;
-        s.status = (uint32_t *)p_status;
     }
     *out = &s;
     return ST_OK;

@@ -89,6 +89,48 @@ def make_addmm_inputs(case):
     return inp, a, b
 
 
+# bwd_matmul through pg_backward (autograd/autograd.c:561-706, :2483-2533).
+# The six shape modes of picograd's tests/test_autograd.c:288-332 (2-D x 2-D, vector x 2-D, 2-D x vector,
+# vector x vector, batched x batched, batched x shared 2-D), loss = sum(matmul): (name, a shape, b shape, seed)
+BWD_MODE_CASES = [
+    ("bwd_mode_2d2d", (3, 4), (4, 2), 90),
+    ("bwd_mode_v2d", (4,), (4, 2), 91),
+    ("bwd_mode_2dv", (3, 4), (4,), 92),
+    ("bwd_mode_vv", (4,), (4,), 93),
+    ("bwd_mode_bmm", (2, 3, 4), (2, 4, 5), 94),
+    ("bwd_mode_bcast_batch", (2, 3, 4), (4, 5), 95),
+]
+# Products large enough for the GEMM route of bwd_matmul (m*n*k > 4096, autograd.c:635), with a seeded
+# upstream gradient (loss = sum(y * upstream)): (name, dtype, a shape, b shape, seed)
+BWD_CASES = [
+    ("bwd_f32_40x72x56", wl.F32, (40, 56), (56, 72), 100),
+    ("bwd_f32_72x136x100", wl.F32, (72, 100), (100, 136), 101),
+    ("bwd_bf16_40x72x56", wl.BF16, (40, 56), (56, 72), 102),
+    ("bwd_bf16_136x264x200", wl.BF16, (136, 200), (200, 264), 103),
+    ("bwd_bf16_128x64x264", wl.BF16, (128, 264), (264, 64), 104),
+    ("bwd_f16_200x264x136", wl.F16, (200, 136), (136, 264), 105),
+    ("bwd_bf16_batched_3x72x136x64", wl.BF16, (3, 72, 64), (3, 64, 136), 106),
+    ("bwd_bf16_shared_b_3x72x136x64", wl.BF16, (3, 72, 64), (64, 136), 107),
+    ("bwd_f32_shared_b_2x48x40x96", wl.F32, (2, 48, 96), (96, 40), 108),
+]
+
+
+def make_bwd_inputs(dtype, ashape, bshape, seed, with_upstream=True):
+    """Seeded operands (f32 values or 16-bit patterns) and the upstream gradient of the matmul's output."""
+    rng = np.random.default_rng(seed)
+    a = rng.uniform(-1, 1, ashape).astype(np.float32)
+    b = rng.uniform(-1, 1, bshape).astype(np.float32)
+    if dtype == wl.BF16:
+        a, b = wl.to_bf16_bits(a), wl.to_bf16_bits(b)
+    elif dtype == wl.F16:
+        a, b = wl.to_f16_bits(a), wl.to_f16_bits(b)
+    yshape = tuple(ashape[:-1]) + tuple(bshape[-1:]) if len(bshape) > 1 else tuple(ashape[:-1])
+    if len(ashape) == 1:
+        yshape = tuple(bshape[1:]) if len(bshape) > 1 else (1,)
+    g = rng.standard_normal(yshape).astype(np.float32) if with_upstream else None
+    return a, b, g
+
+
 def make_bias(n, seed):
     return np.random.default_rng(seed + 1000).uniform(-1, 1, n).astype(np.float32)
 
@@ -138,6 +180,31 @@ def main():
     for case in CONV_CASES:
         x, wt, b = make_conv_inputs(case)
         out[case[0]] = ref.conv2d(x, wt, b, case[8], case[9])
+    # the matmul node of the autograd, driven through picograd's public pg_ag_matmul / pg_backward
+    for name, ash, bsh, seed in BWD_MODE_CASES:
+        a, b, _ = make_bwd_inputs(wl.F32, ash, bsh, seed, with_upstream=False)
+        y, ga, gb = ref.matmul_backward(wl.F32, a, b, None)
+        out[name + "_y"], out[name + "_ga"], out[name + "_gb"] = y, ga, gb
+    for name, dt, ash, bsh, seed in BWD_CASES:
+        a, b, g = make_bwd_inputs(dt, ash, bsh, seed)
+        y, ga, gb = ref.matmul_backward(dt, a, b, g)
+        y2, ga2, gb2 = ref.matmul_backward(dt, a, b, g, jit=False)      # the eager route gives the same bits
+        assert np.array_equal(ga, ga2) and np.array_equal(gb, gb2) and np.array_equal(y, y2), name
+        out[name + "_ga"], out[name + "_gb"] = ga, gb
+    # leaves drawn the way picograd's own tests draw them (tests/test_autograd.c:319-330: pg_seed(11), then
+    # pg_var_uniform per leaf), kept in the file because only picograd's generator can reproduce them
+    ba, bb, ba2, bw = ref.uniform(11, [(2, 3, 4), (2, 4, 5), (2, 3, 4), (4, 5)])
+    for name, a, b in (("bwd_pgseed11_bmm", ba, bb), ("bwd_pgseed11_bcast_batch", ba2, bw)):
+        y, ga, gb = ref.matmul_backward(wl.F32, a, b, None)
+        out[name + "_a"], out[name + "_b"] = a, b
+        out[name + "_y"], out[name + "_ga"], out[name + "_gb"] = y, ga, gb
+    # the two-layer network of tests/test_autograd.c:393-421 (pg_seed(55)); zero biases as there
+    x, = ref.uniform(55, [(2, 3)])
+    w1, w2 = ref.uniform(56, [(3, 8), (8, 2)], -0.5, 0.5)
+    mlp = ref.mlp_backward(x, w1, np.zeros(8, np.float32), w2, np.zeros(2, np.float32))
+    out["bwd_mlp_x"], out["bwd_mlp_w1"], out["bwd_mlp_w2"] = x, w1, w2
+    for key, v in mlp.items():
+        out["bwd_mlp_" + key] = v
     # picograd's own dyadic correctness data (benchmarks/bench_gemm_cuda.c:16-65), exact in f32
     s = 64
     d = wl.dyadic(s * s).reshape(s, s)

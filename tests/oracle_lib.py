@@ -99,6 +99,29 @@ class Oracle:
                                    _ptr(ga) if want_a else None, _ptr(gb) if want_b else None)
         return ga, gb
 
+    def matmul_backward_nd(self, dtype, a, b, g):
+        """bwd_matmul with picograd's shape modes (autograd/autograd.c:591-706): a 1-D operand is a row / column
+        vector, batch dimensions are looped over, and a B shared by the batch sums its gradient over the batch.
+        g has the shape of the matmul's output.  Returns gradients with the shapes of a and b."""
+        av, bv = a.ndim == 1, b.ndim == 1
+        a2 = a.reshape(1, -1) if av else a
+        b2 = b.reshape(-1, 1) if bv else b
+        m, k = a2.shape[-2:]
+        n = b2.shape[-1]
+        abat, bbat = a2.ndim > 2, b2.ndim > 2
+        nbatch = int(np.prod(a2.shape[:-2])) if abat else (int(np.prod(b2.shape[:-2])) if bbat else 1)
+        a3 = a2.reshape(nbatch if abat else 1, m, k)
+        b3 = b2.reshape(nbatch if bbat else 1, k, n)
+        g3 = np.ascontiguousarray(g, np.float32).reshape(nbatch, m, n)
+        ga = np.zeros(a3.shape, np.float32)
+        gb = np.zeros(b3.shape, np.float32)
+        for s in range(nbatch):
+            x, y = self.matmul_backward(dtype, np.ascontiguousarray(a3[s if abat else 0]),
+                                        np.ascontiguousarray(b3[s if bbat else 0]), g3[s])
+            ga[s if abat else 0] += x
+            gb[s if bbat else 0] += y
+        return ga.reshape(a.shape), gb.reshape(b.shape)
+
     def addmm(self, dtype, inp, a, b, alpha, beta):
         """pg_addmm: beta * inp + alpha * (a @ b); inp f32 of shape [m,n], [1,n], [n], [m,1] or [1,1]."""
         m, k = a.shape
@@ -167,6 +190,26 @@ class _PgTensor(C.Structure):
 
 class _ConvCfg(C.Structure):
     _fields_ = [("stride", C.c_int), ("padding", C.c_int)]       # ops/conv.h:7-10
+
+
+class _PgTensorFull(C.Structure):
+    """All of pg_tensor (core/tensor.h:21-36): needed to read the dtype of a value."""
+    _fields_ = [("ndim", _sz), ("shape", _sz * 8), ("stride", _sz * 8), ("numel", _sz), ("data", _vp),
+                ("data_ref", _vp), ("is_view", C.c_bool), ("view_parent", _vp), ("dtype", C.c_int), ("elem_size", _sz)]
+
+
+class _PgNode(C.Structure):
+    """pg_node (autograd/autograd.h:51-62); public in picograd, so that a 16-bit leaf can be built by hand."""
+    _fields_ = [("value", C.POINTER(_PgTensorFull)), ("grad", C.POINTER(_PgTensorFull)), ("nparents", _sz),
+                ("parents", _vp), ("ctx", _vp), ("backward", _vp), ("ag_op", C.c_int), ("requires_grad", C.c_bool),
+                ("refs", C.c_uint), ("mark", C.c_ubyte)]
+
+
+def _tensor_to_numpy(tp):
+    """f32 pg_tensor* -> numpy copy with the tensor's shape."""
+    t = tp.contents
+    shape = tuple(t.shape[i] for i in range(t.ndim))
+    return np.ctypeslib.as_array(C.cast(t.data, C.POINTER(C.c_float)), shape=(t.numel,)).reshape(shape).copy()
 
 
 class Reference:
@@ -242,6 +285,111 @@ class Reference:
         out = np.ctypeslib.as_array(C.cast(t.data, C.POINTER(C.c_float)), shape=(t.numel,)).reshape(shape).copy()
         for h in (y, tx, tw) + ((tb,) if tb is not None else ()):
             L.pg_tensor_free(h)
+        return out
+
+    # ---- autograd (autograd/autograd.h:64-66, :113, :117, :155) -------------------------------
+    def _ag_bind(self):
+        L = self.L
+        NP, TP, SP = C.POINTER(_PgNode), C.POINTER(_PgTensorFull), C.POINTER(_sz)
+        L.pg_var_from_data.restype = NP
+        L.pg_var_from_data.argtypes = [_sz, SP, _vp, C.c_bool]
+        L.pg_var_uniform.restype = NP
+        L.pg_var_uniform.argtypes = [_sz, SP, C.c_float, C.c_float, C.c_bool]
+        for name in ("pg_ag_matmul", "pg_ag_mul", "pg_ag_add"):
+            getattr(L, name).restype = NP
+            getattr(L, name).argtypes = [NP, NP]
+        for name in ("pg_ag_sum_all", "pg_ag_mean_all", "pg_ag_sigmoid"):
+            getattr(L, name).restype = NP
+            getattr(L, name).argtypes = [NP]
+        L.pg_backward.argtypes = [NP]
+        L.pg_backward.restype = None
+        L.pg_node_free.argtypes = [NP]
+        L.pg_node_free.restype = None
+        L.pg_tensor_from_data_dtype.restype = TP
+        L.pg_tensor_from_data_dtype.argtypes = [C.c_int, _sz, SP, _vp]
+        L.pg_tensor_free.argtypes = [_vp]
+        L.pg_tensor_free.restype = None
+        L.pg_seed.argtypes = [C.c_ulonglong]
+        L.pg_autograd_set_jit.argtypes = [C.c_bool]
+        return L
+
+    def _leaf(self, dtype, arr, requires_grad=True):
+        """A leaf node holding `arr` (f32 values, or uint16 bit patterns of f16/bf16).  A 16-bit leaf is an
+        f32 leaf whose value tensor is swapped for one of the 16-bit dtype, as autograd.c:566-590 expects."""
+        L = self.L
+        arr = np.ascontiguousarray(arr)
+        shape = (_sz * arr.ndim)(*arr.shape)
+        if dtype == F32:
+            arr = np.ascontiguousarray(arr, np.float32)
+            node = L.pg_var_from_data(arr.ndim, shape, _ptr(arr), requires_grad)
+            assert node
+            return node
+        zeros = np.zeros(arr.shape, np.float32)
+        node = L.pg_var_from_data(arr.ndim, shape, _ptr(zeros), requires_grad)
+        assert node and arr.dtype == np.uint16
+        t16 = L.pg_tensor_from_data_dtype(dtype, arr.ndim, shape, _ptr(arr))
+        assert t16 and t16.contents.dtype == dtype
+        L.pg_tensor_free(C.cast(node.contents.value, _vp))
+        node.contents.value = t16
+        return node
+
+    def matmul_backward(self, dtype, a, b, upstream=None, jit=True):
+        """pg_ag_matmul(a, b) followed by pg_backward of loss = sum(y * upstream) (loss = sum(y) when upstream
+        is None, the form of picograd's tests/test_autograd.c:281-286).  Returns (y, grad a, grad b)."""
+        L = self._ag_bind()
+        L.pg_autograd_set_jit(bool(jit))
+        A, B = self._leaf(dtype, a), self._leaf(dtype, b)
+        y = L.pg_ag_matmul(A, B)
+        assert y, "pg_ag_matmul returned NULL"
+        nodes = [A, B, y]
+        top = y
+        if upstream is not None:
+            w = self._leaf(F32, np.ascontiguousarray(upstream, np.float32), requires_grad=False)
+            top = L.pg_ag_mul(y, w)
+            assert top, "pg_ag_mul returned NULL"
+            nodes += [w, top]
+        loss = L.pg_ag_sum_all(top)
+        assert loss
+        nodes.append(loss)
+        L.pg_backward(loss)
+        out = (_tensor_to_numpy(y.contents.value), _tensor_to_numpy(A.contents.grad), _tensor_to_numpy(B.contents.grad))
+        for n in reversed(nodes):
+            L.pg_node_free(n)
+        L.pg_autograd_set_jit(True)
+        return out
+
+    def uniform(self, seed, shapes, lo=-1.0, hi=1.0):
+        """pg_seed(seed) then one pg_var_uniform per shape, as picograd's tests draw their leaves
+        (tests/test_autograd.c:319-330); returns the drawn f32 arrays."""
+        L = self._ag_bind()
+        L.pg_seed(seed)
+        out = []
+        for shp in shapes:
+            n = L.pg_var_uniform(len(shp), (_sz * len(shp))(*shp), lo, hi, True)
+            assert n
+            out.append(_tensor_to_numpy(n.contents.value))
+            L.pg_node_free(n)
+        return out
+
+    def mlp_backward(self, x, w1, b1, w2, b2):
+        """The two-layer network of picograd's tests/test_autograd.c:393-421: mean(sigmoid(x w1 + b1) w2 + b2),
+        pg_backward.  Returns the values and gradients around both matmul nodes."""
+        L = self._ag_bind()
+        X, W1, B1, W2, B2 = (self._leaf(F32, t) for t in (x, w1, b1, w2, b2))
+        mm1 = L.pg_ag_matmul(X, W1)
+        z1 = L.pg_ag_add(mm1, B1)
+        h = L.pg_ag_sigmoid(z1)
+        mm2 = L.pg_ag_matmul(h, W2)
+        y = L.pg_ag_add(mm2, B2)
+        loss = L.pg_ag_mean_all(y)
+        assert mm1 and z1 and h and mm2 and y and loss
+        L.pg_backward(loss)
+        val = lambda n: _tensor_to_numpy(n.contents.value)
+        grd = lambda n: _tensor_to_numpy(n.contents.grad)
+        out = {"h": val(h), "g_mm1": grd(mm1), "g_mm2": grd(mm2), "g_x": grd(X), "g_w1": grd(W1), "g_h": grd(h),
+               "g_w2": grd(W2)}
+        for n in (loss, y, mm2, h, z1, mm1, B2, W2, B1, W1, X):
+            L.pg_node_free(n)
         return out
 
     def gemm_ex(self, dtype, a, b, c=None):

@@ -14,13 +14,23 @@ from gpu_util import to_dev
 pytestmark = pytest.mark.gpu
 
 
+# Normwise error of the whole chain measured on B200 where the second product's own bound is smallest (short rows):
+# a last-bit difference in a score or in exp() flips the 16-bit rounding of a few probabilities, which shows as an
+# error of O that does not shrink with the row length.  The floors are twice the largest value measured over the
+# shapes of this file.
+E2E_FLOOR = {wl.BF16: 1.2e-4, wl.F16: 1.6e-5}
+
+
 def e2e_tolerance(dt, sk):
-    """End-to-end bound for the whole chain.  Each product alone meets 1e-5 * sqrt(K) on identical input bytes
-    (tests/test_gemm_gpu.py).  End to end, a last-bit difference in a score or in exp() can flip the 16-bit
-    rounding of an element of P by one unit (2^-8 relative for bf16, 2^-11 for f16); a small fraction of the
-    elements does, which adds about a quarter of that unit to the normwise error of O."""
-    eps16 = 2.0 ** -8 if dt == wl.BF16 else 2.0 ** -11
-    return max(wl.tolerance(dt, sk), 0.25 * eps16)
+    """End-to-end bound for the whole chain: the stated tolerance of the second product, 1e-5 * sqrt(Sk) (each product
+    alone meets it on identical input bytes, tests/test_gemm_gpu.py), with the measured rounding-flip floor for short
+    rows."""
+    return max(wl.tolerance(dt, sk), E2E_FLOOR[dt])
+
+
+def within(err, dt, sk, what=""):
+    print(f"attention e2e {what} dt={dt} sk={sk}: {err:.3e} (bound {e2e_tolerance(dt, sk):.2e})")
+    return err <= e2e_tolerance(dt, sk)
 
 
 def make_qkv(bt, sq, sk, d, dt, seed):
@@ -52,7 +62,7 @@ def test_fused_equals_the_chain_on_the_cpu(pg, oracle, dt, shape):
     got = pg.pg_attention_bmm(to_dev(q, dt), to_dev(kt, dt), to_dev(v, dt))
     pg.pg_dev_sync()
     assert pg.last_path() == "attn:fused_128x128"
-    assert wl.relerr(got.cpu().numpy(), want) <= e2e_tolerance(dt, sk)
+    assert within(wl.relerr(got.cpu().numpy(), want), dt, sk, str(shape))
 
 
 def test_q_from_shared_memory_and_from_tensor_memory_agree_bit_for_bit(pg):
@@ -79,7 +89,7 @@ def test_many_units_per_cta_and_both_paths_agree(pg):
     chain = pg.pg_attention_bmm(qd, ktd, vd); pg.pg_dev_sync()
     pg.set_option("fused_attention", 1)
     assert pg.last_path() == "attn:chain"
-    assert wl.relerr(fused.cpu().numpy(), chain.cpu().numpy()) <= e2e_tolerance(wl.BF16, sk)
+    assert within(wl.relerr(fused.cpu().numpy(), chain.cpu().numpy()), wl.BF16, sk, 'fused vs chain')
     # rows of P sum to one: with V all ones every output is 1 up to the 16-bit rounding of P
     ones = torch.ones_like(vd)
     o = pg.pg_attention_bmm(qd, ktd, ones); pg.pg_dev_sync()
@@ -93,7 +103,7 @@ def test_shapes_the_fused_kernel_does_not_take_run_the_chain(pg, oracle, shape):
     want = oracle_chain(oracle, wl.BF16, q, kt, v)
     got = pg.pg_attention_bmm(to_dev(q, wl.BF16), to_dev(kt, wl.BF16), to_dev(v, wl.BF16)); pg.pg_dev_sync()
     assert pg.last_path() == "attn:chain"
-    assert wl.relerr(got.cpu().numpy(), want) <= e2e_tolerance(wl.BF16, sk)
+    assert within(wl.relerr(got.cpu().numpy(), want), wl.BF16, sk)
 
 
 def test_large_scores_do_not_overflow(pg, oracle):
@@ -104,4 +114,4 @@ def test_large_scores_do_not_overflow(pg, oracle):
     want = oracle_chain(oracle, wl.BF16, q, kt, v)
     got = pg.pg_attention_bmm(to_dev(q, wl.BF16), to_dev(kt, wl.BF16), to_dev(v, wl.BF16)); pg.pg_dev_sync()
     assert np.isfinite(got.cpu().numpy()).all()
-    assert wl.relerr(got.cpu().numpy(), want) <= e2e_tolerance(wl.BF16, sk)
+    assert within(wl.relerr(got.cpu().numpy(), want), wl.BF16, sk)
