@@ -176,6 +176,16 @@ PG_B200_API int pg_b200_gelu_grad(const float *x, const float *gy, float *out, s
 PG_B200_API int pg_b200_cast_f32(const float *src, uint16_t *dst, int dtype16, size_t n);
 PG_B200_API int pg_b200_fill_f32(float *dst, float value, size_t n);
 
+/* ---- more than one GPU ------------------------------------------------------- */
+
+/* No counterpart in picograd (one device only, backend/cuda/cuda.c:49-55).  pg_gemm_ex is partitioned over the GPUs
+ * of a node by N-column shards of B and C, and a caller that wants the whole C on one device all-gathers the shards
+ * (NCCL).  An all-gather delivers shard g as a contiguous row-major [rows][width] block at staging + g*rows*width;
+ * this kernel writes the row-major [rows][n] matrix (leading dimension ld) whose columns [g*width, (g+1)*width),
+ * clipped at n, are shard g.  Device pointers; HBM-bound (each element read once, written once). */
+PG_B200_API int pg_b200_gather_relayout(const float *staging, float *dst, size_t shards, size_t rows, size_t width,
+                                        size_t n, size_t ld);
+
 /* ---- for callers that must not allocate ------------------------------------- */
 
 /* No counterpart in picograd.  pg_gemm_ex for f16/bf16 through the split-K tensor-core path, with
@@ -228,6 +238,12 @@ PG_B200_API int pg_b200_selftest_wait_timeout(unsigned limit_ms);
 /* Diagnostics of the timing experiments (option "debug" bit 32): copies per-CTA cycle counters
  * of the last tensor-core launch, 16 per CTA, to `out`. */
 PG_B200_API int pg_b200_debug_counters(uint64_t *out, size_t count);
+/* Test hook (host arithmetic only, needs no GPU): how the tensor-core kernel deals the K ranges of a partly filled
+ * last wave out to all SMs.  `tiles` output tiles of `k_blocks` 64-deep K blocks on `slots` resident CTA pairs;
+ * part (0, 1) of CTA pair `cluster`.  out = {1 if the balanced schedule is used, whole-tile waves, index of the tail
+ * tile, first K block, number of K blocks (0 = no such part), role (1 = first slice: stored, 2 = second slice: added)}. */
+PG_B200_API int pg_b200_debug_tail_schedule(uint64_t tiles, unsigned slots, unsigned k_blocks, unsigned cluster,
+                                            unsigned part, unsigned out[6]);
 /* Number of kernels this library has launched since it was loaded. */
 PG_B200_API uint64_t pg_b200_launch_count(void);
 /* Name of the path the last GEMM call took ("tc:2cta_256x256", "simt", ...). */

@@ -42,6 +42,7 @@ SIGNATURES = {
     "pg_b200_gelu_grad": (_i, [_vp, _vp, _vp, _sz]),
     "pg_b200_cast_f32": (_i, [_vp, _vp, _i, _sz]),
     "pg_b200_fill_f32": (_i, [_vp, C.c_float, _sz]),
+    "pg_b200_gather_relayout": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _sz]),
     "pg_b200_gemm_ex_static_scratch": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _i]),
     "pg_b200_set_device": (_i, [_i]),
     "pg_b200_set_stream": (_i, [_vp]),
@@ -52,6 +53,7 @@ SIGNATURES = {
     "pg_b200_launch_count": (C.c_uint64, []),
     "pg_b200_last_path": (C.c_char_p, []),
     "pg_b200_debug_counters": (_i, [_vp, _sz]),
+    "pg_b200_debug_tail_schedule": (_i, [C.c_uint64, C.c_uint, C.c_uint, C.c_uint, C.c_uint, _vp]),
     "pg_b200_selftest_wait_timeout": (_i, [C.c_uint]),
 }
 

@@ -319,6 +319,17 @@ def pg_addmm(inp, m1, m2, alpha=1.0, beta=1.0):
     return out
 
 
+def pg_gather_relayout(staging, full, shards, rows, width, n):
+    """The re-layout after an all-gather of N-column shards (no counterpart in picograd, which is single-device):
+    staging [shards][rows][width] f32 (shard g a contiguous row-major block) -> full [rows][n] row-major, columns
+    [g*width, (g+1)*width) from shard g.  Device tensors."""
+    _ready()
+    if staging.dtype != torch.float32 or full.dtype != torch.float32:
+        raise TypeError("pg_gather_relayout: float32")
+    _check(lib.pg_b200_gather_relayout(staging.data_ptr(), full.data_ptr(), shards, rows, width, n, full.stride(0)),
+           "pg_b200_gather_relayout")
+
+
 def _permute_copy(t, perm):
     """permute_copy (ops/matmul.c:21-42) with the library's own kernel: a new contiguous tensor whose dimension d
     is dimension perm[d] of t."""

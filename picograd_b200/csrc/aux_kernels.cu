@@ -265,6 +265,44 @@ int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t n
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
+// Re-layout after an all-gather of N-column shards: `staging` holds the G shards one after the other, shard g as a
+// row-major [rows][width] block (the layout an all-gather of contiguous shards produces); dst is the row-major
+// [rows][n] matrix whose columns [g*width, g*width + width) (clipped at n) are shard g.  HBM-bound: every element is
+// read once and written once, 16 bytes per thread per step when width, n, ld and the bases allow it.
+template <typename V>
+__global__ void gather_relayout_kernel(const V *__restrict__ staging, V *__restrict__ dst, uint32_t shards, uint64_t rows,
+                                       uint64_t width_v, uint64_t n_v, uint64_t ld_v) {
+    // one "v" = one V (4 floats or 1 float); n_v columns of dst in units of V
+    const uint64_t total = rows * n_v;
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const uint64_t r = i / n_v, c = i - r * n_v;
+        const uint64_t g = c / width_v, j = c - g * width_v;
+        dst[r * ld_v + c] = __ldcs(staging + (g * rows + r) * width_v + j);
+    }
+}
+int gather_relayout_launch(const float *staging, float *dst, uint32_t shards, uint64_t rows, uint64_t width, uint64_t n,
+                           uint64_t ld, cudaStream_t s) {
+    if (!rows || !n) return ST_OK;
+    if (!shards || !width || (uint64_t)shards * width < n || ld < n) return ST_UNSUPPORTED;
+    const bool vec = width % 4 == 0 && n % 4 == 0 && ld % 4 == 0 && ((uintptr_t)staging & 15u) == 0 && ((uintptr_t)dst & 15u) == 0;
+    const int sms = device_sm_count();
+    if (vec) {
+        const uint64_t total = rows * (n / 4);
+        uint64_t blocks = (total + 255) / 256;
+        if (blocks > (uint64_t)sms * 16) blocks = (uint64_t)sms * 16;
+        gather_relayout_kernel<float4><<<(unsigned)blocks, 256, 0, s>>>((const float4 *)staging, (float4 *)dst, shards, rows,
+                                                                       width / 4, n / 4, ld / 4);
+    } else {
+        const uint64_t total = rows * n;
+        uint64_t blocks = (total + 255) / 256;
+        if (blocks > (uint64_t)sms * 16) blocks = (uint64_t)sms * 16;
+        gather_relayout_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(staging, dst, shards, rows, width, n, ld);
+    }
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+
 // The element-wise tail of pg_addmm (ops/matmul.c:383-404): c = (0 + input) * beta + c * alpha with every step a
 // separate rounded f32 operation (no contraction into an FMA), input read through (row, column) element strides.
 __global__ void addmm_finish_kernel(float *__restrict__ c, uint64_t ldc, const float *__restrict__ input, uint64_t in_rs,

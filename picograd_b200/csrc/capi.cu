@@ -45,8 +45,9 @@ struct State {
     DeviceBuf attn_ws;           // S and P of the chain form of pg_b200_attention_bmm
     int opt_cluster_splitk = 1;  // K-slices of a skinny product as one cluster (reduction through distributed shared memory)
     int opt_host_blk = 0;        // slab size of the staged host-pointer pipeline (0 = 2048)
-    int opt_stream_k = 0;        // stream-K for a partly filled last wave: correct, but measured 5-20 % slower
-                                 // than the plain schedule on B200 (partial waves already run faster), so off
+    int opt_stream_k = 1;        // balanced last wave: the K ranges of the tiles of a partly filled last wave are dealt
+                                 // out to all SMs, two slices per tile at most (chosen when it gains >= 2 %)
+    int opt_pdl = 1;             // programmatic dependent launch of the tensor-core kernels
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
     int opt_l2_hints = 0;    // see TcParams::l2_hints
     int opt_group_m = 0;     // 0: choose
@@ -250,7 +251,8 @@ static int run_tc(const Problem &p) {
     t.force_cfg = g.opt_cfg; t.force_epilogue = g.opt_epilogue;
     t.stages = g.opt_stages; t.debug = g.opt_debug; t.l2_hints = g.opt_l2_hints; t.group_m = g.opt_group_m;
     t.stream = g.stream; t.dev_status = g.dev_status; t.prof = g.prof;
-    t.allow_stream_k = g.opt_stream_k;
+    t.allow_stream_k = g.opt_stream_k && !p.no_split_k;
+    t.pdl = g.opt_pdl;
     t.cluster_splitk = g.opt_cluster_splitk;
     t.counters = g.counters; t.num_counters = g.num_counters;
 
@@ -932,6 +934,14 @@ int pg_b200_fill_f32(float *dst, float value, size_t n) {
     return fill_f32_launch(dst, value, n, g.stream);
 }
 
+int pg_b200_gather_relayout(const float *staging, float *dst, size_t shards, size_t rows, size_t width, size_t n, size_t ld) {
+    if (!ready()) return g.init_status;
+    if (shards > 0xFFFFFFFFull) return ST_UNSUPPORTED;
+    const int st = gather_relayout_launch(staging, dst, (uint32_t)shards, rows, width, n, ld, g.stream);
+    if (st == ST_UNSUPPORTED) set_error("pg_b200_gather_relayout: %zu shards of %zu columns do not cover n = %zu (ld %zu)", shards, width, n, ld);
+    return st;
+}
+
 int pg_b200_debug_counters(uint64_t *out, size_t count) {
     if (!ready() || !g.prof) return ST_UNSUPPORTED;
     if (count > 512 * 16) count = 512 * 16;
@@ -942,6 +952,11 @@ int pg_b200_debug_counters(uint64_t *out, size_t count) {
 int pg_b200_selftest_wait_timeout(unsigned limit_ms) {
     if (!ready()) return g.init_status;
     return wait_timeout_selftest_launch(g.dev_status, limit_ms, g.stream);
+}
+
+int pg_b200_debug_tail_schedule(uint64_t tiles, unsigned slots, unsigned k_blocks, unsigned cluster, unsigned part,
+                                 unsigned out[6]) {
+    return tc_tail_schedule(tiles, slots, k_blocks, cluster, part, out);
 }
 
 const char *pg_b200_last_error(void) { return g.err; }
@@ -970,6 +985,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "cluster_splitk")) { g.opt_cluster_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "pdl")) { g.opt_pdl = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);
     return ST_UNSUPPORTED;

@@ -29,7 +29,17 @@
 #include <stdio.h>
 #include <string.h>
 
+// Timing experiments (TcParams::debug: loads / stores / MMAs switched off, in-kernel cycle counters) exist only in
+// builds made with -DPG_TC_EXPERIMENTS=1.  In the product build the switches are compile-time false, so the role
+// loops hold no experiment branch and the "debug" option does nothing.
+#ifndef PG_TC_EXPERIMENTS
+#define PG_TC_EXPERIMENTS 0
+#endif
+
 namespace pgb {
+
+constexpr bool kExperiments = PG_TC_EXPERIMENTS != 0;
+#define PG_DBG(bits) (kExperiments && (p.debug & (bits)))
 
 // ---------------------------------------------------------------------------------------------
 // Tile constants
@@ -103,12 +113,11 @@ struct TcParams {
     float *Cout;
     uint64_t ldc_out;
     uint32_t *counters;           // one per (tile, CTA of the pair, epilogue warp); zero between launches
-    // Stream-K schedule (when units != nullptr): the host lists the work units; cluster c runs
-    // units[unit_start[c] .. unit_start[c+1]).  A tile whose K range is shared by several clusters
-    // has its partial sums in `ws` (tile-local slices) and is finished by the last arriver.
-    const struct TcUnit *units;
-    const uint32_t *unit_start;
-    float *ws;
+    // Balanced last wave (sk_on): with T tiles on S resident clusters, the first sk_full = T / S waves are whole
+    // tiles; the K ranges of the remaining T % S tiles are dealt out so that every cluster gets the same share
+    // and no tile has more than two K-slices (see tail_unit).  `counters` then holds one hand-over flag per
+    // (tail tile, CTA of the pair, epilogue warp).
+    uint32_t sk_on, sk_full, sk_q, sk_r;
     uint32_t *status;
     unsigned long long *prof;     // debug & 32: 16 cycle counters per CTA
 };
@@ -116,23 +125,11 @@ struct TcParams {
 struct WorkUnit {
     uint32_t m_blk, n_blk, batch, split;
     uint32_t kb_begin, kb_count;
-    uint32_t nslices, ws_slice0, ws_tile;   // stream-K: slices of this tile, its first slice and index in ws
+    uint32_t role;        // 0: the tile's whole K range (or a K-split slice with its own output)
+                          // 1: first K-slice of a shared tail tile: written to C, then the hand-over flag is raised
+                          // 2: second K-slice of a shared tail tile: added to C once the flag is up
+    uint32_t flag_tile;   // roles 1, 2: index of the tail tile (selects the flags)
 };
-
-// One entry of the host-made work list (32 bytes).
-struct TcUnit {
-    uint32_t m_blk, n_blk, batch, kb_begin;
-    uint32_t kb_count, slice, nslices, ws_slice0;
-};
-
-__device__ __forceinline__ WorkUnit load_unit(const TcUnit *u) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(u));
-    const uint4 b = __ldg(reinterpret_cast<const uint4 *>(u) + 1);
-    WorkUnit w;
-    w.m_blk = a.x; w.n_blk = a.y; w.batch = a.z; w.kb_begin = a.w;
-    w.kb_count = b.x; w.split = b.y; w.nslices = b.z & 0xFFFFu; w.ws_tile = b.z >> 16; w.ws_slice0 = b.w;
-    return w;
-}
 
 __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
     WorkUnit w;
@@ -152,8 +149,93 @@ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
     uint32_t kb_end = w.kb_begin + p.kb_per_split;
     if (kb_end > p.k_blocks) kb_end = p.k_blocks;
     w.kb_count = kb_end - w.kb_begin;
-    w.nslices = 1; w.ws_slice0 = 0; w.ws_tile = 0;
+    w.role = 0; w.flag_tile = 0;
     return w;
+}
+
+// Balanced last wave.  R = T % S tail tiles (R < S) are handled by S clusters in G = S - R groups; a group of k
+// tiles has k + 1 clusters (R = q G + r: the first r groups have k = q + 1 tiles, the others k = q).  Inside a group,
+// tile t is shared by clusters t and t + 1 only:
+//     cluster t + 1 computes K blocks [0, s_t)  first  (role 1: stores the partial tile, raises the flag),
+//     cluster t     computes K blocks [s_t, KB) second (role 2: waits for the flag, adds its partial tile),
+// with s_t = KB (t + 1) / (k + 1), so that every cluster multiplies KB k / (k + 1) blocks.  A cluster does its
+// role-1 part before its role-2 part, so the part a role-2 unit waits for was started a whole role-1 part earlier
+// than the role-2 unit itself: the wait is over before it begins, except for one pair per group whose two parts end
+// together.  Each element of a shared tile is (slice 0) + (slice 1): two terms, one order, deterministic.
+// j = 0, 1 enumerates the parts of cluster c; false when there is none.
+__host__ __device__ inline bool tail_part(uint32_t q, uint32_t r, uint32_t KB, uint32_t c, uint32_t j, uint32_t &tile,
+                                          uint32_t &kb_begin, uint32_t &kb_count, uint32_t &role) {
+    const uint32_t big = r * (q + 2);
+    uint32_t pos, k, tile0;
+    if (c < big) {
+        const uint32_t g = c / (q + 2);
+        pos = c - g * (q + 2); k = q + 1; tile0 = g * (q + 1);
+    } else {
+        const uint32_t c2 = c - big, g = c2 / (q + 1);
+        pos = c2 - g * (q + 1); k = q; tile0 = r * (q + 1) + g * q;
+    }
+    if (k == 0) return false;
+    const bool has0 = pos >= 1, has1 = pos + 1 <= k;
+    uint32_t which;
+    if (j == 0) which = has0 ? 0u : 1u;
+    else if (j == 1 && has0 && has1) which = 1u;
+    else return false;
+    const uint32_t t = which == 0 ? pos - 1 : pos;
+    uint32_t split = (uint32_t)(((uint64_t)KB * (t + 1) + (k + 1) / 2) / (k + 1));
+    split = split < 1 ? 1 : (split > KB - 1 ? KB - 1 : split);
+    tile = tile0 + t;
+    if (which == 0) { kb_begin = 0; kb_count = split; role = 1; }
+    else { kb_begin = split; kb_count = KB - split; role = 2; }
+    return true;
+}
+__device__ __noinline__ bool tail_unit(const TcParams &p, uint32_t c, uint32_t S, uint32_t j, WorkUnit &w) {
+    uint32_t tile, kb_begin, kb_count, role;
+    if (!tail_part(p.sk_q, p.sk_r, p.k_blocks, c, j, tile, kb_begin, kb_count, role)) return false;
+    w = decode_unit(p, p.sk_full * S + tile);
+    w.kb_begin = kb_begin; w.kb_count = kb_count; w.role = role; w.flag_tile = tile;
+    return true;
+}
+
+// The i-th work unit of a cluster (i = 0, 1, ...); false past the last one.  Every role of the CTA (pair) walks the
+// same sequence.
+__device__ __forceinline__ bool get_unit(const TcParams &p, uint32_t cluster_id, uint32_t num_clusters, uint32_t total_units,
+                                         uint32_t i, WorkUnit &w) {
+    if (!p.sk_on) {
+        const uint64_t u = (uint64_t)cluster_id + (uint64_t)i * num_clusters;
+        if (u >= total_units) return false;
+        w = decode_unit(p, (uint32_t)u);
+        return true;
+    }
+    if (i < p.sk_full) {
+        w = decode_unit(p, cluster_id + i * num_clusters);
+        return true;
+    }
+    return tail_unit(p, cluster_id, num_clusters, i - p.sk_full, w);
+}
+
+// Hand-over flag of a shared tail tile (global memory, gpu scope).
+__device__ __forceinline__ void flag_raise(uint32_t *flag) {
+    asm volatile("fence.proxy.async;" ::: "memory");      // the partial tile was written by bulk copies
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
+}
+// Whole warp; false when the wait ran out of time (2 s) or the CTA is aborting.
+__device__ __noinline__ bool flag_wait(uint32_t *flag, volatile uint32_t *abort_flag, uint32_t *status) {
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (__all_sync(0xffffffffu, v != 0)) break;
+        __nanosleep(128);
+        uint32_t give_up = *abort_flag;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) give_up = 1;
+        if (__any_sync(0xffffffffu, give_up)) {
+            if ((threadIdx.x & 31) == 0) { *abort_flag = 1; atomicOr(status, DEV_ERR_WAIT_TILE_FLAG); }
+            return false;
+        }
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");      // the add that follows is a bulk copy
+    return true;
 }
 
 // 0.5 x (1 + erf(x / sqrt 2)), picograd's act_apply (backend/cpu/gemm.c:632-636), with
@@ -244,48 +326,6 @@ __device__ __noinline__ void sum_slices_chunk(const TcParams &p, uint32_t row0, 
     }
 }
 
-// Stream-K: the same for a tile whose partial sums lie in tile-local slices of `ws`
-// ([slice][tile rows][bn] f32): the warp sums its 32 rows x `w` columns over the slices, in slice
-// order, into the final C.  16-byte loads, eight (w = 32) in flight per lane and slice: lane l owns
-// columns 4*(l % (w/4)) .. +3 of rows l / (w/4) + (32*4/w) * i.
-__device__ __noinline__ void sum_ws_chunk(const TcParams &p, const float *ws_tile, uint32_t nslices, uint32_t tile_elems,
-                                          uint32_t bn, uint32_t lrow0, uint32_t lcol, uint32_t w, float *c_tile_origin,
-                                          uint32_t rows_left, uint32_t cols_left, uint32_t lane) {
-    const uint32_t lanes_per_row = w / 4;                 // 8 or 4
-    const uint32_t rows_per_pass = 32 / lanes_per_row;    // 4 or 8
-    const uint32_t passes = 32 / rows_per_pass;           // 8 or 4
-    const uint32_t r_in = lane / lanes_per_row, c4 = (lane % lanes_per_row) * 4;
-    const float *base = ws_tile + (uint64_t)(lrow0 + r_in) * bn + lcol + c4;
-    float4 sum[8];
-#pragma unroll
-    for (uint32_t i = 0; i < 8; ++i)
-        if (i < passes) sum[i] = __ldcg(reinterpret_cast<const float4 *>(base + (uint64_t)(i * rows_per_pass) * bn));
-    for (uint32_t sidx = 1; sidx < nslices; ++sidx) {
-        const float *sl = base + (uint64_t)sidx * tile_elems;
-        float4 v[8];
-#pragma unroll
-        for (uint32_t i = 0; i < 8; ++i)
-            if (i < passes) v[i] = __ldcg(reinterpret_cast<const float4 *>(sl + (uint64_t)(i * rows_per_pass) * bn));
-#pragma unroll
-        for (uint32_t i = 0; i < 8; ++i)
-            if (i < passes) { sum[i].x += v[i].x; sum[i].y += v[i].y; sum[i].z += v[i].z; sum[i].w += v[i].w; }
-    }
-    const bool vec_ok = p.c_vec4 != 0;
-#pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) {
-        if (i >= passes) break;
-        const uint32_t r = r_in + i * rows_per_pass;
-        if (r >= rows_left || c4 >= cols_left) continue;
-        float *d = c_tile_origin + (uint64_t)r * p.ldc + c4;
-        if (vec_ok && c4 + 4 <= cols_left && !p.accumulate) {
-            *reinterpret_cast<float4 *>(d) = sum[i];
-        } else {
-            const float s4[4] = {sum[i].x, sum[i].y, sum[i].z, sum[i].w};
-            for (uint32_t j = 0; j < 4 && c4 + j < cols_left; ++j) d[j] = p.accumulate ? d[j] + s4[j] : s4[j];
-        }
-    }
-}
-
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
@@ -302,7 +342,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     // timing experiments: wall-clock nanoseconds at which this CTA started / set up / ended (counters 14, 15, 7)
-    if ((p.debug & 32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 14] = globaltimer_ns();
+    if (PG_DBG(32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 14] = globaltimer_ns();
 
     const uint32_t stage_base = smem_base;
     const uint32_t epi_base = smem_base + STAGES * C_::STAGE_BYTES;
@@ -324,12 +364,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t cluster_id = blockIdx.x / CG;
     const uint32_t num_clusters = gridDim.x / CG;
     const uint32_t total_units = p.batch * p.m_tiles * p.n_tiles * p.splits;
-    // work units of this cluster: a strided walk over the implicit list, or a range of the host-made one
-    const bool listed = p.units != nullptr;
-    const uint32_t u_begin = listed ? __ldg(p.unit_start + cluster_id) : cluster_id;
-    const uint32_t u_end = listed ? __ldg(p.unit_start + cluster_id + 1) : total_units;
-    const uint32_t u_step = listed ? 1u : num_clusters;
-
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         prefetch_tmap(&map_a);
@@ -355,7 +389,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (CG == 2 || p.cluster_k > 1) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
-    if ((p.debug & 32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 7] = globaltimer_ns();
+    // Programmatic dependent launch: everything above touched no global memory, so it may run while the previous
+    // kernel of the stream is still finishing; from here on its results (and its hand-over flags) are needed.  The
+    // next kernel of the stream may be scheduled as soon as SMs become free (its own prologue then waits here).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (PG_DBG(32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 7] = globaltimer_ns();
 
     // Each role loop below is executed by its whole warp with warp-uniform state; the instructions
     // that must come from one thread (TMA, tcgen05.mma, tcgen05.commit, barrier arrives) sit under
@@ -364,11 +403,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------ TMA producer ------------------------------
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        const bool prof = (p.debug & 32u) != 0;
+        const bool prof = PG_DBG(32u);
         long long tp_wait = 0, tp_issue = 0;
         const uint64_t pol_a = l2_policy((int)(p.l2_hints & 3u)), pol_b = l2_policy((int)((p.l2_hints >> 2) & 3u));
-        for (uint32_t u = u_begin; u < u_end && ok; u += u_step) {
-            const WorkUnit w = listed ? load_unit(p.units + u) : decode_unit(p, u);
+        for (uint32_t ui = 0; ok; ++ui) {
+            WorkUnit w;
+            if (!get_unit(p, cluster_id, num_clusters, total_units, ui, w)) break;
             const int32_t m0 = (int32_t)(w.m_blk * BM_CTA * CG + cta_rank * BM_CTA);
             const int32_t n0 = (int32_t)(w.n_blk * BN + cta_rank * C_::BN_CTA);
             const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
@@ -386,7 +426,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t sbase = stage_base + stage * C_::STAGE_BYTES;
                     const int32_t kbase = (int32_t)((w.kb_begin + r * SUB) * BK);
                     if (elect_one()) {
-                        if (p.debug & 1u) {
+                        if PG_DBG(1u) {
                             if (cta_rank == 0) mbar_arrive(full_bar(stage));
                         } else {
                             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C_::STAGE_BYTES * CG);
@@ -445,7 +485,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t idesc = p.idesc;
             bool ok = true;
             bool ready = false;             // full_bar(stage) has already been seen complete
-            const bool prof = (p.debug & 32u) != 0;
+            const bool prof = PG_DBG(32u);
             long long t_wait = 0, t_issue = 0, t_commit = 0, t_tmem = 0, t_all = prof ? clock64() : 0, n_rounds = 0;
 
             auto issue = [&](uint32_t m, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t nsub, uint32_t accum) {
@@ -457,8 +497,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                               b_hi, idesc, accum);
             };
 
-            for (uint32_t u = u_begin; u < u_end && ok; u += u_step) {
-                const WorkUnit w = listed ? load_unit(p.units + u) : decode_unit(p, u);
+            WorkUnit w, w_next;
+            bool have = get_unit(p, cluster_id, num_clusters, total_units, 0, w);
+            for (uint32_t ui = 0; have && ok; ++ui, w = w_next) {
+                const bool more_units = get_unit(p, cluster_id, num_clusters, total_units, ui + 1, w_next);
+                have = more_units;
                 long long c0 = prof ? clock64() : 0;
                 ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
                 if (!ok) break;
@@ -467,7 +510,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
                 const uint32_t iters = p.npass * rounds;
-                const bool more_units = u + u_step < u_end;
                 uint32_t r = 0;
                 for (uint32_t it = 0; it < iters; ++it) {
                     long long c1 = prof ? clock64() : 0;
@@ -480,7 +522,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t a_lo = a_lo0 + soff, b_lo = b_lo0 + soff;
                     uint32_t nsub = SUB;
                     if (SUB > 1 && w.kb_count - r * SUB < (uint32_t)SUB) nsub = w.kb_count - r * SUB;  // rest belongs to the next split
-                    const bool do_mma = !(p.debug & 16u);
+                    const bool do_mma = !PG_DBG(16u);
                     if (elect_one()) {
                         if (do_mma) {
 #pragma unroll
@@ -540,11 +582,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         const bool cluster_mode = CG == 1 && BN <= 32 && STAGING && p.cluster_k > 1;
         const bool fused = p.splits > 1 && p.Cout != nullptr && !cluster_mode;
-        const uint64_t pol_c = l2_policy((int)((p.l2_hints >> 4) & 3u));
-        const bool prof = (p.debug & 32u) != 0 && ew == 0;
+        const uint64_t pol_c = l2_policy((int)((p.l2_hints >> 4) & 3u)), pol_keep = l2_policy(0);
+        const bool prof = PG_DBG(32u) && ew == 0;
         long long te_wait = 0, te_ld = 0, te_math = 0, te_store = 0, last_e3 = 0;
-        for (uint32_t u = u_begin; u < u_end && ok; u += u_step) {
-            const WorkUnit w = listed ? load_unit(p.units + u) : decode_unit(p, u);
+        for (uint32_t ui = 0; ok; ++ui) {
+            WorkUnit w;
+            if (!get_unit(p, cluster_id, num_clusters, total_units, ui, w)) break;
             // Bias of a chunk: lane l holds bias[col + l], fetched one chunk ahead (the first one before the
             // wait for the accumulator) and handed round by shuffles, so no chunk waits for a load.
             auto bias_fetch = [&](uint32_t c) -> float {
@@ -564,11 +607,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t row = row0 + lane;
             float *cbase = p.C + (uint64_t)zc * p.c_stride;
             const bool accum = p.accumulate && !fused;      // K-slices are plain stores; only the final sum accumulates
-            // stream-K: this unit covers only part of the tile's K range -> tile-local slice in ws
-            const bool partial = w.nslices > 1;
-            constexpr uint32_t TILE_ELEMS = BM_CTA * CG * BN;
-            const uint32_t lrow0 = cta_rank * BM_CTA + q * 32;              // tile-local first row of this warp
-            float *ws_slice = partial ? p.ws + (uint64_t)(w.ws_slice0 + w.split) * TILE_ELEMS : nullptr;
+            // shared tail tile: hand-over flag of this warp's slab; the second slice is added to the first
+            uint32_t *tile_flag = w.role ? p.counters + ((w.flag_tile * CG + cta_rank) * EPI_WARPS + ew) : nullptr;
+            bool flag_pending = w.role == 2;
             if constexpr (CG == 1 && BN <= 32 && STAGING) {
                 if (cluster_mode) {
                     // Split-K inside a cluster: CTA r of the cluster holds K-slice r of this tile (one chunk of
@@ -598,7 +639,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 break;
                             }
                         }
-                        if (landed && !(p.debug & 2u)) {
+                        if (landed && !PG_DBG(2u)) {
                             for (uint32_t r = 1; r < p.cluster_k; ++r) {
                                 const uint4 *src = reinterpret_cast<const uint4 *>(smem_gen + (epi_base - smem_base) + ((r - 1) * 4 + q) * SLOT + lane * (W * 4));
 #pragma unroll
@@ -629,7 +670,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (uint32_t c = half; c < CHUNKS && !cluster_mode; c += CSTEP) {
                 const uint32_t col = col0 + c * W;
                 if (col >= p.N || row0 >= p.M) break;   // nothing of this warp's slab is inside C
-                if (p.debug & 4u) break;
+                if PG_DBG(4u) break;
                 uint32_t v[32];
                 const float bias_cur = bias_next;
                 bias_next = bias_fetch(c + CSTEP);
@@ -638,7 +679,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if constexpr (W == 32) tmem_ld32(taddr + c * W, v); else tmem_ld16(taddr + c * W, v);
                 tmem_ld_wait();
                 long long e2 = prof ? clock64() : 0;
-                if (p.debug & 2u) continue;
+                if PG_DBG(2u) continue;
                 if (p.bias || p.act || p.c16) {
                     // bias and activation on the f32 accumulators, in registers (no split/partial route reaches here)
                     if (p.bias) {
@@ -718,13 +759,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 long long e3 = prof ? clock64() : 0;
                 if (prof) { te_ld += e2 - e1; te_math += e3 - e2; last_e3 = e3; }
-                if (partial) {
-                    // always in bounds: the slice holds the whole tile
-                    float *d = ws_slice + (uint64_t)(lrow0 + lane) * BN + c * W;
-#pragma unroll
-                    for (uint32_t j = 0; j < W / 4; ++j)
-                        *reinterpret_cast<uint4 *>(d + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else if (STAGING && p.epilogue_tma) {
+                if (STAGING && p.epilogue_tma) {
                     // the store issued EPI_BUFS chunks ago must have finished reading this buffer
                     if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
                     __syncwarp();
@@ -736,11 +771,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
+                    if (flag_pending) {
+                        // the first K-slice of this slab must be in C before anything is added to it
+                        ok = flag_wait(tile_flag, abort_flag, p.status);
+                        flag_pending = false;
+                        if (!ok) break;
+                    }
                     if (lane == 0) {
-                        if (accum)
+                        if (accum || w.role == 2)
                             tma_reduce_add_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc);
-                        else
-                            tma_store_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc, pol_c);
+                        else   // a slab that a second slice will be added to should not leave L2 first
+                            tma_store_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc,
+                                         w.role == 1 ? pol_keep : pol_c);
                         tma_store_commit();
                     }
                     if (++buf == EPI_BUFS) buf = 0;
@@ -790,29 +832,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
 
-            if (partial && row0 < p.M && !(p.debug & 6u)) {
-                // Stream-K hand-over, same protocol as the fused split-K reduction below.
-                const uint32_t slab = ((w.ws_tile * CG + cta_rank) * EPI_WARPS) + ew;
-                __threadfence();
-                __syncwarp();
-                uint32_t old = 0;
-                if (lane == 0) old = atomicAdd(p.counters + slab, 1u);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == w.nslices - 1) {
-                    __threadfence();
-                    const float *ws_tile = p.ws + (uint64_t)w.ws_slice0 * TILE_ELEMS;
-                    for (uint32_t c = half; c < CHUNKS; c += CSTEP) {
-                        const uint32_t col = col0 + c * W;
-                        if (col >= p.N) break;
-                        sum_ws_chunk(p, ws_tile, w.nslices, TILE_ELEMS, BN, lrow0, c * W, W,
-                                     p.C + (uint64_t)w.batch * p.c_stride + (uint64_t)row0 * p.ldc + col, p.M - row0,
-                                     p.N - col, lane);
-                    }
-                    __syncwarp();
-                    if (lane == 0) p.counters[slab] = 0;
+            if (w.role == 1) {
+                // first slice: once this warp's stores have completed, raise the flag of its slab
+                if (lane == 0) {
+                    tma_store_wait_all();
+                    flag_raise(tile_flag);
                 }
+                __syncwarp();
+            } else if (w.role == 2 && ok) {
+                // second slice: consume the flag (also when no chunk of this slab lay inside C) and re-arm it
+                if (flag_pending) ok = flag_wait(tile_flag, abort_flag, p.status);
+                if (lane == 0) *tile_flag = 0;
             }
-            if (fused && row0 < p.M && !(p.debug & 6u)) {
+            if (fused && row0 < p.M && !PG_DBG(6u)) {
                 // Fused split-K reduction.  This warp's slab of slice `split` is in global memory
                 // (plain stores); publish it and count.  The warp that finds all other slices already
                 // counted sums the slab over the slices in slice order — the result does not depend on
@@ -845,12 +877,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     // ------------------------------ teardown ------------------------------
     tc_fence_before();
-    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    // (K-slices as a cluster: no CTA may leave while a peer can still write into its shared memory)
+    if (CG == 2 || p.cluster_k > 1) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc<CG>(tmem_base, C_::TMEM_COLS);
     }
-    if ((p.debug & 32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 15] = globaltimer_ns();
+    if (PG_DBG(32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 15] = globaltimer_ns();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -905,10 +938,6 @@ static const TcConfig g_cfgs[] = {
     PG_TC_CFG("1cta_128x64", 1, 64, 1, true, 4, 2, true),
     PG_TC_CFG("2cta_256x256", 2, 256, 1, true, 4, 2, true),
     PG_TC_CFG("2cta_256x128", 2, 128, 1, true, 4, 2, true),
-    PG_TC_CFG("2cta_256x256_k128", 2, 256, 2, true, 4, 2, false),
-    PG_TC_CFG("1cta_128x256_k128", 1, 256, 2, true, 4, 2, false),
-    PG_TC_CFG("2cta_256x256_s7", 2, 256, 1, false, 4, 2, false),
-    PG_TC_CFG("2cta_256x256_e8", 2, 256, 1, true, 8, 2, false),   // store-bound shapes (small K): 8 epilogue warps
     PG_TC_CFG("1cta_128x16_t", 1, 16, 1, true, 4, 2, false),      // swapped operands for M <= 16 (staging area = cluster reduction)
     PG_TC_CFG("1cta_128x32_t", 1, 32, 1, true, 4, 2, false),      // swapped operands for M <= 32
 };
@@ -1038,6 +1067,32 @@ static const CfgRuntime &prepare_cfg(int cfg) {
 
 static uint32_t cdiv(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 
+// ---------------------------------------------------------------------------------------------
+// Balanced last wave (see tail_unit).  With T tiles on S resident clusters and R = T % S != 0, the plain
+// schedule runs R clusters for a whole tile while S - R wait; here every cluster gets k / (k + 1) of a tile,
+// k = ceil(R / (S - R)) tiles per group.  Worth it when that is clearly less than the plain last wave
+// (a partly filled wave already runs faster than a full one: more clock and more L2 per CTA, measured as
+// 0.5 + 0.5 * occupancy of a full wave's time).
+// ---------------------------------------------------------------------------------------------
+static bool balanced_tail(uint64_t tiles, uint32_t slots, uint32_t k_blocks, uint32_t &full, uint32_t &q, uint32_t &r,
+                          double *last_wave = nullptr) {
+    full = (uint32_t)(tiles / slots);
+    const uint32_t rem = (uint32_t)(tiles % slots);
+    if (last_wave) *last_wave = rem ? 0.5 + 0.5 * (double)rem / slots : 0.0;
+    if (rem == 0 || k_blocks < 16) return false;
+    const uint32_t groups = slots - rem;
+    q = rem / groups; r = rem % groups;
+    const uint32_t kmax = q + (r ? 1 : 0);
+    if (kmax + 1 > k_blocks / 4) return false;             // slices shorter than 4 K blocks are not worth a hand-over
+    const double share = kmax ? (double)kmax / (kmax + 1) : 0.0;
+    const double plain = 0.5 + 0.5 * (double)rem / slots;
+    // hand-over and a second epilogue cost about 3 % of a tile; products of many waves gain too little to give up
+    // "every element is one accumulation over K in order" (which makes all tile configurations agree bit for bit)
+    if ((plain - (share + 0.03)) / ((double)full + plain) < 0.02) return false;
+    if (last_wave) *last_wave = share + 0.03;
+    return true;
+}
+
 // Pick a tile configuration.  Cost model fitted to measurements on B200 (bf16, K = 8192):
 // relative throughput per configuration at full occupancy, and a last partial wave that costs
 // 0.5 + 0.5 * occupancy of a full one (fewer CTAs run faster: more clock and more L2 each).
@@ -1052,8 +1107,16 @@ static int choose_cfg(const TcGemm &g) {
         if (!rt.usable) continue;
         const uint64_t tiles = (uint64_t)g.batch * cdiv(g.M, BM_CTA * c.cg) * cdiv(g.N, c.bn) * (g.splits ? g.splits : 1);
         const uint64_t slots = (uint64_t)rt.max_clusters;
-        const uint64_t full = tiles / slots, tail = tiles % slots;
-        const double waves = (double)full + (tail ? 0.5 + 0.5 * (double)tail / (double)slots : 0.0);
+        uint32_t full = 0, q = 0, r = 0;
+        double last = 0.0;
+        const bool may_balance = g.allow_stream_k && !g.bias && !g.act && !g.c16 && (g.splits ? g.splits : 1) == 1 &&
+                                 g.npass == 1 && !g.c_trans && g.counters;
+        if (!may_balance || !balanced_tail(tiles, (uint32_t)slots, cdiv(g.K, BK), full, q, r, &last)) {
+            full = (uint32_t)(tiles / slots);
+            const uint64_t tail = tiles % slots;
+            last = tail ? 0.5 + 0.5 * (double)tail / (double)slots : 0.0;
+        }
+        const double waves = (double)full + last;
         double eff;
         if (c.cg == 2) eff = c.bn >= 256 ? 1.0 : 0.75;
         else eff = c.bn >= 256 ? 0.885 : (c.bn == 128 ? 0.71 : 0.45);
@@ -1064,169 +1127,17 @@ static int choose_cfg(const TcGemm &g) {
     return best;
 }
 
-// ---------------------------------------------------------------------------------------------
-// Stream-K schedule.  With T tiles on S resident clusters and T % S != 0 the last wave is partly
-// empty.  The first floor(T / S) waves stay whole tiles; the K blocks of the remaining T % S tiles are
-// dealt out evenly, as contiguous runs, to all S clusters.  A tile shared by several clusters gets one
-// slice of `ws` per sharer; the kernel's last arriver sums them in slice order.
-// The list depends only on the shape and the configuration, so it is built once and cached.
-// ---------------------------------------------------------------------------------------------
-struct SkPlan {
-    uint64_t key[6] = {};
-    bool valid = false;
-    TcUnit *d_units = nullptr;
-    uint32_t *d_start = nullptr;
-    uint32_t ws_slices = 0, ws_tiles = 0;
-    uint64_t age = 0;
-};
-static SkPlan g_sk[8];
-static uint64_t g_sk_clock = 0;
-static float *g_sk_ws = nullptr;
-static size_t g_sk_ws_bytes = 0;
-
-static void host_decode_tile(const TcParams &p, uint32_t t, uint32_t &batch, uint32_t &m_blk, uint32_t &n_blk) {
-    const uint32_t per_batch = p.m_tiles * p.n_tiles;
-    batch = t / per_batch;
-    const uint32_t r = t - batch * per_batch;
-    const uint32_t gsz = p.group_m * p.n_tiles;
-    const uint32_t grp = r / gsz;
-    const uint32_t first_m = grp * p.group_m;
-    const uint32_t gm = p.m_tiles - first_m < p.group_m ? p.m_tiles - first_m : p.group_m;
-    const uint32_t in_g = r - grp * gsz;
-    m_blk = first_m + in_g % gm;
-    n_blk = in_g / gm;
-}
-
-// Returns the plan to use, or nullptr when a plain schedule is as good (or scratch cannot be had).
-static const SkPlan *stream_k_plan(const TcParams &p, const TcConfig &c, int cfg, uint32_t slots, cudaStream_t stream) {
-    const uint32_t tiles = p.batch * p.m_tiles * p.n_tiles;
-    const uint32_t rem = tiles % slots, full = tiles / slots;
-    const uint32_t kb = p.k_blocks;
-    if (rem == 0 || kb < 8) return nullptr;
-    // estimated cost in tile-times: plain = full + 0.5 + 0.5 * occupancy of the last wave
-    const double plain = full + 0.5 + 0.5 * (double)rem / slots;
-    const double sk = (double)tiles / slots + 0.06;
-    if (sk > plain * 0.985) return nullptr;
-    if ((uint64_t)rem * kb / slots < 4) return nullptr;          // runs shorter than 4 K blocks are not worth it
-
-    const uint64_t key[6] = {((uint64_t)p.M << 32) | p.N, ((uint64_t)p.K << 32) | p.batch, (uint64_t)cfg, p.group_m, slots, 0};
-    SkPlan *hit = nullptr, *victim = nullptr;
-    for (SkPlan &e : g_sk) {
-        if (e.valid && !memcmp(e.key, key, sizeof key)) hit = &e;
-        if (!victim) victim = &e;
-        else if (victim->valid && (!e.valid || e.age < victim->age)) victim = &e;   // a free entry, else the oldest
-    }
-    if (hit) { hit->age = ++g_sk_clock; return hit; }
-
-    // ---- build the list on the host
-    struct HostUnit { TcUnit u; };
-    const uint32_t dp_tiles = tiles - rem;
-    const uint64_t total_kb = (uint64_t)rem * kb;
-    const uint64_t base = total_kb / slots, extra = total_kb % slots;
-    // slices per stream-K tile
-    uint32_t *nsl = (uint32_t *)calloc(rem, sizeof(uint32_t));
-    uint32_t *slice0 = (uint32_t *)calloc(rem + 1, sizeof(uint32_t));
-    if (!nsl || !slice0) { free(nsl); free(slice0); return nullptr; }
-    uint64_t pos = 0;
-    for (uint32_t cl = 0; cl < slots; ++cl) {
-        uint64_t len = base + (cl < extra ? 1 : 0), end = pos + len;
-        for (uint64_t q = pos; q < end;) {
-            const uint32_t t = (uint32_t)(q / kb);
-            const uint64_t tile_end = (uint64_t)(t + 1) * kb;
-            const uint64_t stop = end < tile_end ? end : tile_end;
-            nsl[t]++;
-            q = stop;
-        }
-        pos = end;
-    }
-    uint32_t ws_slices = 0, ws_tiles = 0;
-    uint32_t *ws_tile_idx = (uint32_t *)calloc(rem, sizeof(uint32_t));
-    if (!ws_tile_idx) { free(nsl); free(slice0); return nullptr; }
-    for (uint32_t t = 0; t < rem; ++t) {
-        slice0[t] = ws_slices;
-        if (nsl[t] > 1) { ws_tile_idx[t] = ws_tiles++; ws_slices += nsl[t]; }
-    }
-    if (ws_tiles > 0xFFFFu) { free(nsl); free(slice0); free(ws_tile_idx); return nullptr; }
-    const uint32_t max_units = full * slots + rem + 2 * slots + 8;
-    TcUnit *units = (TcUnit *)malloc((size_t)max_units * sizeof(TcUnit));
-    uint32_t *start = (uint32_t *)malloc((size_t)(slots + 1) * sizeof(uint32_t));
-    uint32_t *seen = (uint32_t *)calloc(rem, sizeof(uint32_t));     // slices handed out so far per tile
-    if (!units || !start || !seen) { free(nsl); free(slice0); free(ws_tile_idx); free(units); free(start); free(seen); return nullptr; }
-    uint32_t n = 0;
-    pos = 0;
-    // NOTE: slice indices must follow ascending K within a tile; clusters are walked in ascending order
-    // of their runs, so `seen` counts in that order.  Build per-cluster SK runs first.
-    struct Run { uint32_t t, kb0, cnt, slice; };
-    Run *runs = (Run *)malloc((size_t)(2 * slots + rem + 8) * sizeof(Run));
-    uint32_t *run_start = (uint32_t *)malloc((size_t)(slots + 1) * sizeof(uint32_t));
-    if (!runs || !run_start) { free(nsl); free(slice0); free(ws_tile_idx); free(units); free(start); free(seen); free(runs); free(run_start); return nullptr; }
-    uint32_t nr = 0;
-    for (uint32_t cl = 0; cl < slots; ++cl) {
-        run_start[cl] = nr;
-        uint64_t len = base + (cl < extra ? 1 : 0), end = pos + len;
-        for (uint64_t q = pos; q < end;) {
-            const uint32_t t = (uint32_t)(q / kb);
-            const uint64_t tile_end = (uint64_t)(t + 1) * kb;
-            const uint64_t stop = end < tile_end ? end : tile_end;
-            runs[nr++] = {t, (uint32_t)(q - (uint64_t)t * kb), (uint32_t)(stop - q), seen[t]++};
-            q = stop;
-        }
-        pos = end;
-    }
-    run_start[slots] = nr;
-    for (uint32_t cl = 0; cl < slots; ++cl) {
-        start[cl] = n;
-        for (uint32_t w = 0; w < full; ++w) {                       // whole tiles, strided like the plain schedule
-            TcUnit u = {};
-            host_decode_tile(p, w * slots + cl, u.batch, u.m_blk, u.n_blk);
-            u.kb_begin = 0; u.kb_count = kb; u.slice = 0; u.nslices = 1; u.ws_slice0 = 0;
-            units[n++] = u;
-        }
-        for (uint32_t r = run_start[cl]; r < run_start[cl + 1]; ++r) {
-            TcUnit u = {};
-            host_decode_tile(p, dp_tiles + runs[r].t, u.batch, u.m_blk, u.n_blk);
-            u.kb_begin = runs[r].kb0; u.kb_count = runs[r].cnt; u.slice = runs[r].slice;
-            u.nslices = nsl[runs[r].t] | (ws_tile_idx[runs[r].t] << 16);
-            u.ws_slice0 = slice0[runs[r].t];
-            units[n++] = u;
-        }
-    }
-    start[slots] = n;
-    free(nsl); free(slice0); free(ws_tile_idx); free(seen); free(runs); free(run_start);
-
-    // ---- device copies
-    SkPlan *e = victim;
-    if (e->valid) {
-        cudaStreamSynchronize(stream);       // a launch in flight may still read the old list
-        cudaFree(e->d_units); cudaFree(e->d_start);
-        e->valid = false; e->d_units = nullptr; e->d_start = nullptr;
-    }
-    const size_t tile_bytes = (size_t)BM_CTA * c.cg * c.bn * sizeof(float);
-    const size_t need_ws = (size_t)ws_slices * tile_bytes;
-    if (need_ws > g_sk_ws_bytes) {
-        cudaStreamSynchronize(stream);
-        if (g_sk_ws) cudaFree(g_sk_ws);
-        g_sk_ws = nullptr; g_sk_ws_bytes = 0;
-        if (cudaMalloc((void **)&g_sk_ws, need_ws) != cudaSuccess) { cudaGetLastError(); free(units); free(start); return nullptr; }
-        g_sk_ws_bytes = need_ws;
-    }
-    bool ok = cudaMalloc((void **)&e->d_units, (size_t)n * sizeof(TcUnit)) == cudaSuccess &&
-              cudaMalloc((void **)&e->d_start, (size_t)(slots + 1) * sizeof(uint32_t)) == cudaSuccess &&
-              cudaMemcpyAsync(e->d_units, units, (size_t)n * sizeof(TcUnit), cudaMemcpyHostToDevice, stream) == cudaSuccess &&
-              cudaMemcpyAsync(e->d_start, start, (size_t)(slots + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, stream) == cudaSuccess;
-    if (ok) ok = cudaStreamSynchronize(stream) == cudaSuccess;      // the host arrays are freed below
-    free(units); free(start);
-    if (!ok) {
-        cudaGetLastError();
-        if (e->d_units) cudaFree(e->d_units);
-        if (e->d_start) cudaFree(e->d_start);
-        e->d_units = nullptr; e->d_start = nullptr;
-        return nullptr;
-    }
-    memcpy(e->key, key, sizeof key);
-    e->ws_slices = ws_slices; e->ws_tiles = ws_tiles;
-    e->valid = true; e->age = ++g_sk_clock;
-    return e;
+// Host view of the balanced last wave, for tests: part j (0, 1) of cluster c when `tiles` tiles of `k_blocks` K
+// blocks run on `slots` clusters.  out = {used, whole-tile waves, tail tile, first K block, K blocks, role}.
+int tc_tail_schedule(uint64_t tiles, uint32_t slots, uint32_t k_blocks, uint32_t c, uint32_t j, uint32_t out[6]) {
+    uint32_t full = 0, q = 0, r = 0;
+    for (int i = 0; i < 6; ++i) out[i] = 0;
+    if (slots == 0 || c >= slots) return ST_UNSUPPORTED;
+    if (!balanced_tail(tiles, slots, k_blocks, full, q, r)) return ST_OK;       // out[0] == 0: plain schedule
+    out[0] = 1; out[1] = full;
+    uint32_t tile, b, n, role;
+    if (tail_part(q, r, k_blocks, c, j, tile, b, n, role)) { out[2] = tile; out[3] = b; out[4] = n; out[5] = role; }
+    return ST_OK;
 }
 
 int tc_gemm_launch(const TcGemm &g) {
@@ -1344,11 +1255,15 @@ int tc_gemm_launch(const TcGemm &g) {
     if (units > 0xFFFFFFFFull) return ST_UNSUPPORTED;
     uint32_t clusters = (uint32_t)(units < (uint64_t)rt.max_clusters ? units : (uint64_t)rt.max_clusters);
     bool stream_k = false;
-    if (g.allow_stream_k && !g.bias && !g.act && !g.c16 && p.splits == 1 && p.npass == 1 && !p.c_trans && g.counters && c.bn >= 32 && !(p.debug & 31u)) {
-        const SkPlan *plan = stream_k_plan(p, c, cfg, (uint32_t)rt.max_clusters, g.stream);
-        if (plan && (uint64_t)plan->ws_tiles * c.cg * c.ew <= g.num_counters) {
-            p.units = plan->d_units; p.unit_start = plan->d_start; p.ws = g_sk_ws; p.counters = g.counters;
-            clusters = (uint32_t)rt.max_clusters;
+    if (g.allow_stream_k && !g.bias && !g.act && !g.c16 && p.splits == 1 && p.npass == 1 && !p.c_trans && p.epilogue_tma &&
+        g.counters && !(kExperiments && (p.debug & 31u))) {
+        uint32_t full = 0, q = 0, r = 0;
+        const uint32_t slots = (uint32_t)rt.max_clusters;
+        if (balanced_tail(units, slots, p.k_blocks, full, q, r) &&
+            (units % slots) * c.cg * c.ew <= (uint64_t)g.num_counters) {
+            p.sk_on = 1; p.sk_full = full; p.sk_q = q; p.sk_r = r;
+            p.counters = g.counters;
+            clusters = slots;
             stream_k = true;
         }
     }
@@ -1359,13 +1274,20 @@ int tc_gemm_launch(const TcGemm &g) {
     lc.blockDim = dim3(c.threads, 1, 1);
     lc.dynamicSmemBytes = c.smem;
     lc.stream = g.stream;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = p.cluster_k ? p.cluster_k : (unsigned)c.cg;
     at[0].val.clusterDim.y = 1;
     at[0].val.clusterDim.z = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
+    if (g.pdl) {
+        // the kernel's prologue (barriers, tensor memory, descriptor prefetch) may overlap the tail of the kernel
+        // before it in the stream; it waits (griddepcontrol.wait) before its first global access
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
+        lc.numAttrs = 2;
+    }
     void *args[4] = {(void *)&ma, (void *)&mb, (void *)&mc, (void *)&p};
     cudaError_t e = cudaLaunchKernelExC(&lc, c.fn, args);
     if (e != cudaSuccess) {
@@ -1375,7 +1297,7 @@ int tc_gemm_launch(const TcGemm &g) {
     }
     note_launch();
     set_last_path("tc:%s%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
-                  p.cluster_k ? ":cluster" : (p.Cout ? ":fused" : ""), stream_k ? ":streamk" : "");
+                  p.cluster_k ? ":cluster" : (p.Cout ? ":fused" : ""), stream_k ? ":balanced_tail" : "");
     return ST_OK;
 }
 

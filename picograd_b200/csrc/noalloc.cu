@@ -127,6 +127,7 @@ extern "C" int pg_b200_gemm_ex_static_scratch(int dtype, size_t m, size_t n, siz
     t.accumulate = 0;
     t.splits = splits;
     t.force_cfg = -1; t.force_epilogue = -1;
+    t.pdl = 0;
     t.stream = current_stream();
     t.dev_status = ss->status;
     t.prof = nullptr;

@@ -22,6 +22,7 @@ enum : uint32_t {
     DEV_ERR_WAIT_FULL = 1u << 1,       // MMA issuer: TMA bytes never landed
     DEV_ERR_WAIT_TMEM_EMPTY = 1u << 2, // MMA issuer: epilogue never drained TMEM
     DEV_ERR_WAIT_TMEM_FULL = 1u << 3,  // epilogue: accumulator never completed
+    DEV_ERR_WAIT_TILE_FLAG = 1u << 4,  // epilogue: the first K-slice of a shared tile never arrived
     DEV_ERR_SELFTEST = 1u << 8,        // the wait-timeout self-test kernel ran out of time, as it must
 };
 
@@ -57,7 +58,8 @@ struct TcGemm {
     uint32_t *counters;        // zeroed device words, one per (tile, CTA, epilogue warp)
     uint32_t num_counters;
     int cluster_splitk;        // may run the K-slices of a narrow tile as one cluster, summed through distributed shared memory
-    int allow_stream_k;        // may deal the K blocks of a partly filled last wave out to all clusters
+    int allow_stream_k;        // may deal the K ranges of a partly filled last wave out to all clusters (two slices per tile)
+    int pdl;                   // launch with programmatic stream serialisation: the prologue overlaps the previous kernel's tail
     uint32_t splits;           // >1: split-K, slice s goes to C + s*c_stride (batch must be 1)
     int force_cfg;             // -1 = choose; else index into the config table
     int force_epilogue;        // -1 = choose; 0 = direct stores; 1 = TMA stores
@@ -77,6 +79,7 @@ int tc_gemm_launch(const TcGemm &g);
 bool tc_gemm_supported(const TcGemm &g);
 int wait_timeout_selftest_launch(uint32_t *status, unsigned limit_ms, cudaStream_t stream);
 extern int g_l2_promotion;   // CUtensorMapL2promotion of the operand tensor maps
+int tc_tail_schedule(uint64_t tiles, uint32_t slots, uint32_t k_blocks, uint32_t c, uint32_t j, uint32_t out[6]);
 int tc_num_configs();
 const char *tc_config_name(int cfg);
 int tc_config_index(const char *name);   // -1 if unknown
@@ -140,6 +143,8 @@ int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t n
 int addmm_finish_launch(float *c, uint64_t ldc, const float *input, uint64_t in_rs, uint64_t in_cs, float alpha, float beta,
                         uint64_t rows, uint64_t n, cudaStream_t s);
 int fill_f32_launch(float *dst, float v, uint64_t n, cudaStream_t s);
+int gather_relayout_launch(const float *staging, float *dst, uint32_t shards, uint64_t rows, uint64_t width, uint64_t n,
+                           uint64_t ld, cudaStream_t s);
 
 void set_error(const char *fmt, ...);
 void set_last_path(const char *fmt, ...);

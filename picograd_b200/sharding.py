@@ -43,21 +43,90 @@ def batch_shards(batch, world):
     return out
 
 
-def gather_columns(c_local, n_total, group=None, align=8):
+def gather_columns(c_local, n_total, group=None, align=8, out=None, staging=None):
     """All ranks receive the full row-major [M, n_total] matrix from the column shards.
-    Shards are padded to the widest one so that a single all_gather moves them."""
+
+    On the GPU: one NCCL all-gather of the shards into a [world][M][width] staging buffer (a shard narrower than
+    the widest one is padded first), then the library's re-layout kernel (pg_b200_gather_relayout) writes the
+    row-major matrix.  `out` and `staging` may be passed in to keep allocations out of a timed loop.
+    On the CPU (gloo, used by the tests of the host logic) the re-layout is a loop of slice copies."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     shards = column_shards(n_total, world, align)
     m = c_local.shape[0]
     width = max(c for _, c in shards)
     assert c_local.shape[1] == shards[rank][1], "local shard has the wrong width"
-    send = torch.zeros((m, width), dtype=c_local.dtype, device=c_local.device)
-    send[:, :c_local.shape[1]] = c_local
-    recv = torch.empty((world, m, width), dtype=c_local.dtype, device=c_local.device)
+    if c_local.shape[1] == width and c_local.is_contiguous():
+        send = c_local
+    else:
+        send = torch.zeros((m, width), dtype=c_local.dtype, device=c_local.device)
+        send[:, :c_local.shape[1]] = c_local
+    recv = staging if staging is not None else torch.empty((world, m, width), dtype=c_local.dtype, device=c_local.device)
+    full = out if out is not None else torch.empty((m, n_total), dtype=c_local.dtype, device=c_local.device)
+    if c_local.is_cuda:
+        if c_local.dtype != torch.float32:
+            raise TypeError("gather_columns on the GPU takes the float32 output of pg_gemm_ex")
+        from . import backend as _b
+        from ._lib import lib
+        dist.all_gather_into_tensor(recv, send, group=group)
+        _b._ready()
+        _b._check(lib.pg_b200_gather_relayout(recv.data_ptr(), full.data_ptr(), world, m, width, n_total, full.stride(0)),
+                  "pg_b200_gather_relayout")
+        return full
     dist.all_gather(list(recv.unbind(0)), send, group=group)
-    full = torch.empty((m, n_total), dtype=c_local.dtype, device=c_local.device)
     for r, (start, count) in enumerate(shards):
         if count:
             full[:, start:start + count] = recv[r, :, :count]
     return full
+
+
+def row_shards(m, world):
+    """[(start, count)] per rank: contiguous row ranges of A for the upload of a replicated operand."""
+    return batch_shards(m, world)
+
+
+class HostShardedGemm:
+    """pg_gemm_ex with HOST operands on `world` GPUs: the end-to-end form of the N-column partition.
+
+    Every rank needs all of A.  Sending all of A over PCIe once per GPU would make the host side the limit
+    (world copies of A leave host memory), so each rank uploads only rows [r*M/world, (r+1)*M/world) of A and the
+    ranks all-gather A over NVLink (NCCL; row blocks are contiguous, so no re-layout), while the rank's column
+    shard of B is uploaded on a second stream.  Then the local product, then the C shard goes back to the host.
+    Buffers are created once; call() runs one step."""
+
+    def __init__(self, dtype, m, n, k, group=None):
+        from . import backend as _b
+        self._b = _b
+        self.dtype, self.m, self.n, self.k = dtype, m, n, k
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if m % self.world:
+            raise ValueError("M must be a multiple of the number of GPUs for the row-block upload of A")
+        self.c0, self.n_loc = column_shards(n, self.world)[self.rank]
+        self.r0, self.m_loc = row_shards(m, self.world)[self.rank]
+        t16 = torch.float16 if dtype == _b.PG_DTYPE_F16 else torch.bfloat16
+        self.a_dev = torch.empty((m, k), dtype=t16, device="cuda")
+        self.b_dev = torch.empty((k, self.n_loc), dtype=t16, device="cuda")
+        self.c_dev = torch.empty((m, self.n_loc), dtype=torch.float32, device="cuda")
+        self.side = torch.cuda.Stream()
+        self.h2d_bytes = (self.m_loc * k + k * self.n_loc) * 2
+        self.d2h_bytes = m * self.n_loc * 4
+
+    def __call__(self, a_rows_host, b_shard_host, c_shard_host):
+        """a_rows_host: this rank's row block of A [m_loc, k]; b_shard_host: its column shard of B [k, n_loc];
+        c_shard_host: receives its column shard of C [m, n_loc].  Pinned host tensors (16-bit data viewed as int16
+        is fine).  Returns after the result is on the host."""
+        cur = torch.cuda.current_stream()
+        self.side.wait_stream(cur)
+        with torch.cuda.stream(self.side):
+            self.b_dev.view(torch.int16).copy_(b_shard_host.view(torch.int16), non_blocking=True)
+        a_rows = self.a_dev[self.r0:self.r0 + self.m_loc]
+        a_rows.view(torch.int16).copy_(a_rows_host.view(torch.int16), non_blocking=True)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.a_dev.view(torch.int16), a_rows.view(torch.int16), group=self.group)
+        cur.wait_stream(self.side)
+        self._b.pg_gemm_ex(self.dtype, self.m, self.n_loc, self.k, self.a_dev, self.k, self.b_dev, self.n_loc,
+                           self.c_dev, self.n_loc)
+        c_shard_host.copy_(self.c_dev, non_blocking=True)
+        cur.synchronize()

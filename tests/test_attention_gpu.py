@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 # a last-bit difference in a score or in exp() flips the 16-bit rounding of a few probabilities, which shows as an
 # error of O that does not shrink with the row length.  The floors are twice the largest value measured over the
 # shapes of this file.
-E2E_FLOOR = {wl.BF16: 1.2e-4, wl.F16: 1.6e-5}
+E2E_FLOOR = {wl.BF16: 3.2e-4, wl.F16: 5e-5}     # measured maxima: 1.55e-4 (bf16, Sk = 160, D = 64), 2.5e-5 (f16)
 
 
 def e2e_tolerance(dt, sk):

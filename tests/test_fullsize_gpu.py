@@ -41,7 +41,7 @@ def test_config2_bf16_8192(pg, oracle):
     _panels(oracle, wl.BF16, a, b, c, 8192)
     assert freivalds(c, ad.double(), bd.double()) < wl.tolerance(wl.BF16, 8192) / 10
     # every tile configuration must produce the same product (same K order per element)
-    for cfg in (0, 5, 7):
+    for cfg in (0, 1, 4):
         pg.set_option("tile_config", cfg)
         c2 = torch.empty_like(c)
         pg.pg_gemm_ex(wl.BF16, 8192, 8192, 8192, ad, 8192, bd, 8192, c2, 8192)

@@ -94,8 +94,7 @@ def test_tensor_core_epilogue(pg, oracle, dt, act, shape):
         assert got.min() >= 0.0
 
 
-@pytest.mark.parametrize("cfg_name", ["1cta_128x256", "1cta_128x128", "1cta_128x64", "2cta_256x256", "2cta_256x128",
-                                      "2cta_256x256_e8"])
+@pytest.mark.parametrize("cfg_name", ["1cta_128x256", "1cta_128x128", "1cta_128x64", "2cta_256x256", "2cta_256x128"])
 def test_every_auto_tile_config(pg, oracle, cfg_name):
     from picograd_b200 import _lib
     names = [_lib.lib.pg_b200_tile_config_name(i).decode() for i in range(_lib.lib.pg_b200_num_tile_configs())]

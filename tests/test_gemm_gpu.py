@@ -106,7 +106,7 @@ def test_gemm_ex_vs_oracle(pg, oracle, dt, shape, path):
         assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("cfg", range(9))
+@pytest.mark.parametrize("cfg", range(5))
 @pytest.mark.parametrize("epi", [0, 1])
 def test_every_tile_config(pg, oracle, cfg, epi):
     a, b = wl.config2(520, 776, 328)
@@ -159,8 +159,9 @@ def test_fused_split_k_equals_two_kernel_form(pg, oracle):
 
 @pytest.mark.parametrize("shape", [(8192, 1024, 2048), (2048, 3000, 1096), (1304, 1800, 8192)])
 def test_stream_k_schedule(pg, oracle, shape):
-    """A partly filled last wave is dealt out over all SMs by K blocks; tiles shared by several CTAs are
-    finished by the last arriver.  Must agree with the plain schedule and with the oracle."""
+    """A partly filled last wave is dealt out over all SMs by K ranges, two slices per tile at most: the first slice
+    is stored, the second added once the first has landed.  Must agree with the plain schedule and with the
+    oracle, and give the same bits every time (two terms per element, one order)."""
     m, n, k = shape
     a, b = wl.config2(m, n, k)
     ad, bd = to_dev(a, wl.BF16), to_dev(b, wl.BF16)
@@ -168,10 +169,16 @@ def test_stream_k_schedule(pg, oracle, shape):
     for sk in (1, 0):
         pg.set_option("stream_k", sk); pg.set_option("path", 1); pg.set_option("tile_config", 3)
         c = torch.full((m, n), 5.0, device="cuda")
-        for _ in range(2):                      # second call: cached list, re-armed counters
+        for _ in range(2):                      # second call: re-armed hand-over flags
             pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c, n)
         pg.pg_dev_sync()
-        assert ("streamk" in pg.last_path()) == bool(sk), pg.last_path()
+        assert ("balanced_tail" in pg.last_path()) == bool(sk), pg.last_path()
+        if sk:
+            for _ in range(3):
+                c2 = torch.full((m, n), -1.0, device="cuda")
+                pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c2, n)
+                pg.pg_dev_sync()
+                assert torch.equal(c, c2)
         outs[sk] = c
     assert wl.relerr(to_host(outs[1]), to_host(outs[0])) <= wl.tolerance(wl.BF16, k) / 10   # other K cuts, other rounding
     for r0, r1, c0, c1 in ((0, 40, 0, 64), (m - 24, m, n - 40, n), (m // 2, m // 2 + 16, n // 3, n // 3 + 48)):
