@@ -176,6 +176,42 @@ PG_B200_API int pg_b200_gelu_grad(const float *x, const float *gy, float *out, s
 PG_B200_API int pg_b200_cast_f32(const float *src, uint16_t *dst, int dtype16, size_t n);
 PG_B200_API int pg_b200_fill_f32(float *dst, float value, size_t n);
 
+/* ---- picograd's tensor-level callers, device-resident ------------------------ */
+
+/* What the callers read of a pg_tensor (core/tensor.h:21-36), with a DEVICE data pointer.  Strides in elements. */
+#define PG_B200_MAX_NDIM 8      /* PG_MAX_NDIM */
+typedef struct pg_b200_tensor {
+    int dtype;                          /* PG_DTYPE_* */
+    size_t ndim;                        /* 1 .. 8 */
+    size_t shape[PG_B200_MAX_NDIM];
+    size_t stride[PG_B200_MAX_NDIM];
+    void *data;
+} pg_b200_tensor;
+
+/* pg_matmul (ops/matmul.c:186-284), pg_bmm (:340-369), pg_tensordot (:407-490) with picograd's shape rules applied
+ * in this library: 1-D operands promoted to a row / a column, batch dimensions equal or absent on one side, any
+ * batch strides (picograd's odometer), operand dtypes equal, last-dimension stride 1; result always f32, of
+ * picograd's result shape.  `out`: set out->data = NULL to have the result allocated with pg_b200_malloc (free it
+ * with pg_b200_free), or point it at a contiguous f32 buffer of the result's size; dtype / ndim / shape / stride are
+ * filled in either way.  PG_ERR_UNSUPPORTED where picograd returns NULL (reason in pg_b200_last_error()); one rule
+ * is stricter: a 1-D b must have as many elements as a's last dimension (picograd does not check).  pg_bmm takes
+ * contiguous operands, as picograd assumes. */
+PG_B200_API int pg_b200_matmul(const pg_b200_tensor *a, const pg_b200_tensor *b, pg_b200_tensor *out);
+PG_B200_API int pg_b200_bmm(const pg_b200_tensor *a, const pg_b200_tensor *b, pg_b200_tensor *out);
+/* The shape rules alone: fill dtype / ndim / shape / stride of the result (or refuse) without touching any data,
+ * for a caller that allocates the result itself before the call proper. */
+PG_B200_API int pg_b200_matmul_result_shape(const pg_b200_tensor *a, const pg_b200_tensor *b, pg_b200_tensor *out);
+PG_B200_API int pg_b200_tensordot_result_shape(const pg_b200_tensor *a, const pg_b200_tensor *b, size_t ndims,
+                                               const size_t *axes_a, const size_t *axes_b, pg_b200_tensor *out);
+PG_B200_API int pg_b200_tensordot(const pg_b200_tensor *a, const pg_b200_tensor *b, size_t ndims, const size_t *axes_a,
+                                  const size_t *axes_b, pg_b200_tensor *out);
+/* bwd_matmul (autograd/autograd.c:561-706) with the same operand shapes as pg_b200_matmul: grad_out has the shape
+ * of the matmul's result; grad_a / grad_b (either may be NULL) have the shapes of a / b, f32, contiguous.  A
+ * gradient shared by the batch (b 2-D under a batched a, or a 2-D under a batched b) sums over the batch.
+ * accumulate != 0: grad += product (picograd's form); 0: the gradients are overwritten. */
+PG_B200_API int pg_b200_matmul_backward_nd(const pg_b200_tensor *a, const pg_b200_tensor *b, const float *grad_out,
+                                           float *grad_a, float *grad_b, int accumulate);
+
 /* ---- more than one GPU ------------------------------------------------------- */
 
 /* No counterpart in picograd (one device only, backend/cuda/cuda.c:49-55).  pg_gemm_ex is partitioned over the GPUs

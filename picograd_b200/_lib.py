@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libpg_b200.so")
+# $PG_B200_LIBRARY: another build of the same library (e.g. the one with the timing experiments compiled in)
+LIB_PATH = os.environ.get("PG_B200_LIBRARY") or os.path.join(_HERE, "lib", "libpg_b200.so")
 
 _sz = C.c_size_t
 _vp = C.c_void_p
@@ -42,6 +43,12 @@ SIGNATURES = {
     "pg_b200_gelu_grad": (_i, [_vp, _vp, _vp, _sz]),
     "pg_b200_cast_f32": (_i, [_vp, _vp, _i, _sz]),
     "pg_b200_fill_f32": (_i, [_vp, C.c_float, _sz]),
+    "pg_b200_matmul": (_i, [_vp, _vp, _vp]),
+    "pg_b200_bmm": (_i, [_vp, _vp, _vp]),
+    "pg_b200_matmul_result_shape": (_i, [_vp, _vp, _vp]),
+    "pg_b200_tensordot_result_shape": (_i, [_vp, _vp, _sz, _vp, _vp, _vp]),
+    "pg_b200_tensordot": (_i, [_vp, _vp, _sz, _vp, _vp, _vp]),
+    "pg_b200_matmul_backward_nd": (_i, [_vp, _vp, _vp, _vp, _vp, _i]),
     "pg_b200_gather_relayout": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _sz]),
     "pg_b200_gemm_ex_static_scratch": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _i]),
     "pg_b200_set_device": (_i, [_i]),

@@ -213,87 +213,68 @@ def _gemm_batched(dta, dtb, ta, tb, batch, m, n, k, a, lda, sa, b, ldb, sb, c, l
            "pg_b200_gemm_batched")
 
 
+class _Tensor(C.Structure):
+    """pg_b200_tensor (include/pg_b200.h): what picograd's callers read of a pg_tensor, with a device pointer."""
+    _fields_ = [("dtype", C.c_int), ("ndim", C.c_size_t), ("shape", C.c_size_t * 8), ("stride", C.c_size_t * 8),
+                ("data", C.c_void_p)]
+
+
+def _desc(t, dtype=None):
+    d = _Tensor()
+    d.dtype = _code(t, dtype)
+    d.ndim = t.dim()
+    for i in range(t.dim()):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    d.data = t.data_ptr()
+    return d
+
+
+def _result(shape_call, run_call, device):
+    """Two steps through the C entries: the shape rules fill the result's shape (or refuse: None, as picograd
+    returns NULL), the result is allocated as a torch tensor, then the call proper runs into it."""
+    out = _Tensor()
+    st = shape_call(C.byref(out))
+    if st == PG_ERR_UNSUPPORTED:
+        return None
+    _check(st, "result shape")
+    res = torch.empty([out.shape[i] for i in range(out.ndim)], dtype=torch.float32, device=device)
+    out.data = res.data_ptr()
+    if res.numel():
+        _check(run_call(C.byref(out)), "matmul")
+    return res
+
+
+def _usable(*ts):
+    return all(t is not None and isinstance(t, torch.Tensor) and 1 <= t.dim() <= 8 and t.is_cuda for t in ts)
+
+
 def pg_matmul(a, b, dtype=None):
     """pg_matmul (ops/matmul.c:186-284): NumPy-style matmul with 1-D promotion; batch dims must be
     equal or one side unbatched; dtypes must match; last-dim stride must be 1; output float32.
-    Returns None where picograd returns NULL."""
-    if a is None or b is None or a.dim() < 1 or b.dim() < 1:
+    The shape rules run in the C library (pg_b200_matmul).  Returns None where picograd returns NULL."""
+    if not _usable(a, b) or a.dtype != b.dtype:
         return None
-    if a.dtype != b.dtype:
-        return None
-    dt = _code(a, dtype)
-    av, bv = a.dim() == 1, b.dim() == 1
-    if not bv and a.shape[-1] != b.shape[-2]:
-        return None
-    if bv and a.shape[-1] != b.shape[0]:
-        return None
-    if a.stride(-1) != 1 or (not bv and b.stride(-1) != 1):
-        return None
-    am = 1 if av else a.shape[-2]
-    ak = a.shape[-1]
-    bn = 1 if bv else b.shape[-1]
-    abat = list(a.shape[:-2]) if not av else []
-    bbat = list(b.shape[:-2]) if not bv else []
-    if abat and bbat and abat != bbat:
-        return None
-    bshape = abat or bbat
-    nbatch = 1
-    for d in bshape:
-        if d == 0:
-            return None
-        nbatch *= d
-    rshape = list(bshape) + ([] if av else [am]) + ([] if bv else [bn])
-    if not rshape:
-        rshape = [1]
-    out = torch.empty(rshape, dtype=torch.float32, device=a.device)
-    lda = ak if av else a.stride(-2)
-    ldb = 1 if bv else b.stride(-2)
-    # batch strides: contiguous batches (as every picograd constructor makes them) or shared
-    if abat:
-        ac = a if a.is_contiguous() or _uniform_batch(a) else a.contiguous()
-        sa = _batch_stride(ac)
-    else:
-        ac, sa = a, 0
-    if bbat:
-        bc = b if b.is_contiguous() or _uniform_batch(b) else b.contiguous()
-        sb = _batch_stride(bc)
-    else:
-        bc, sb = b, 0
-    if bv:
-        # [k] vector as a k x 1 matrix
-        ldb = 1
-    _gemm_batched(dt, dt, 0, 0, nbatch, am, bn, ak, ac, lda, sa, bc, ldb, sb, out, bn, am * bn)
-    return out
-
-
-def _uniform_batch(t):
-    """True when all leading (batch) dims collapse to one stride."""
-    if t.dim() <= 3:
-        return True
-    exp = t.stride(-3)
-    for d in range(t.dim() - 3, -1, -1):
-        if t.stride(d) != exp:
-            return False
-        exp *= t.shape[d]
-    return True
-
-
-def _batch_stride(t):
-    return t.stride(-3) if t.dim() >= 3 else 0
+    _ready()
+    da, db = _desc(a, dtype), _desc(b, dtype)
+    return _result(lambda o: lib.pg_b200_matmul_result_shape(C.byref(da), C.byref(db), o),
+                   lambda o: lib.pg_b200_matmul(C.byref(da), C.byref(db), o), a.device)
 
 
 def pg_bmm(a, b, dtype=None):
     """pg_bmm (ops/matmul.c:340-369): strict [B,M,K] x [B,K,N] -> float32 [B,M,N]."""
-    if a is None or b is None or a.dim() != 3 or b.dim() != 3:
+    if not _usable(a, b) or a.dim() != 3 or b.dim() != 3:
         return None
     if a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1] or a.dtype != b.dtype:
         return None
-    dt = _code(a, dtype)
+    _ready()
     a, b = a.contiguous(), b.contiguous()
-    bt, m, k = a.shape
-    n = b.shape[2]
-    out = torch.empty((bt, m, n), dtype=torch.float32, device=a.device)
-    _gemm_batched(dt, dt, 0, 0, bt, m, n, k, a, k, m * k, b, n, k * n, out, n, m * n)
+    out = torch.empty((a.shape[0], a.shape[1], b.shape[2]), dtype=torch.float32, device=a.device)
+    da, db, do = _desc(a, dtype), _desc(b, dtype), _desc(out, PG_DTYPE_F32)
+    st = lib.pg_b200_bmm(C.byref(da), C.byref(db), C.byref(do))
+    if st == PG_ERR_UNSUPPORTED:
+        return None
+    _check(st, "pg_bmm")
     return out
 
 
@@ -348,29 +329,19 @@ def _permute_copy(t, perm):
 
 def pg_tensordot(a, b, axes_a, axes_b, dtype=None):
     """pg_tensordot (ops/matmul.c:407-490): contract axes_a of a with axes_b of b — permute to
-    (free, contracted) x (contracted, free), reshape to 2-D, matmul, reshape back."""
-    if a is None or b is None or a.dtype != b.dtype:
+    (free, contracted) x (contracted, free), reshape to 2-D, matmul, reshape back; all inside pg_b200_tensordot."""
+    if not _usable(a, b) or a.dtype != b.dtype or len(axes_a) != len(axes_b):
         return None
+    _ready()
     nd = len(axes_a)
-    if nd < 1 or nd != len(axes_b) or nd > a.dim() or nd > b.dim():
+    arr = C.c_size_t * max(nd, 1)
+    try:
+        xa, xb = arr(*axes_a), arr(*axes_b)
+    except (TypeError, OverflowError):
         return None
-    for i in range(nd):
-        if axes_a[i] >= a.dim() or axes_b[i] >= b.dim() or a.shape[axes_a[i]] != b.shape[axes_b[i]]:
-            return None
-    pa = [d for d in range(a.dim()) if d not in axes_a] + list(axes_a)
-    pb = list(axes_b) + [d for d in range(b.dim()) if d not in axes_b]
-    free_a = [a.shape[d] for d in pa[:a.dim() - nd]]
-    free_b = [b.shape[d] for d in pb[nd:]]
-    kdim = 1
-    for d in axes_a:
-        kdim *= a.shape[d]
-    ra = _permute_copy(a, pa).reshape(-1, kdim)
-    rb = _permute_copy(b, pb).reshape(kdim, -1)
-    rc = pg_matmul(ra, rb, dtype=dtype)
-    if rc is None:
-        return None
-    fshape = free_a + free_b
-    return rc.reshape(fshape if fshape else [1])
+    da, db = _desc(a, dtype), _desc(b, dtype)
+    return _result(lambda o: lib.pg_b200_tensordot_result_shape(C.byref(da), C.byref(db), nd, xa, xb, o),
+                   lambda o: lib.pg_b200_tensordot(C.byref(da), C.byref(db), nd, xa, xb, o), a.device)
 
 
 def _zeros_f32(shape, device):
@@ -381,28 +352,21 @@ def _zeros_f32(shape, device):
 
 
 def pg_matmul_backward(a, b, g, need_a=True, need_b=True, ga=None, gb=None, dtype=None):
-    """bwd_matmul (autograd/autograd.c:561-706): ga += g * B^T, gb += A^T * g with float32 g and
-    float32 gradients; a: [..., m, k], b: [..., k, n] or [k, n]; a, b of one dtype.  Gradient
-    tensors are created zeroed when not passed in (pg_backward zeroes them, :2490-2492)."""
+    """bwd_matmul (autograd/autograd.c:561-706): ga += g * B^T, gb += A^T * g with float32 g and float32
+    gradients; a and b as pg_matmul takes them (1-D operands, batches, a batch-shared operand whose gradient sums
+    over the batch), of one dtype; g has the shape of pg_matmul(a, b).  Gradient tensors are created when not
+    passed in — pg_backward would have zeroed them (:2490-2492), so the products then overwrite instead of adding
+    to zeros; gradients passed in are accumulated into, as in picograd.  Shape logic: pg_b200_matmul_backward_nd."""
     _ready()
-    dt = _code(a, dtype)
     a, b, g = a.contiguous(), b.contiguous(), g.contiguous()
-    m, k = a.shape[-2], a.shape[-1]
-    n = b.shape[-1]
-    batch = 1
-    for d in a.shape[:-2]:
-        batch *= d
-    b_batched = b.dim() > 2
-    # Gradients created here would be zero (pg_backward zeroes them, autograd.c:2490-2492): the products then
-    # overwrite instead of adding to zeros; gradients passed in are accumulated into, as in picograd.
     fresh_a, fresh_b = need_a and ga is None, need_b and gb is None
     overwrite = (fresh_a or not need_a) and (fresh_b or not need_b)
     if fresh_a:
         ga = torch.empty(a.shape, dtype=torch.float32, device=a.device) if overwrite else _zeros_f32(a.shape, a.device)
     if fresh_b:
         gb = torch.empty(b.shape, dtype=torch.float32, device=a.device) if overwrite else _zeros_f32(b.shape, a.device)
-    _check(lib.pg_b200_matmul_backward_ex(dt, batch, m, n, k, a.data_ptr(), b.data_ptr(), int(b_batched),
-                                          g.data_ptr(), ga.data_ptr() if need_a else None,
+    da, db = _desc(a, dtype), _desc(b, dtype)
+    _check(lib.pg_b200_matmul_backward_nd(C.byref(da), C.byref(db), g.data_ptr(), ga.data_ptr() if need_a else None,
                                           gb.data_ptr() if need_b else None, 0 if overwrite else 1),
-           "pg_b200_matmul_backward")
+           "pg_b200_matmul_backward_nd")
     return ga, gb

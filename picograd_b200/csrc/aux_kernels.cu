@@ -36,13 +36,24 @@ __device__ __forceinline__ void split3(float x, unsigned short &h0, unsigned sho
     h2 = bf16_rne(r1 - bf16_up(h1));
 }
 
+// Which pieces hold something: bit i for a non-zero element (either sign of zero counts as zero) in piece i.
+__device__ __forceinline__ uint32_t piece_bits(unsigned short h0, unsigned short h1, unsigned short h2) {
+    return ((h0 & 0x7FFFu) ? 1u : 0u) | ((h1 & 0x7FFFu) ? 2u : 0u) | ((h2 & 0x7FFFu) ? 4u : 0u);
+}
+__device__ __forceinline__ void publish_piece_mask(uint32_t *mask, uint32_t seen) {
+    if (!mask) return;
+    seen = __reduce_or_sync(0xffffffffu, seen);
+    if ((threadIdx.x & 31) == 0 && seen) atomicOr(mask, seen);
+}
+
 // General form: any leading dimensions, one element per thread step.
 __global__ void split_f32_kernel(const float *__restrict__ src, uint64_t ld_src, uint64_t src_bs,
                                  unsigned short *__restrict__ dst, uint64_t ld_dst, uint32_t rows, uint32_t cols,
-                                 uint32_t batch, uint32_t nparts) {
+                                 uint32_t batch, uint32_t nparts, uint32_t *mask) {
     const uint64_t per_batch = (uint64_t)rows * cols;
     const uint64_t total = per_batch * batch;
     const uint64_t part_stride = (uint64_t)rows * ld_dst;
+    uint32_t seen = 0;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t b = i / per_batch;
         const uint64_t r = (i - b * per_batch) / cols;
@@ -53,14 +64,17 @@ __global__ void split_f32_kernel(const float *__restrict__ src, uint64_t ld_src,
         d[0] = h0;
         d[part_stride] = h1;
         if (nparts > 2) d[2 * part_stride] = h2;
+        seen |= piece_bits(h0, h1, nparts > 2 ? h2 : 0);
     }
+    publish_piece_mask(mask, seen);
 }
 
 // Fast form for the common case (cols and both leading dimensions multiples of 4, 16-byte aligned
 // bases): four elements per thread step, one 16-byte load and one 8-byte store per piece.
 __global__ void split_f32_vec4_kernel(const float *__restrict__ src, uint64_t ld_src, uint64_t src_bs,
                                       unsigned short *__restrict__ dst, uint64_t ld_dst, uint32_t rows, uint32_t cols4,
-                                      uint32_t batch, uint32_t nparts) {
+                                      uint32_t batch, uint32_t nparts, uint32_t *mask) {
+    uint32_t seen = 0;
     const uint64_t per_batch = (uint64_t)rows * cols4;
     const uint64_t total = per_batch * batch;
     const uint64_t part_stride = (uint64_t)rows * ld_dst;
@@ -80,21 +94,24 @@ __global__ void split_f32_vec4_kernel(const float *__restrict__ src, uint64_t ld
             v.x = (uint32_t)h[p][0] | ((uint32_t)h[p][1] << 16);
             v.y = (uint32_t)h[p][2] | ((uint32_t)h[p][3] << 16);
             *reinterpret_cast<uint2 *>(d + p * part_stride) = v;
+            if ((v.x | v.y) & 0x7FFF7FFFu) seen |= 1u << p;
         }
     }
+    publish_piece_mask(mask, seen);
 }
 
 int split_f32_to_bf16_launch(const float *src, uint64_t ld_src, uint64_t src_bs, uint16_t *dst, uint64_t ld_dst,
-                             uint32_t rows, uint32_t cols, uint32_t batch, uint32_t nparts, cudaStream_t s) {
+                             uint32_t rows, uint32_t cols, uint32_t batch, uint32_t nparts, cudaStream_t s, uint32_t *mask) {
     const uint64_t total = (uint64_t)rows * cols * batch;
     if (!total) return ST_OK;
+    if (mask && cudaMemsetAsync(mask, 0, sizeof(uint32_t), s) != cudaSuccess) { cudaGetLastError(); return ST_GEMM; }
     const bool vec = cols % 4 == 0 && ld_src % 4 == 0 && ld_dst % 4 == 0 && src_bs % 4 == 0 &&
                      ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 7) == 0;
     if (vec)
         split_f32_vec4_kernel<<<grid_for(total / 4, 256), 256, 0, s>>>(src, ld_src, src_bs, dst, ld_dst, rows, cols / 4,
-                                                                       batch, nparts);
+                                                                       batch, nparts, mask);
     else
-        split_f32_kernel<<<grid_for(total, 256), 256, 0, s>>>(src, ld_src, src_bs, dst, ld_dst, rows, cols, batch, nparts);
+        split_f32_kernel<<<grid_for(total, 256), 256, 0, s>>>(src, ld_src, src_bs, dst, ld_dst, rows, cols, batch, nparts, mask);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
@@ -243,12 +260,12 @@ __global__ void permute_copy_kernel(const T *__restrict__ src, T *__restrict__ d
     }
 }
 int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t ndim, const uint64_t *shape, const uint32_t *perm,
-                        cudaStream_t s) {
+                        cudaStream_t s, const uint64_t *src_stride) {
     if (ndim == 0 || ndim > 8 || (elem_size != 2 && elem_size != 4)) return ST_UNSUPPORTED;
     PermuteParams p = {};
     p.ndim = ndim;
     uint64_t stride[8], run = 1;
-    for (int d = (int)ndim - 1; d >= 0; --d) { stride[d] = run; run *= shape[d]; }
+    for (int d = (int)ndim - 1; d >= 0; --d) { stride[d] = src_stride ? src_stride[d] : run; run *= shape[d]; }
     uint32_t seen = 0;
     p.total = 1;
     for (uint32_t d = 0; d < ndim; ++d) {

@@ -43,10 +43,13 @@ struct State {
     int opt_attn_q_tmem = 1;     // attention kernel: Q copied to tensor memory once per unit and read from there (0: from shared memory)
     int opt_fused_attention = 1; // 0: pg_b200_attention_bmm always runs the three-kernel chain
     DeviceBuf attn_ws;           // S and P of the chain form of pg_b200_attention_bmm
+    DeviceBuf caller_ws[2];      // permuted operand copies of pg_b200_tensordot
     int opt_cluster_splitk = 1;  // K-slices of a skinny product as one cluster (reduction through distributed shared memory)
     int opt_host_blk = 0;        // slab size of the staged host-pointer pipeline (0 = 2048)
-    int opt_stream_k = 1;        // balanced last wave: the K ranges of the tiles of a partly filled last wave are dealt
-                                 // out to all SMs, two slices per tile at most (chosen when it gains >= 2 %)
+    int opt_stream_k = 0;        // balanced last wave: the K ranges of the tiles of a partly filled last wave are dealt
+                                 // out to all SMs, two slices per tile at most.  Off: on B200 it cuts the MMA cycles
+                                 // of the busiest SM pair by 10 % (8192x1024x8192: 160 k -> 143 k) and the clock under
+                                 // the power limit falls by as much (1.52 -> 1.39 GHz): same time to within 1 %
     int opt_pdl = 1;             // programmatic dependent launch of the tensor-core kernels
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
     int opt_l2_hints = 0;    // see TcParams::l2_hints
@@ -179,6 +182,11 @@ static int grow(DeviceBuf &b, size_t bytes) {
     return ST_OK;
 }
 
+void *caller_scratch(int slot, size_t bytes) {
+    if (slot < 0 || slot > 1 || grow(g.caller_ws[slot], bytes ? bytes : 1) != ST_OK) return nullptr;
+    return g.caller_ws[slot].ptr;
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static size_t esize(int dt) { return dt == DT_F32 ? 4 : 2; }
 
@@ -195,6 +203,7 @@ struct Problem {
     const uint16_t *a_pieces = nullptr, *b_pieces = nullptr;
     size_t pieces_ld = 0;
     uint32_t pieces_n = 0;
+    const uint32_t *pieces_mask = nullptr;    // device word: which of those pieces hold a non-zero element
     // pg_cpu_gemm_fused_ex (backend/cpu/gemm.c:718-817): C = act(bias[col] + A*B), batch == 1, no
     // accumulate; c16 (optional) receives C rounded to dtype16
     const float *bias = nullptr;
@@ -276,7 +285,7 @@ static int run_tc(const Problem &p) {
     const size_t b_rows = p.trans_b ? p.n : p.k, b_cols = p.trans_b ? p.k : p.n;
     const size_t a_ld2 = p.a_pieces ? p.pieces_ld : align_up(a_cols, 8);
     const size_t b_ld2 = p.b_pieces ? p.pieces_ld : align_up(b_cols, 8);
-    size_t off = 0, off_a = 0, off_b = 0, off_k = 0;
+    size_t off = 256, off_a = 0, off_b = 0, off_k = 0;      // the first 256 bytes: the piece masks of A (word 0) and B (word 1)
     if (npa > 1 && !p.a_pieces) { off_a = off; off = align_up(off + p.batch * npa * a_rows * a_ld2 * 2, 256); }
     if (npb > 1 && !p.b_pieces) { off_b = off; off = align_up(off + p.batch * npb * b_rows * b_ld2 * 2, 256); }
     // A 16-bit operand that breaks a TMA rule (base not 16-byte aligned, leading dimension or batch
@@ -321,11 +330,12 @@ static int run_tc(const Problem &p) {
     }
     const size_t ws_ld = align_up(p.n, 4);
     if (splits > 1) { off_k = off; off = align_up(off + (size_t)splits * p.m * ws_ld * 4, 256); }
-    if (off) {
+    if (off > 256) {
         int st = grow(g.ws, off);
         if (st != ST_OK) return st;
     }
     char *ws = (char *)g.ws.ptr;
+    uint32_t *ws_masks = (uint32_t *)ws;
 
     // ---- re-pitched copies ----------------------------------------------------------
     if (repitch_a || repitch_b) {
@@ -349,12 +359,15 @@ static int run_tc(const Problem &p) {
     // ---- operand pieces -----------------------------------------------------------
     if (p.a_pieces) {
         t.A.ptr = p.a_pieces; t.A.ld = a_ld2; t.A.z_stride = a_rows * a_ld2; t.A.nparts = npa;
+        t.a_piece_mask = p.pieces_mask;
     } else if (npa > 1) {
         uint16_t *dst = (uint16_t *)(ws + off_a);
         int st;
-        if (p.dtype_a == DT_F32)
+        if (p.dtype_a == DT_F32) {
             st = split_f32_to_bf16_launch((const float *)p.a, p.lda, p.stride_a, dst, a_ld2, (uint32_t)a_rows,
-                                          (uint32_t)a_cols, (uint32_t)p.batch, npa, g.stream);
+                                          (uint32_t)a_cols, (uint32_t)p.batch, npa, g.stream, ws_masks);
+            t.a_piece_mask = ws_masks;
+        }
         else
             st = split_f16_to_bf16_launch((const uint16_t *)p.a, p.lda, p.stride_a, dst, a_ld2, (uint32_t)a_rows,
                                           (uint32_t)a_cols, (uint32_t)p.batch, g.stream);
@@ -365,12 +378,15 @@ static int run_tc(const Problem &p) {
     }
     if (p.b_pieces) {
         t.B.ptr = p.b_pieces; t.B.ld = b_ld2; t.B.z_stride = b_rows * b_ld2; t.B.nparts = npb;
+        t.b_piece_mask = p.pieces_mask;
     } else if (npb > 1) {
         uint16_t *dst = (uint16_t *)(ws + off_b);
         int st;
-        if (p.dtype_b == DT_F32)
+        if (p.dtype_b == DT_F32) {
             st = split_f32_to_bf16_launch((const float *)p.b, p.ldb, p.stride_b, dst, b_ld2, (uint32_t)b_rows,
-                                          (uint32_t)b_cols, (uint32_t)p.batch, npb, g.stream);
+                                          (uint32_t)b_cols, (uint32_t)p.batch, npb, g.stream, ws_masks + 1);
+            t.b_piece_mask = ws_masks + 1;
+        }
         else
             st = split_f16_to_bf16_launch((const uint16_t *)p.b, p.ldb, p.stride_b, dst, b_ld2, (uint32_t)b_rows,
                                           (uint32_t)b_cols, (uint32_t)p.batch, g.stream);
@@ -777,16 +793,21 @@ int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size
     // [batch*m, n] matrix, so it is split once.  (f16 operands and tiny or unaligned shapes go
     // through the general route, which splits per product or uses the FFMA kernel.)
     const uint16_t *pieces = nullptr;
+    uint32_t *pieces_mask = nullptr;
     const size_t ld2 = align_up(n, 8);
     const uint32_t np = (uint32_t)g.opt_f32_parts;
     const bool share = dtype == DT_BF16 && g.opt_path != 2 && ga && gb && (uint64_t)batch * m * n * k > (uint64_t)64 * 64 * 64 &&
                        (uint64_t)batch * m <= 0x7FFFFFFFull && (!b_batched || batch == 1);
     if (share) {
-        st = grow(g.grad_pieces, (size_t)np * batch * m * ld2 * 2 + 256);
+        const size_t piece_bytes = align_up((size_t)np * batch * m * ld2 * 2, 256);
+        st = grow(g.grad_pieces, piece_bytes + 256);
         if (st != ST_OK) return st;
-        // one "batch" of batch*m rows: pieces laid out [piece][batch*m][ld2]
+        // one "batch" of batch*m rows: pieces laid out [piece][batch*m][ld2]; behind them the word that says which
+        // pieces hold anything (a gradient of bf16 values, like the ones of a sum loss, has an all-zero second piece
+        // and both products then run one pass instead of two)
+        pieces_mask = (uint32_t *)((char *)g.grad_pieces.ptr + piece_bytes);
         st = split_f32_to_bf16_launch(gr, n, 0, (uint16_t *)g.grad_pieces.ptr, ld2, (uint32_t)(batch * m), (uint32_t)n, 1, np,
-                                      g.stream);
+                                      g.stream, pieces_mask);
         if (st != ST_OK) return st;
         pieces = (const uint16_t *)g.grad_pieces.ptr;
     }
@@ -795,7 +816,7 @@ int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size
         // k x n) read transposed.  A B shared by the batch folds the batch into the rows of g and ga.
         Problem p = {DT_F32, dtype, 0, 1, batch, m, k, n, gr, n, m * n, b, n, k * n, ga, k, m * k, acc};
         if (!b_batched) { p.batch = 1; p.m = batch * m; p.stride_a = p.stride_b = p.stride_c = 0; }
-        if (pieces && p.batch == 1) { p.a_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; }
+        if (pieces && p.batch == 1) { p.a_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; p.pieces_mask = pieces_mask; }
         st = run_problem(p);
         if (st != ST_OK) return st;
     }
@@ -808,7 +829,7 @@ int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size
             // B shared by the batch (or no batch): gb[k][n] += sum_b A[b]^T g[b]  ==  one product with the
             // batch folded into the contraction: A as [(batch*m)][k], g as [(batch*m)][n]
             Problem p = {dtype, DT_F32, 1, 0, 1, k, n, batch * m, a, k, 0, gr, n, 0, gb, n, 0, acc};
-            if (pieces) { p.b_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; }
+            if (pieces) { p.b_pieces = pieces; p.pieces_ld = ld2; p.pieces_n = np; p.pieces_mask = pieces_mask; }
             st = run_problem(p);
         }
     }
@@ -985,6 +1006,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "cluster_splitk")) { g.opt_cluster_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "small_f32_pipe")) { g_small_f32_pipe = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "pdl")) { g.opt_pdl = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);

@@ -313,6 +313,126 @@ __global__ void __launch_bounds__(256) sgemm_nn_kernel(const SimtParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product for SMALL f32 shapes (the 512^3 of pg_matmul's test configuration): 32 x 64 tile and 128
+// threads, so that 512^3 is 128 CTAs on the 148 SMs (a 64 x 64 tile fills 64), each thread a 4 x 4 block; K slabs
+// of 16 go from global to shared memory with 16-byte cp.async copies, four slabs in flight, one barrier per slab,
+// so the L2 latency that bounded the register-staged kernel (~0.8 us per slab, 32 slabs) is hidden behind the
+// arithmetic.  Rows of A stay rows in shared memory ([m][k], read as 16-byte vectors along k); tails in M, N and K
+// are zero-filled by the copy itself (source size < 16).  One fmaf chain per element, k ascending: the bits of
+// picograd's CPU kernels, as above.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gsrc, int src_bytes) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int PM = 32, PN = 64, PSTAGES = 4;
+int g_small_f32_pipe = 1;      // small f32 products take the cp.async kernel (0: the register-staged 64 x 64 one)
+__global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) {
+    constexpr int LDA = SK + 4, LDB = PN + 4;
+    __shared__ __align__(16) float As[PSTAGES][PM][LDA];
+    __shared__ __align__(16) float Bs[PSTAGES][SK][LDB];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;                 // 16 x 8 threads, each 4 columns x 4 rows
+    const uint32_t bz = blockIdx.z;
+    const long long m0 = (long long)blockIdx.y * PM, n0 = (long long)blockIdx.x * PN;
+    const float *A = reinterpret_cast<const float *>(p.A) + (long long)bz * p.a_bs;
+    const float *B = reinterpret_cast<const float *>(p.B) + (long long)bz * p.b_bs;
+
+    float acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const long long gn = n0 + tx * 4 + j;
+        const float b0 = (p.bias && gn < p.N) ? p.bias[gn] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i][j] = b0;
+    }
+
+    // copy roles: A 32 rows x 4 vectors = one per thread; B 16 k-rows x 16 vectors = two per thread
+    const int a_r = tid >> 2, a_kq = (tid & 3) * 4;
+    const int b_k = tid >> 4, b_nq = (tid & 15) * 4;
+    auto issue = [&](int stage, uint32_t k0) {
+        {
+            const long long gm = m0 + a_r, gk = (long long)k0 + a_kq;
+            int bytes = 0;
+            if (gm < p.M && gk < p.K) bytes = (int)((p.K - gk) < 4 ? (p.K - gk) : 4) * 4;
+            cp_async_16(&As[stage][a_r][a_kq], bytes ? A + gm * p.a_rs + gk : A, bytes);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const long long gk = (long long)k0 + b_k + 8 * h, gn = n0 + b_nq;
+            int bytes = 0;
+            if (gk < p.K && gn < p.N) bytes = (int)((p.N - gn) < 4 ? (p.N - gn) : 4) * 4;
+            cp_async_16(&Bs[stage][b_k + 8 * h][b_nq], bytes ? B + gk * p.b_rs + gn : B, bytes);
+        }
+    };
+
+    const uint32_t slabs = (p.K + SK - 1) / SK;
+#pragma unroll
+    for (int s = 0; s < PSTAGES - 1; ++s) {
+        if ((uint32_t)s < slabs) issue(s, s * SK);
+        cp_async_commit();
+    }
+    for (uint32_t s = 0; s < slabs; ++s) {
+        cp_async_wait<PSTAGES - 2>();          // slab s has landed (this thread's copies) ...
+        __syncthreads();                       // ... and everyone's; the stage read in iteration s - 1 is free again
+        if (s + PSTAGES - 1 < slabs) issue((s + PSTAGES - 1) % PSTAGES, (s + PSTAGES - 1) * SK);
+        cp_async_commit();
+        const int st = s % PSTAGES;
+#pragma unroll
+        for (int kq = 0; kq < SK; kq += 4) {
+            float4 a4[4], b4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a4[i] = *reinterpret_cast<const float4 *>(&As[st][ty * 4 + i][kq]);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) b4[kk] = *reinterpret_cast<const float4 *>(&Bs[st][kq + kk][tx * 4]);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float a = kk == 0 ? a4[i].x : (kk == 1 ? a4[i].y : (kk == 2 ? a4[i].z : a4[i].w));
+                    acc[i][0] = __fmaf_rn(a, b4[kk].x, acc[i][0]);
+                    acc[i][1] = __fmaf_rn(a, b4[kk].y, acc[i][1]);
+                    acc[i][2] = __fmaf_rn(a, b4[kk].z, acc[i][2]);
+                    acc[i][3] = __fmaf_rn(a, b4[kk].w, acc[i][3]);
+                }
+            }
+        }
+    }
+
+    float *Cb = p.C + (long long)bz * p.c_bs;
+    const bool vec = (p.ldc % 4 == 0) && (((uintptr_t)Cb & 15) == 0) && !p.accumulate;
+    const long long gn = n0 + tx * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long gm = m0 + ty * 4 + i;
+        if (gm >= p.M) continue;
+        float y[4], c[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            y[j] = simt_act(acc[i][j], p.act);
+            c[j] = p.act_copy_only ? acc[i][j] : y[j];
+        }
+        if (p.c16) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (gn + j < p.N) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn + j] = simt_to16(y[j], p.dtype16);
+        }
+        float *dst = Cb + gm * p.ldc + gn;
+        if (vec && gn + 3 < p.N) {
+            *reinterpret_cast<float4 *>(dst) = make_float4(c[0], c[1], c[2], c[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (gn + j < p.N) dst[j] = p.accumulate ? dst[j] + c[j] : c[j];
+        }
+    }
+}
+
 int simt_gemm_launch(const SimtGemm &g) {
     if (g.M == 0 || g.N == 0 || g.batch == 0) return ST_OK;
     SimtParams p;
@@ -342,7 +462,10 @@ int simt_gemm_launch(const SimtGemm &g) {
                             g.a_rs % 4 == 0 && g.b_rs % 4 == 0 && g.a_bs % 4 == 0 && g.b_bs % 4 == 0 &&
                             (((uintptr_t)g.A | (uintptr_t)g.B) & 15) == 0;
         if (nn_f32 && big) sgemm_nn_kernel<128><<<grid, 256, 0, g.stream>>>(q);
-        else if (nn_f32) sgemm_nn_kernel<64><<<grid, 256, 0, g.stream>>>(q);
+        else if (nn_f32 && g_small_f32_pipe) {
+            dim3 pgrid((g.N + PN - 1) / PN, (g.M + PM - 1) / PM, nb);
+            sgemm_nn_pipe_kernel<<<pgrid, 128, 0, g.stream>>>(q);
+        } else if (nn_f32) sgemm_nn_kernel<64><<<grid, 256, 0, g.stream>>>(q);
         else if (big) simt_gemm_kernel<128><<<grid, 256, 0, g.stream>>>(q);
         else simt_gemm_kernel<64><<<grid, 256, 0, g.stream>>>(q);
         cudaError_t e = cudaGetLastError();

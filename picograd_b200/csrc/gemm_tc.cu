@@ -86,6 +86,10 @@ struct TcParams {
     uint32_t m_tiles, n_tiles;
     uint32_t k_blocks, kb_per_split;
     uint32_t npass, a_sel, b_sel, a_nparts, b_nparts;
+    // Piece masks (device words, may be null): bit i set = piece i of that operand has a non-zero element.  Passes
+    // over an all-zero piece are skipped (they would add exact zeros): a gradient whose values are bf16 numbers —
+    // the ones of a sum loss, for one — costs one pass instead of two.
+    const uint32_t *a_piece_mask, *b_piece_mask;
     uint32_t a_mn, b_mn;          // operand is MN-major in memory
     uint32_t idesc;               // tcgen05 instruction descriptor
     uint32_t group_m;             // M tiles per rasterisation group
@@ -326,6 +330,30 @@ __device__ __noinline__ void sum_slices_chunk(const TcParams &p, uint32_t row0, 
     }
 }
 
+// The K passes this launch really runs: those of the host's list whose pieces both hold a non-zero element.  The
+// list ends with the pass over the leading pieces (0, 0); it is kept when nothing else is, so that C is still
+// written.  Every role computes the same answer from the same two device words.
+struct PassList { uint32_t n, a_sel, b_sel; };
+__device__ __forceinline__ PassList effective_passes(const TcParams &p) {
+    PassList l = {p.npass, p.a_sel, p.b_sel};
+    if (!p.a_piece_mask && !p.b_piece_mask) return l;
+    const uint32_t ma = p.a_piece_mask ? *reinterpret_cast<const volatile uint32_t *>(p.a_piece_mask) : 0xFFFFFFFFu;
+    const uint32_t mb = p.b_piece_mask ? *reinterpret_cast<const volatile uint32_t *>(p.b_piece_mask) : 0xFFFFFFFFu;
+    l.n = 0; l.a_sel = 0; l.b_sel = 0;
+    for (uint32_t pass = 0; pass < p.npass; ++pass) {
+        const uint32_t ai = (p.a_sel >> (4 * pass)) & 0xF, bi = (p.b_sel >> (4 * pass)) & 0xF;
+        if (((ma >> ai) & 1u) && ((mb >> bi) & 1u)) {
+            l.a_sel |= ai << (4 * l.n); l.b_sel |= bi << (4 * l.n); ++l.n;
+        }
+    }
+    if (l.n == 0) {
+        l.n = 1;
+        l.a_sel = (p.a_sel >> (4 * (p.npass - 1))) & 0xF;
+        l.b_sel = (p.b_sel >> (4 * (p.npass - 1))) & 0xF;
+    }
+    return l;
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
@@ -394,6 +422,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // next kernel of the stream may be scheduled as soon as SMs become free (its own prologue then waits here).
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const PassList passes = effective_passes(p);
     if (PG_DBG(32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 7] = globaltimer_ns();
 
     // Each role loop below is executed by its whole warp with warp-uniform state; the instructions
@@ -412,9 +441,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int32_t m0 = (int32_t)(w.m_blk * BM_CTA * CG + cta_rank * BM_CTA);
             const int32_t n0 = (int32_t)(w.n_blk * BN + cta_rank * C_::BN_CTA);
             const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
-            for (uint32_t pass = 0; pass < p.npass && ok; ++pass) {
-                const int32_t za = (int32_t)(w.batch * p.a_nparts + ((p.a_sel >> (4 * pass)) & 0xF));
-                const int32_t zb = (int32_t)(w.batch * p.b_nparts + ((p.b_sel >> (4 * pass)) & 0xF));
+            for (uint32_t pass = 0; pass < passes.n && ok; ++pass) {
+                const int32_t za = (int32_t)(w.batch * p.a_nparts + ((passes.a_sel >> (4 * pass)) & 0xF));
+                const int32_t zb = (int32_t)(w.batch * p.b_nparts + ((passes.b_sel >> (4 * pass)) & 0xF));
                 for (uint32_t r = 0; r < rounds; ++r) {
                     long long c0 = prof ? clock64() : 0;
                     ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
@@ -509,7 +538,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (prof) t_tmem += clock64() - c0;
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
-                const uint32_t iters = p.npass * rounds;
+                const uint32_t iters = passes.n * rounds;
                 uint32_t r = 0;
                 for (uint32_t it = 0; it < iters; ++it) {
                     long long c1 = prof ? clock64() : 0;
@@ -1165,6 +1194,7 @@ int tc_gemm_launch(const TcGemm &g) {
         return ST_GEMM;
     }
     p.npass = g.npass; p.a_sel = g.a_sel; p.b_sel = g.b_sel;
+    p.a_piece_mask = g.a_piece_mask; p.b_piece_mask = g.b_piece_mask;
     p.a_nparts = g.A.nparts; p.b_nparts = g.B.nparts;
     p.a_mn = g.A.mn_major; p.b_mn = g.B.mn_major;
     const uint32_t fmt = g.dtype == DT_BF16 ? 1u : 0u;

@@ -45,6 +45,7 @@ struct TcGemm {
     TcOperand A, B;            // A: MN extent = M, B: MN extent = N
     uint32_t npass;            // K passes; pass p multiplies part a_sel[p] of A with part b_sel[p] of B
     uint32_t a_sel, b_sel;     // 4 bits per pass
+    const uint32_t *a_piece_mask, *b_piece_mask;   // device words (or null): bit i = piece i has a non-zero element
     float *C;
     uint64_t ldc, c_stride;    // elements; c_stride between batch elements (or split-K slices)
     int accumulate;            // C += A*B instead of C = A*B
@@ -116,11 +117,13 @@ struct SimtGemm {
     cudaStream_t stream;
 };
 int simt_gemm_launch(const SimtGemm &g);
+extern int g_small_f32_pipe;   // small f32 x f32 products: cp.async-pipelined 32 x 64 kernel (1) or the 64 x 64 one (0)
 
 // Helper kernels (aux_kernels.cu)
+// mask (device word, may be null; cleared by the launch): bit i is set when piece i holds a non-zero element
 int split_f32_to_bf16_launch(const float *src, uint64_t ld_src, uint64_t src_bs,
                              uint16_t *dst, uint64_t ld_dst, uint32_t rows, uint32_t cols,
-                             uint32_t batch, uint32_t nparts, cudaStream_t s);
+                             uint32_t batch, uint32_t nparts, cudaStream_t s, uint32_t *mask = nullptr);
 int split_f16_to_bf16_launch(const uint16_t *src, uint64_t ld_src, uint64_t src_bs,
                              uint16_t *dst, uint64_t ld_dst, uint32_t rows, uint32_t cols,
                              uint32_t batch, cudaStream_t s);
@@ -138,8 +141,11 @@ int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, int act_
 int im2col_launch(const float *x, float *col, uint32_t batch, uint32_t cin, uint32_t h, uint32_t w, uint32_t kh, uint32_t kw,
                   uint32_t oh, uint32_t ow, int stride, int pad, cudaStream_t s);
 int bias_rows_launch(float *out, const float *bias, uint32_t cout, uint64_t rows, uint64_t n, cudaStream_t s);
+// src_stride (elements, per source dimension) = nullptr: the source is contiguous
 int permute_copy_launch(const void *src, void *dst, size_t elem_size, uint32_t ndim, const uint64_t *shape, const uint32_t *perm,
-                        cudaStream_t s);
+                        cudaStream_t s, const uint64_t *src_stride = nullptr);
+// grow-only device scratch of the tensor-level callers (two slots: the permuted copies of pg_tensordot)
+void *caller_scratch(int slot, size_t bytes);
 int addmm_finish_launch(float *c, uint64_t ldc, const float *input, uint64_t in_rs, uint64_t in_cs, float alpha, float beta,
                         uint64_t rows, uint64_t n, cudaStream_t s);
 int fill_f32_launch(float *dst, float v, uint64_t n, cudaStream_t s);

@@ -124,7 +124,7 @@ class HostShardedGemm:
         a_rows = self.a_dev[self.r0:self.r0 + self.m_loc]
         a_rows.view(torch.int16).copy_(a_rows_host.view(torch.int16), non_blocking=True)
         if self.world > 1:
-            dist.all_gather_into_tensor(self.a_dev.view(torch.int16), a_rows.view(torch.int16), group=self.group)
+            dist.all_gather_into_tensor(self.a_dev.view(torch.uint8), a_rows.view(torch.uint8), group=self.group)    # bytes: any 16-bit type
         cur.wait_stream(self.side)
         self._b.pg_gemm_ex(self.dtype, self.m, self.n_loc, self.k, self.a_dev, self.k, self.b_dev, self.n_loc,
                            self.c_dev, self.n_loc)

@@ -4,6 +4,7 @@
  *   gemm.c:718-817  C = act(bias[j] + A*B), one fused multiply-add chain per element starting at bias[j]
  *   conv.c:10-146   im2col rows in (ci,ki,kj) order, zeros outside the image, GEMM, then + bias
  *   matmul.c:340-369 + activations.c:22-45  O = bf16(softmax_rows(Q*Kt)) * V
+ *   matmul.c:186-490  pg_matmul / pg_bmm / pg_tensordot shape rules, autograd.c:561-706 the matmul node's backward
  * usage: cabi_extras /path/to/libpg_b200.so      exit code 0 and "all passed" on success. */
 #include <dlfcn.h>
 #include <math.h>
@@ -21,6 +22,19 @@ typedef const char *(*str_fn)(void);
 typedef int (*fused_fn)(int, size_t, size_t, size_t, const void *, size_t, const void *, size_t, float *, size_t, const float *, int);
 typedef int (*conv_fn)(size_t, size_t, size_t, size_t, size_t, size_t, size_t, int, int, const float *, const float *, const float *, float *);
 typedef int (*attn_fn)(int, size_t, size_t, size_t, size_t, const void *, const void *, const void *, float *);
+/* pg_b200_tensor of include/pg_b200.h, restated here so that this file needs no header of the library */
+typedef struct { int dtype; size_t ndim; size_t shape[8]; size_t stride[8]; void *data; } tensor_t;
+typedef int (*mm_fn)(const tensor_t *, const tensor_t *, tensor_t *);
+typedef int (*td_fn)(const tensor_t *, const tensor_t *, size_t, const size_t *, const size_t *, tensor_t *);
+typedef int (*bwd_fn)(const tensor_t *, const tensor_t *, const float *, float *, float *, int);
+
+static tensor_t make_tensor(int dtype, size_t ndim, const size_t *shape, void *data) {
+    tensor_t t; memset(&t, 0, sizeof t);
+    t.dtype = dtype; t.ndim = ndim; t.data = data;
+    size_t run = 1;
+    for (size_t d = ndim; d-- > 0;) { t.shape[d] = shape[d]; t.stride[d] = run; run *= shape[d]; }
+    return t;
+}
 
 static int fails = 0;
 #define CHECK(c) do { if (!(c)) { printf("FAIL:%d %s\n", __LINE__, #c); fails++; } } while (0)
@@ -51,6 +65,10 @@ int main(int argc, char **argv) {
     fused_fn fused = (fused_fn)dlsym(h, "pg_b200_gemm_fused_ex");
     conv_fn conv = (conv_fn)dlsym(h, "pg_b200_conv2d");
     attn_fn attn = (attn_fn)dlsym(h, "pg_b200_attention_bmm");
+    mm_fn matmul = (mm_fn)dlsym(h, "pg_b200_matmul"), bmm = (mm_fn)dlsym(h, "pg_b200_bmm");
+    td_fn tensordot = (td_fn)dlsym(h, "pg_b200_tensordot");
+    bwd_fn backward = (bwd_fn)dlsym(h, "pg_b200_matmul_backward_nd");
+    if (!matmul || !bmm || !tensordot || !backward) { printf("missing symbol (tensor-level callers)\n"); return 2; }
     if (!init || !dmalloc || !dfree || !h2d || !d2h || !dsync || !fused || !conv || !attn || !last_path || !last_error) {
         printf("missing symbol\n"); return 2;
     }
@@ -153,6 +171,99 @@ int main(int argc, char **argv) {
         printf("attention bf16 2x160x264x128: rel err %.2e (%s)\n", rel, last_path());
         dfree(dq); dfree(dk); dfree(dv); dfree(dout);
         free(q); free(kt); free(v); free(o); free(want); free(srow);
+    }
+
+
+    /* ---- picograd's tensor-level callers with its shape rules (the shapes of picograd's tests/test_ops.c:368-492):
+     *      2-D x 2-D, vector x vector, vector x matrix, matrix x vector, batched, batch-shared b, pg_bmm,
+     *      pg_tensordot over two axes, the refusals, and the matmul node's backward with a batch-shared b ---- */
+    {
+        enum { BT = 2, BM = 3, BK = 4, BN = 5 };
+        float a[BT * BM * BK], b[BT * BK * BN], w[BK * BN], v[BK], c[BT * BM * BN];
+        for (int i = 0; i < BT * BM * BK; i++) a[i] = urand();
+        for (int i = 0; i < BT * BK * BN; i++) b[i] = urand();
+        for (int i = 0; i < BK * BN; i++) w[i] = urand();
+        for (int i = 0; i < BK; i++) v[i] = urand();
+        void *da = dmalloc(sizeof a), *db = dmalloc(sizeof b), *dw = dmalloc(sizeof w), *dv = dmalloc(sizeof v);
+        CHECK(da && db && dw && dv);
+        CHECK(h2d(da, a, sizeof a) == 0 && h2d(db, b, sizeof b) == 0 && h2d(dw, w, sizeof w) == 0 && h2d(dv, v, sizeof v) == 0);
+        tensor_t ta3 = make_tensor(0, 3, (size_t[]){BT, BM, BK}, da), tb3 = make_tensor(0, 3, (size_t[]){BT, BK, BN}, db);
+        tensor_t ta2 = make_tensor(0, 2, (size_t[]){BM, BK}, da), tw = make_tensor(0, 2, (size_t[]){BK, BN}, dw);
+        tensor_t tv = make_tensor(0, 1, (size_t[]){BK}, dv);
+        tensor_t out; memset(&out, 0, sizeof out);            /* out.data == NULL: the library allocates */
+        /* batched x batched */
+        CHECK(matmul(&ta3, &tb3, &out) == 0 && out.ndim == 3 && out.shape[0] == BT && out.shape[1] == BM && out.shape[2] == BN && out.data);
+        CHECK(dsync() == 0 && d2h(c, out.data, sizeof c) == 0);
+        for (int s2 = 0; s2 < BT; s2++) for (int i = 0; i < BM; i++) for (int j = 0; j < BN; j++) {
+            float acc = 0; for (int k = 0; k < BK; k++) acc = fmaf(a[(s2 * BM + i) * BK + k], b[(s2 * BK + k) * BN + j], acc);
+            CHECK(c[(s2 * BM + i) * BN + j] == acc);
+        }
+        /* pg_bmm gives the same bits */
+        tensor_t out2; memset(&out2, 0, sizeof out2);
+        float c2[BT * BM * BN];
+        CHECK(bmm(&ta3, &tb3, &out2) == 0 && out2.ndim == 3 && dsync() == 0 && d2h(c2, out2.data, sizeof c2) == 0);
+        CHECK(memcmp(c, c2, sizeof c) == 0);
+        dfree(out.data); dfree(out2.data);
+        /* batched a x shared 2-D b */
+        memset(&out, 0, sizeof out);
+        CHECK(matmul(&ta3, &tw, &out) == 0 && out.ndim == 3 && out.shape[2] == BN && dsync() == 0 && d2h(c, out.data, sizeof c) == 0);
+        for (int s2 = 0; s2 < BT; s2++) for (int i = 0; i < BM; i++) for (int j = 0; j < BN; j++) {
+            float acc = 0; for (int k = 0; k < BK; k++) acc = fmaf(a[(s2 * BM + i) * BK + k], w[k * BN + j], acc);
+            CHECK(c[(s2 * BM + i) * BN + j] == acc);
+        }
+        dfree(out.data);
+        /* vector x vector -> [1]; vector x matrix -> [n]; matrix x vector -> [m] */
+        memset(&out, 0, sizeof out);
+        CHECK(matmul(&tv, &tv, &out) == 0 && out.ndim == 1 && out.shape[0] == 1 && dsync() == 0 && d2h(c, out.data, 4) == 0);
+        { float acc = 0; for (int k = 0; k < BK; k++) acc = fmaf(v[k], v[k], acc); CHECK(c[0] == acc); }
+        dfree(out.data); memset(&out, 0, sizeof out);
+        CHECK(matmul(&tv, &tw, &out) == 0 && out.ndim == 1 && out.shape[0] == BN && dsync() == 0 && d2h(c, out.data, 4 * BN) == 0);
+        for (int j = 0; j < BN; j++) { float acc = 0; for (int k = 0; k < BK; k++) acc = fmaf(v[k], w[k * BN + j], acc); CHECK(c[j] == acc); }
+        dfree(out.data); memset(&out, 0, sizeof out);
+        CHECK(matmul(&ta2, &tv, &out) == 0 && out.ndim == 1 && out.shape[0] == BM && dsync() == 0 && d2h(c, out.data, 4 * BM) == 0);
+        for (int i = 0; i < BM; i++) { float acc = 0; for (int k = 0; k < BK; k++) acc = fmaf(a[i * BK + k], v[k], acc); CHECK(c[i] == acc); }
+        dfree(out.data);
+        /* refusals: inner dimensions, batch dimensions, dtypes */
+        memset(&out, 0, sizeof out);
+        CHECK(matmul(&tw, &ta2, &out) == -1 && out.data == NULL);
+        tensor_t tb_other = make_tensor(0, 3, (size_t[]){BT + 1, BK, BN}, db);
+        CHECK(matmul(&ta3, &tb_other, &out) == -1);
+        tensor_t tw16 = tw; tw16.dtype = 2;
+        CHECK(matmul(&ta2, &tw16, &out) == -1 && strlen(last_error()) > 0);
+        CHECK(bmm(&ta2, &tw, &out) == -1);
+        /* pg_tensordot: a [2,3,4] (viewed from `a`), b [4,3,5]: contract a's axes (1,2) with b's axes (1,0) -> [2,5] */
+        float tb[BK * BM * BN], td[BT * BN];
+        for (int i = 0; i < BK * BM * BN; i++) tb[i] = urand();
+        void *dtb = dmalloc(sizeof tb);
+        CHECK(dtb && h2d(dtb, tb, sizeof tb) == 0);
+        tensor_t tdb = make_tensor(0, 3, (size_t[]){BK, BM, BN}, dtb);
+        memset(&out, 0, sizeof out);
+        CHECK(tensordot(&ta3, &tdb, 2, (size_t[]){1, 2}, (size_t[]){1, 0}, &out) == 0 && out.ndim == 2 && out.shape[0] == BT && out.shape[1] == BN);
+        CHECK(dsync() == 0 && d2h(td, out.data, sizeof td) == 0);
+        for (int s2 = 0; s2 < BT; s2++) for (int j = 0; j < BN; j++) {
+            double acc = 0;
+            for (int i = 0; i < BM; i++) for (int k = 0; k < BK; k++) acc += (double)a[(s2 * BM + i) * BK + k] * tb[(k * BM + i) * BN + j];
+            CHECK(fabs(td[s2 * BN + j] - acc) < 1e-5);
+        }
+        dfree(out.data);
+        CHECK(tensordot(&ta3, &tdb, 2, (size_t[]){1, 2}, (size_t[]){0, 1}, &out) == -1);     /* lengths 3,4 against 4,3 */
+        /* backward of batched a x shared b, loss = sum: ga[s] = 1 * w^T, gw = sum_s a[s]^T * 1 */
+        float g[BT * BM * BN], ga[BT * BM * BK], gw[BK * BN];
+        for (int i = 0; i < BT * BM * BN; i++) g[i] = 1.0f;
+        void *dg = dmalloc(sizeof g), *dga = dmalloc(sizeof ga), *dgw = dmalloc(sizeof gw);
+        CHECK(dg && dga && dgw && h2d(dg, g, sizeof g) == 0);
+        CHECK(backward(&ta3, &tw, (const float *)dg, (float *)dga, (float *)dgw, 0) == 0);
+        CHECK(dsync() == 0 && d2h(ga, dga, sizeof ga) == 0 && d2h(gw, dgw, sizeof gw) == 0);
+        for (int s2 = 0; s2 < BT; s2++) for (int i = 0; i < BM; i++) for (int k = 0; k < BK; k++) {
+            double acc = 0; for (int j = 0; j < BN; j++) acc += w[k * BN + j];
+            CHECK(fabs(ga[(s2 * BM + i) * BK + k] - acc) < 1e-5);
+        }
+        for (int k = 0; k < BK; k++) for (int j = 0; j < BN; j++) {
+            double acc = 0; for (int s2 = 0; s2 < BT; s2++) for (int i = 0; i < BM; i++) acc += a[(s2 * BM + i) * BK + k];
+            CHECK(fabs(gw[k * BN + j] - acc) < 1e-5);
+        }
+        printf("tensor-level callers: matmul shape modes, bmm, tensordot, refusals, backward: done\n");
+        dfree(da); dfree(db); dfree(dw); dfree(dv); dfree(dtb); dfree(dg); dfree(dga); dfree(dgw);
     }
 
     if (fails) { printf("%d check(s) failed: %s\n", fails, last_error()); return 1; }

@@ -88,3 +88,38 @@ def test_tensor_core_route_is_taken_for_16_bit_leaves(pg):
     a, b, g = make_bwd_inputs(dt, ash, bsh, seed)
     _gpu_backward(pg, dt, a, b, g)
     assert pg.last_path().startswith("tc:"), pg.last_path()
+
+
+@pytest.mark.parametrize("kind", ["ones", "bf16-valued", "zeros", "one-row-f32"])
+def test_gradients_whose_second_piece_is_empty(pg, oracle, kind):
+    """The f32 gradient meets the tensor cores as bf16 pieces; a piece without a non-zero element is skipped on the
+    device (the split kernel reports which pieces hold something).  Gradients made of bf16 numbers — the ones of a
+    sum loss — therefore take one pass, a zero gradient still writes zeros, and one f32-valued row brings the second
+    pass back.  All must equal the CPU result."""
+    rng = np.random.default_rng(31)
+    m, n, k = 264, 200, 136
+    a = wl.to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32))
+    b = wl.to_bf16_bits(rng.standard_normal((k, n), dtype=np.float32))
+    if kind == "ones":
+        g = np.ones((m, n), np.float32)
+    elif kind == "zeros":
+        g = np.zeros((m, n), np.float32)
+    else:
+        g = wl.bf16_bits_to_f32(wl.to_bf16_bits(rng.standard_normal((m, n), dtype=np.float32)))
+        if kind == "one-row-f32":
+            g[17] = rng.standard_normal(n, dtype=np.float32)
+    ga0 = torch.full((m, k), 3.0, device="cuda")          # overwritten, not added to
+    gb0 = torch.full((k, n), 3.0, device="cuda")
+    from picograd_b200._lib import lib
+    pg.pg_dev_sync()
+    st = lib.pg_b200_matmul_backward_ex(wl.BF16, 1, m, n, k, to_dev(a, wl.BF16).data_ptr(), to_dev(b, wl.BF16).data_ptr(), 0,
+                                        to_dev(g, wl.F32).data_ptr(), ga0.data_ptr(), gb0.data_ptr(), 0)
+    assert st == 0
+    pg.pg_dev_sync()
+    assert pg.last_path().startswith("tc:"), pg.last_path()
+    ga_ref, gb_ref = oracle.matmul_backward(wl.BF16, a, b, g)
+    if kind == "zeros":
+        assert not ga0.any().item() and not gb0.any().item()
+    else:
+        assert wl.relerr(to_host(ga0), ga_ref) <= wl.tolerance(wl.BF16, n)
+        assert wl.relerr(to_host(gb0), gb_ref) <= wl.tolerance(wl.BF16, m)

@@ -65,6 +65,23 @@ def test_f32_large_bit_exact(pg, oracle, lds):
     assert np.array_equal(got, oracle.gemm_ex(wl.F32, a, b))
 
 
+@pytest.mark.parametrize("pipe", [1, 0], ids=["cp.async-32x64", "register-staged-64x64"])
+@pytest.mark.parametrize("shape", [(512, 512, 512, 0), (97, 203, 301, 0), (33, 65, 17, 4), (1, 4, 1, 0), (250, 120, 1000, 8)])
+def test_f32_small_kernels_bit_exact(pg, oracle, shape, pipe):
+    """Both kernels that serve small f32 products (pg_matmul's 512^3 among them) keep one fused-multiply-add chain
+    per element over k ascending: the CPU result bit for bit, with ragged edges in M, N and K (K not a multiple of
+    the 16-deep slab, N not a multiple of 4) and padded leading dimensions."""
+    m, n, k, pad = shape
+    rng = np.random.default_rng(21)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    pg.set_option("small_f32_pipe", pipe)
+    r4 = lambda v: (v + 3) // 4 * 4
+    got = gemm_dev(pg, wl.F32, a, b, lda=r4(k) + pad, ldb=r4(n) + pad, ldc=r4(n) + pad)
+    assert pg.last_path() == "simt"
+    assert np.array_equal(got, oracle.gemm_ex(wl.F32, a, b))
+
+
 def test_f32_on_tensor_cores_within_1e6(pg, oracle):
     """f32 x f32 as three exact bf16 pieces per operand, six tensor-core passes."""
     a, b = wl.config1(512)
