@@ -614,9 +614,9 @@ def mlp_step(pg, ops, wl, xd, w1d, w2d, dy, h, a16):
                         pg.PG_ACT_GELU | pg.PG_ACT_COPY_ONLY, a16, 16384)
     y = pg.pg_matmul(a16, w2d)
     da, dw2 = pg.pg_matmul_backward(a16, w2d, dy)
-    dh = ops.gelu_grad(h, da)
-    dx, dw1 = pg.pg_matmul_backward(xd, w1d, dh)
-    return y, da, dw2, dh, dx, dw1
+    # the GELU node's backward (dh = da * gelu'(h)) happens inside the split that feeds the first layer's backward
+    dx, dw1, _ = pg.pg_matmul_backward_act(xd, w1d, da, pg.PG_ACT_GELU, h)
+    return y, da, dw2, dx, dw1
 
 
 def main():

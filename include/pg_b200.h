@@ -165,6 +165,16 @@ PG_B200_API int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, si
                                const void *a, const void *b, int b_batched,
                                const float *g, float *ga, float *gb, int accumulate);
 
+/* The same with the backward of an activation node folded in (no counterpart as one call in picograd, whose
+ * autograd runs bwd_gelu / bwd_relu, autograd.c:794-801 / :557, as a pass of its own before bwd_matmul): the
+ * gradient that enters the products is g' = g * act'(act_input), act = PG_ACT_RELU or PG_ACT_GELU, act_input f32 of
+ * g's shape [batch*m, n].  On the tensor-core route g' is cut into its bf16 pieces as it is computed and never
+ * written as f32; pass gr_pre (f32, g's shape) to receive it as well, or NULL.  act == 0: plain
+ * pg_b200_matmul_backward_ex. */
+PG_B200_API int pg_b200_matmul_backward_act(int dtype, size_t batch, size_t m, size_t n, size_t k,
+                                const void *a, const void *b, int b_batched, const float *g, int act,
+                                const float *act_input, float *gr_pre, float *ga, float *gb, int accumulate);
+
 /* Harness steps between the GEMMs of the attention-shaped and MLP workloads
  * (ops/activations.c:22-45 softmax rows, :114 GELU, autograd.c:794-801 GELU
  * gradient), so that those workloads stay on the device.  out16 (optional)
@@ -255,7 +265,10 @@ PG_B200_API int pg_b200_gemm_ex_static_scratch(int dtype, size_t m, size_t n, si
 /* Device ordinal used by pg_b200_init (picograd uses device 0, cuda.c:49). */
 PG_B200_API int pg_b200_set_device(int ordinal);
 /* Run the library's kernels and copies on this CUDA stream (a cudaStream_t /
- * CUstream handle; NULL = the default stream). */
+ * CUstream handle; NULL = the default stream).  Calls are stream-ordered: the library keeps ONE scratch
+ * buffer, one set of arrival counters, one set of staging buffers and one status word per process, so two
+ * calls in flight on different streams would share them and return wrong sums.  Switch streams only after
+ * the previous stream's work has been synchronised; one caller thread, like picograd (backend.c:50). */
 PG_B200_API int pg_b200_set_stream(void *stream);
 /* Text of the last error recorded by this library ("" if none). */
 PG_B200_API const char *pg_b200_last_error(void);

@@ -34,6 +34,7 @@ SIGNATURES = {
                                   _vp, _sz, _sz, _i]),
     "pg_b200_matmul_backward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _vp, _i, _vp, _vp, _vp]),
     "pg_b200_matmul_backward_ex": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _vp, _i, _vp, _vp, _vp, _i]),
+    "pg_b200_matmul_backward_act": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i]),
     "pg_b200_addmm": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _sz, C.c_float, C.c_float]),
     "pg_b200_permute_copy": (_i, [_i, _sz, _vp, _vp, _vp, _vp]),
     "pg_b200_conv2d": (_i, [_sz] * 7 + [_i, _i, _vp, _vp, _vp, _vp]),

@@ -47,7 +47,9 @@ def pg_set_device(ordinal=None):
 def _ready():
     if not _initialised:
         pg_set_device()
-    # kernels are queued on torch's current stream so that torch events time them
+    # kernels are queued on torch's current stream so that torch events time them.  The library's scratch, counters
+    # and status word exist once per process: callers that change torch's current stream must synchronise the old
+    # stream first (calls in flight on two streams would share that scratch).
     lib.pg_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
@@ -349,6 +351,29 @@ def _zeros_f32(shape, device):
     t = torch.empty(tuple(shape), dtype=torch.float32, device=device)
     _check(lib.pg_b200_fill_f32(t.data_ptr(), 0.0, t.numel()), "pg_b200_fill_f32")
     return t
+
+
+def pg_matmul_backward_act(a, b, g, act, act_input, need_a=True, need_b=True, want_pre=False, dtype=None):
+    """bwd of an activation node (autograd/autograd.c:794-801 GELU, :557 ReLU) followed by bwd_matmul (:561-706) in
+    one call: the gradient entering the products is g * act'(act_input).  a [m,k] (or [batch,m,k] with a shared
+    b [k,n]), g and act_input float32 of the matmul output's shape.  Returns (ga, gb, g') with g' None unless
+    want_pre; fresh gradients are overwritten (pg_backward would have zeroed them)."""
+    _ready()
+    a, b, g, act_input = a.contiguous(), b.contiguous(), g.contiguous(), act_input.contiguous()
+    dt = _code(a, dtype)
+    m, k = a.shape[-2], a.shape[-1]
+    n = b.shape[-1]
+    batch = 1
+    for d in a.shape[:-2]:
+        batch *= d
+    ga = torch.empty(a.shape, dtype=torch.float32, device=a.device) if need_a else None
+    gb = torch.empty(b.shape, dtype=torch.float32, device=a.device) if need_b else None
+    pre = torch.empty(g.shape, dtype=torch.float32, device=a.device) if want_pre else None
+    _check(lib.pg_b200_matmul_backward_act(dt, batch, m, n, k, a.data_ptr(), b.data_ptr(), int(b.dim() > 2), g.data_ptr(),
+                                           int(act), act_input.data_ptr(), pre.data_ptr() if want_pre else None,
+                                           ga.data_ptr() if need_a else None, gb.data_ptr() if need_b else None, 0),
+           "pg_b200_matmul_backward_act")
+    return ga, gb, pre
 
 
 def pg_matmul_backward(a, b, g, need_a=True, need_b=True, ga=None, gb=None, dtype=None):

@@ -429,6 +429,68 @@ int gelu_grad_launch(const float *x, const float *gy, float *out, uint64_t n, cu
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
 }
 
+// The backward of an activation node folded into the split that feeds the next matmul node's backward:
+// g' = gy * act'(x) (autograd/autograd.c:794-801 for GELU, :557 for ReLU) is cut into bf16 pieces as it is made and
+// never stored as f32 (unless out32 is given).  Same arithmetic as gelu_grad_kernel followed by the split kernel.
+// Layout of dst: [part][rows*cols padded to ld]: one "batch" of rows x cols with leading dimension ld_dst.
+__global__ void act_grad_split_kernel(const float *__restrict__ x, const float *__restrict__ gy, int act,
+                                      float *__restrict__ out32, unsigned short *__restrict__ dst, uint64_t ld_dst,
+                                      uint32_t rows, uint32_t cols4, uint32_t nparts, uint32_t *mask) {
+    const uint64_t total = (uint64_t)rows * cols4;
+    const uint64_t part_stride = (uint64_t)rows * ld_dst;
+    const uint64_t cols = (uint64_t)cols4 * 4;
+    uint32_t seen = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = i / cols4, c = (i - r * cols4) * 4;
+        const float4 v = *reinterpret_cast<const float4 *>(x + r * cols + c);
+        const float4 g = *reinterpret_cast<const float4 *>(gy + r * cols + c);
+        float4 y;
+        if (act == 2) y = make_float4(gelu_grad_f(v.x, g.x), gelu_grad_f(v.y, g.y), gelu_grad_f(v.z, g.z), gelu_grad_f(v.w, g.w));
+        else y = make_float4(v.x > 0.0f ? g.x : 0.0f, v.y > 0.0f ? g.y : 0.0f, v.z > 0.0f ? g.z : 0.0f, v.w > 0.0f ? g.w : 0.0f);
+        if (out32) *reinterpret_cast<float4 *>(out32 + r * cols + c) = y;
+        unsigned short h[3][4];
+        split3(y.x, h[0][0], h[1][0], h[2][0]);
+        split3(y.y, h[0][1], h[1][1], h[2][1]);
+        split3(y.z, h[0][2], h[1][2], h[2][2]);
+        split3(y.w, h[0][3], h[1][3], h[2][3]);
+        unsigned short *d = dst + r * ld_dst + c;
+        for (uint32_t p = 0; p < nparts; ++p) {
+            uint2 w;
+            w.x = (uint32_t)h[p][0] | ((uint32_t)h[p][1] << 16);
+            w.y = (uint32_t)h[p][2] | ((uint32_t)h[p][3] << 16);
+            *reinterpret_cast<uint2 *>(d + p * part_stride) = w;
+            if ((w.x | w.y) & 0x7FFF7FFFu) seen |= 1u << p;
+        }
+    }
+    publish_piece_mask(mask, seen);
+}
+// rows x cols contiguous f32 inputs, cols a multiple of 4, 16-byte aligned bases; ST_UNSUPPORTED otherwise
+int act_grad_split_launch(const float *x, const float *gy, int act, float *out32, uint16_t *dst, uint64_t ld_dst,
+                          uint32_t rows, uint32_t cols, uint32_t nparts, cudaStream_t s, uint32_t *mask) {
+    if (!rows || !cols) return ST_OK;
+    if ((act != 1 && act != 2) || cols % 4 || ld_dst % 4 || (((uintptr_t)x | (uintptr_t)gy | (uintptr_t)out32) & 15) ||
+        ((uintptr_t)dst & 7))
+        return ST_UNSUPPORTED;
+    if (mask && cudaMemsetAsync(mask, 0, sizeof(uint32_t), s) != cudaSuccess) { cudaGetLastError(); return ST_GEMM; }
+    act_grad_split_kernel<<<grid_for((uint64_t)rows * cols / 4, 256), 256, 0, s>>>(x, gy, act, out32, dst, ld_dst, rows, cols / 4,
+                                                                                  nparts, mask);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+// the same product as f32 only (no pieces): g' = gy * act'(x), for the routes that split per product
+__global__ void act_grad_kernel(const float *__restrict__ x, const float *__restrict__ gy, int act, float *__restrict__ out,
+                                uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = act == 2 ? gelu_grad_f(x[i], gy[i]) : (x[i] > 0.0f ? gy[i] : 0.0f);
+}
+int act_grad_launch(const float *x, const float *gy, int act, float *out, uint64_t n, cudaStream_t s) {
+    if (!n) return ST_OK;
+    if (act != 1 && act != 2) return ST_UNSUPPORTED;
+    act_grad_kernel<<<grid_for(n, 256), 256, 0, s>>>(x, gy, act, out, n);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_GEMM;
+}
+
 // One warp per row: max, sum of exp(x - max), normalise (picograd ops/activations.c:22-45).
 // General form: three passes over the row (it stays in L1/L2 between them).
 __global__ void softmax_rows_kernel(const float *__restrict__ src, float *__restrict__ d32,

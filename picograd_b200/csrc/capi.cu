@@ -785,9 +785,17 @@ int pg_b200_matmul_backward(int dtype, size_t batch, size_t m, size_t n, size_t 
 
 int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size_t k, const void *a, const void *b,
                                int b_batched, const float *gr, float *ga, float *gb, int accumulate) {
+    return pg_b200_matmul_backward_act(dtype, batch, m, n, k, a, b, b_batched, gr, 0, nullptr, nullptr, ga, gb, accumulate);
+}
+
+int pg_b200_matmul_backward_act(int dtype, size_t batch, size_t m, size_t n, size_t k, const void *a, const void *b,
+                                int b_batched, const float *gr, int act, const float *act_input, float *gr_pre, float *ga,
+                                float *gb, int accumulate) {
     if (!ready()) return g.init_status;
     const int acc = accumulate ? 1 : 0;
     if (batch == 0 || m == 0 || n == 0 || k == 0) return ST_OK;
+    if (act < 0 || act > 2 || (act && !act_input)) { set_error("pg_b200_matmul_backward_act: activation %d needs its input", act); return ST_UNSUPPORTED; }
+    if (!gr) { set_error("pg_b200_matmul_backward_act: no incoming gradient"); return ST_UNSUPPORTED; }
     int st = ST_OK;
     // The f32 gradient meets the tensor cores as exact bf16 pieces; both products read the same
     // [batch*m, n] matrix, so it is split once.  (f16 operands and tiny or unaligned shapes go
@@ -806,10 +814,34 @@ int pg_b200_matmul_backward_ex(int dtype, size_t batch, size_t m, size_t n, size
         // pieces hold anything (a gradient of bf16 values, like the ones of a sum loss, has an all-zero second piece
         // and both products then run one pass instead of two)
         pieces_mask = (uint32_t *)((char *)g.grad_pieces.ptr + piece_bytes);
-        st = split_f32_to_bf16_launch(gr, n, 0, (uint16_t *)g.grad_pieces.ptr, ld2, (uint32_t)(batch * m), (uint32_t)n, 1, np,
-                                      g.stream, pieces_mask);
+        st = ST_UNSUPPORTED;
+        // (only where the tensor-core route is certain to take both products: the FFMA fallback would need the f32 form)
+        const bool tma_safe = n % 8 == 0 && k % 8 == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0;
+        if (act && (gr_pre || tma_safe))   // the activation node's backward happens inside the split
+            st = act_grad_split_launch(act_input, gr, act, gr_pre, (uint16_t *)g.grad_pieces.ptr, ld2, (uint32_t)(batch * m),
+                                       (uint32_t)n, np, g.stream, pieces_mask);
+        if (st == ST_OK && act) {
+            // without gr_pre the f32 form of g' does not exist; the products below read the pieces only
+            gr = gr_pre ? gr_pre : (const float *)g.grad_pieces.ptr;
+            act = 0;
+        } else if (!act) {
+            st = split_f32_to_bf16_launch(gr, n, 0, (uint16_t *)g.grad_pieces.ptr, ld2, (uint32_t)(batch * m), (uint32_t)n, 1, np,
+                                          g.stream, pieces_mask);
+        }
+        if (st == ST_OK) pieces = (const uint16_t *)g.grad_pieces.ptr;
+        else if (st != ST_UNSUPPORTED) return st;
+    }
+    if (act) {
+        // general route: g' = g * act'(input) as f32 (into the caller's buffer, else scratch), then as any gradient
+        float *dst = gr_pre;
+        if (!dst) {
+            st = grow(g.caller_ws[0], batch * m * n * sizeof(float));
+            if (st != ST_OK) return st;
+            dst = (float *)g.caller_ws[0].ptr;
+        }
+        st = act_grad_launch(act_input, gr, act, dst, batch * m * n, g.stream);
         if (st != ST_OK) return st;
-        pieces = (const uint16_t *)g.grad_pieces.ptr;
+        gr = dst;
     }
     if (ga) {
         // ga[batch][m][k] += g[batch][m][n] * B^T : the product's "A" is g (m x n), its "B" is B (stored

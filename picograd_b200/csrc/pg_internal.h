@@ -134,6 +134,9 @@ int add_inplace_launch(float *dst, const float *src, uint64_t n, cudaStream_t s)
 int cast_f32_launch(const float *src, uint16_t *dst, uint64_t n, int dtype, cudaStream_t s);
 int gelu_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16, uint64_t n, cudaStream_t s);
 int gelu_grad_launch(const float *x, const float *gy, float *out, uint64_t n, cudaStream_t s);
+int act_grad_split_launch(const float *x, const float *gy, int act, float *out32, uint16_t *dst, uint64_t ld_dst,
+                          uint32_t rows, uint32_t cols, uint32_t nparts, cudaStream_t s, uint32_t *mask);
+int act_grad_launch(const float *x, const float *gy, int act, float *out, uint64_t n, cudaStream_t s);
 int softmax_rows_launch(const float *src, float *dst_f32, uint16_t *dst_16, int dtype16,
                         uint64_t rows, uint32_t len, cudaStream_t s);
 int bias_act_launch(float *c, uint64_t ldc, const float *bias, int act, int act_copy_only, uint16_t *c16, uint64_t ld16,

@@ -112,8 +112,9 @@ def test_gradients_whose_second_piece_is_empty(pg, oracle, kind):
     gb0 = torch.full((k, n), 3.0, device="cuda")
     from picograd_b200._lib import lib
     pg.pg_dev_sync()
-    st = lib.pg_b200_matmul_backward_ex(wl.BF16, 1, m, n, k, to_dev(a, wl.BF16).data_ptr(), to_dev(b, wl.BF16).data_ptr(), 0,
-                                        to_dev(g, wl.F32).data_ptr(), ga0.data_ptr(), gb0.data_ptr(), 0)
+    ad, bd, gd = to_dev(a, wl.BF16), to_dev(b, wl.BF16), to_dev(g, wl.F32)      # held until the call has run
+    st = lib.pg_b200_matmul_backward_ex(wl.BF16, 1, m, n, k, ad.data_ptr(), bd.data_ptr(), 0, gd.data_ptr(), ga0.data_ptr(),
+                                        gb0.data_ptr(), 0)
     assert st == 0
     pg.pg_dev_sync()
     assert pg.last_path().startswith("tc:"), pg.last_path()

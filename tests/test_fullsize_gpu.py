@@ -105,32 +105,39 @@ def test_config4_attention_bmm_full(pg, oracle):
 
 
 def test_config5_mlp_step_full(pg, oracle):
-    """x[8192,4096] -> Linear(4096->16384) -> gelu -> Linear(16384->4096) -> sum; forward and backward.
-    Each of the six GEMMs is checked with the Freivalds property on its own inputs, and panels of the
-    forward products against the oracle."""
+    """x[8192,4096] -> Linear(4096->16384) -> gelu -> Linear(16384->4096) -> sum; forward and backward, through the
+    very calls bench.py --config 5 times: first layer fused (h in f32 and bf16(gelu(h)) from one kernel), gradients
+    overwritten, the GELU node's backward folded into the split that feeds the first layer's backward.  Each of the six
+    GEMMs is checked with the Freivalds property on its own inputs, and panels against the oracle."""
+    import math
     from picograd_b200 import ops
+    from bench import mlp_step
     x, w1, w2 = wl.config5()
     xd, w1d, w2d = (to_dev(t, wl.BF16) for t in (x, w1, w2))
-    h = pg.pg_matmul(xd, w1d); pg.pg_dev_sync()
+    dy = torch.ones((8192, 4096), dtype=torch.float32, device="cuda")
+    h = torch.empty((8192, 16384), dtype=torch.float32, device="cuda")
+    a16 = torch.empty((8192, 16384), dtype=torch.bfloat16, device="cuda")
+    y, da, dw2, dx, dw1 = mlp_step(pg, ops, wl, xd, w1d, w2d, dy, h, a16)
+    pg.pg_dev_sync()
+    # forward
     _panels(oracle, wl.BF16, x, w1, h, 4096, rows=((0, 24), (-16, None)), cols=((0, 48), (-32, None)))
     assert freivalds(h, xd.double(), w1d.double()) < wl.tolerance(wl.BF16, 4096) / 10
-    a32, a16 = ops.gelu(h, out16=torch.bfloat16); pg.pg_dev_sync()
-    del a32
-    y = pg.pg_matmul(a16, w2d); pg.pg_dev_sync()
+    hp = to_host(h[:64, :256])
+    assert np.array_equal(bits_to_host(a16[:64, :256]), wl.to_bf16_bits(oracle.gelu(hp))) or \
+        np.abs(to_host(a16[:64, :256]) - oracle.gelu(hp)).max() < 2.0 ** -8 * np.abs(oracle.gelu(hp)).max()
     assert freivalds(y, a16.double(), w2d.double()) < wl.tolerance(wl.BF16, 16384) / 10
-    dy = torch.ones_like(y)
-    da, dw2 = pg.pg_matmul_backward(a16, w2d, dy); pg.pg_dev_sync()
-    # dA = dY W2^T ; dW2 = A^T dY  (two bf16 pieces of the f32 gradient: 2^-17 per element)
+    # backward of the second layer: dA = dY W2^T ; dW2 = A^T dY (dY = 1: its second bf16 piece is empty, one pass each)
     assert freivalds(da, dy.double(), w2d.double(), transb=True) < wl.tolerance(wl.BF16, 4096) / 10
     assert freivalds(dw2, a16.double(), dy.double(), transa=True) < wl.tolerance(wl.BF16, 8192) / 10
-    dh = ops.gelu_grad(h, da); pg.pg_dev_sync()
-    del da, dy, y
-    dx, dw1 = pg.pg_matmul_backward(xd, w1d, dh); pg.pg_dev_sync()
-    assert freivalds(dx, dh.double(), w1d.double(), transb=True) < wl.tolerance(wl.BF16, 16384) / 10
-    assert freivalds(dw1, xd.double(), dh.double(), transa=True) < wl.tolerance(wl.BF16, 8192) / 10
-    # one panel of a gradient against the oracle's f32 definition
-    dh_h = to_host(dh[:, :64])
-    # (the full-size CPU backward would take minutes; use the definition dW1 = X^T dH as an f32 GEMM)
+    del y, dy
+    # the GELU node: dH = dA * gelu'(h), here in float64 from the same h and dA
+    h64 = h.double()
+    dh = da.double() * (0.5 * (1 + torch.erf(h64 / math.sqrt(2))) + h64 * torch.exp(-0.5 * h64 * h64) / math.sqrt(2 * math.pi))
+    del h64
+    assert freivalds(dx, dh, w1d.double(), transb=True) < wl.tolerance(wl.BF16, 16384) / 10
+    assert freivalds(dw1, xd.double(), dh, transa=True) < wl.tolerance(wl.BF16, 8192) / 10
+    # one panel of a gradient against the oracle's f32 definition dW1 = X^T dH
+    dh_h = dh[:, :64].float().cpu().numpy()
     xt = np.ascontiguousarray(wl.bf16_bits_to_f32(x).T)          # [4096, 8192] f32, exact upcast
     want = oracle.gemm_ex(wl.F32, xt[:32], dh_h)                 # rows 0..31 of dW1[:, :64]
     assert wl.relerr(to_host(dw1[:32, :64]), want) <= wl.tolerance(wl.BF16, 8192)

@@ -563,3 +563,29 @@ def test_backward_batched_and_shared_b(pg, oracle):
         ga_ref[s] = x; gb_ref += y
     assert wl.relerr(to_host(ga), ga_ref) <= wl.tolerance(wl.BF16, n)
     assert wl.relerr(to_host(gb), gb_ref) <= wl.tolerance(wl.BF16, bt * m)
+
+
+@pytest.mark.parametrize("act", [1, 2], ids=["relu", "gelu"])
+@pytest.mark.parametrize("shape", [(256, 512, 128, True), (136, 264, 200, False), (72, 100, 50, False)],
+                         ids=["tma-safe", "want-pre", "odd-sizes"])
+def test_backward_with_folded_activation_gradient(pg, oracle, act, shape):
+    """pg_b200_matmul_backward_act: the activation node's backward inside the split that feeds bwd_matmul.  Against the
+    CPU chain: g' = g * act'(h) (autograd.c:794-801 / :557), then ga = g' B^T, gb = A^T g' on identical g' bytes where
+    the f32 form is returned, within the path tolerance otherwise."""
+    m, n, k, drop_pre = shape
+    rng = np.random.default_rng(33)
+    a = wl.to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32))
+    b = wl.to_bf16_bits(rng.uniform(-0.1, 0.1, (k, n)).astype(np.float32))
+    h = rng.standard_normal((m, n), dtype=np.float32) * 2
+    g = rng.standard_normal((m, n), dtype=np.float32)
+    ga, gb, pre = pg.pg_matmul_backward_act(to_dev(a, wl.BF16), to_dev(b, wl.BF16), to_dev(g, wl.F32), act, to_dev(h, wl.F32),
+                                            want_pre=not drop_pre)
+    pg.pg_dev_sync()
+    want_pre = oracle.gelu_grad(h, g) if act == 2 else np.where(h > 0, g, 0).astype(np.float32)
+    if pre is not None:
+        assert np.abs(to_host(pre) - want_pre).max() < 1e-4
+        want_pre = to_host(pre)               # identical bytes feed both sides
+    ga_ref, gb_ref = oracle.matmul_backward(wl.BF16, a, b, want_pre)
+    slack = 1.0 if pre is not None else 2.0   # without the f32 form the two sides' g' differ by erf rounding
+    assert wl.relerr(to_host(ga), ga_ref) <= slack * wl.tolerance(wl.BF16, n)
+    assert wl.relerr(to_host(gb), gb_ref) <= slack * wl.tolerance(wl.BF16, m)
