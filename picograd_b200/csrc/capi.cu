@@ -26,6 +26,8 @@ struct State {
     uint32_t *dev_status = nullptr;
     uint32_t *host_status = nullptr;   // pinned mirror
     unsigned long long *prof = nullptr;   // per-CTA cycle counters of the timing experiments
+    unsigned char *die_table = nullptr;   // smid -> die, measured at init (null when the measurement was not clean)
+    uint32_t *die_claim = nullptr;        // claim counters of the die-aware walk (zero between launches)
     uint32_t *counters = nullptr;         // arrival counters of the fused split-K reduction (zero between launches)
     uint32_t num_counters = 0;
     DeviceBuf ws;                      // scratch: operand pieces, split-K slices
@@ -51,6 +53,7 @@ struct State {
                                  // of the busiest SM pair by 10 % (8192x1024x8192: 160 k -> 143 k) and the clock under
                                  // the power limit falls by as much (1.52 -> 1.39 GHz): same time to within 1 %
     int opt_pdl = 1;             // programmatic dependent launch of the tensor-core kernels
+    int opt_die_aware = 1;       // large products: each die of the B200 walks its own half of every rasterisation group
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
     int opt_l2_hints = 0;    // see TcParams::l2_hints
     int opt_group_m = 0;     // 0: choose
@@ -135,6 +138,17 @@ static int do_init() {
     } else {
         g.counters = nullptr; g.num_counters = 0; cudaGetLastError();
     }
+    // die topology: 8 KB = scratch of the measurement (4 KB), then the table (256 B) and the claim words
+    void *topo = nullptr;
+    if (cudaMalloc(&topo, 8192) == cudaSuccess && cudaMemset(topo, 0, 8192) == cudaSuccess) {
+        unsigned char table[256];
+        if (measure_die_table(table, topo, nullptr) &&
+            cudaMemcpy((char *)topo + 4096, table, 256, cudaMemcpyHostToDevice) == cudaSuccess) {
+            g.die_table = (unsigned char *)topo + 4096;
+            g.die_claim = (uint32_t *)((char *)topo + 4096 + 256);
+        }
+    }
+    cudaGetLastError();
     return g.init_status = ST_OK;
 }
 
@@ -261,6 +275,7 @@ static int run_tc(const Problem &p) {
     t.stages = g.opt_stages; t.debug = g.opt_debug; t.l2_hints = g.opt_l2_hints; t.group_m = g.opt_group_m;
     t.stream = g.stream; t.dev_status = g.dev_status; t.prof = g.prof;
     t.allow_stream_k = g.opt_stream_k && !p.no_split_k;
+    if (g.opt_die_aware) { t.die_table = g.die_table; t.die_claim = g.die_claim; }
     t.pdl = g.opt_pdl;
     t.cluster_splitk = g.opt_cluster_splitk;
     t.counters = g.counters; t.num_counters = g.num_counters;
@@ -728,6 +743,7 @@ int pg_b200_sync(void) {
         *g.host_status = 0;
         cudaMemsetAsync(g.dev_status, 0, 4, g.stream);
         if (g.counters) cudaMemsetAsync(g.counters, 0, (size_t)g.num_counters * 4, g.stream);   // an aborted kernel may leave counts
+        if (g.die_claim) cudaMemsetAsync(g.die_claim, 0, 16, g.stream);
         cudaStreamSynchronize(g.stream);
         return ST_GEMM;
     }
@@ -1039,6 +1055,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "small_f32_pipe")) { g_small_f32_pipe = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "die_aware")) { g.opt_die_aware = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "pdl")) { g.opt_pdl = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }
     set_error("unknown option %s", name);

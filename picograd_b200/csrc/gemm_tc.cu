@@ -122,6 +122,14 @@ struct TcParams {
     // and no tile has more than two K-slices (see tail_unit).  `counters` then holds one hand-over flag per
     // (tail tile, CTA of the pair, epilogue warp).
     uint32_t sk_on, sk_full, sk_q, sk_r;
+    // Die-aware walk (die_table != nullptr): the two dies of a B200 each have their own half of the L2, and a line
+    // read by SMs of both dies occupies both halves.  Each rasterisation group of group_m M-tiles is cut in two:
+    // the CTA pairs of die 0 walk the upper group_m / 2 M-tiles, those of die 1 the lower ones, both along N in
+    // step.  The A panel of a group then lives in ONE half of the L2 (half the footprint per half, so it survives
+    // from wave to wave) and only B is shared across the link.  die_table[smid] is measured once per process;
+    // die_claim = {pairs of die 0 so far, of die 1, pairs finished} gives every pair a rank on its die.
+    const unsigned char *die_table;
+    uint32_t *die_claim;
     uint32_t *status;
     unsigned long long *prof;     // debug & 32: 16 cycle counters per CTA
 };
@@ -202,19 +210,31 @@ __device__ __noinline__ bool tail_unit(const TcParams &p, uint32_t c, uint32_t S
 
 // The i-th work unit of a cluster (i = 0, 1, ...); false past the last one.  Every role of the CTA (pair) walks the
 // same sequence.
-__device__ __forceinline__ bool get_unit(const TcParams &p, uint32_t cluster_id, uint32_t num_clusters, uint32_t total_units,
-                                         uint32_t i, WorkUnit &w) {
+struct Walk { uint32_t id, count, die; };    // this CTA pair's position: id of count (on its die when die-aware)
+
+__device__ __forceinline__ bool get_unit(const TcParams &p, const Walk &wk, uint32_t total_units, uint32_t i, WorkUnit &w) {
+    if (p.die_table) {
+        // this die's half of every group: h = group_m / 2 M-tiles x n_tiles, M fastest
+        const uint32_t h = p.group_m >> 1, per_g = h * p.n_tiles;
+        const uint32_t j = wk.id + i * wk.count;
+        if (j >= (p.m_tiles >> 1) * p.n_tiles) return false;
+        const uint32_t g = j / per_g, in_g = j - g * per_g;
+        w.n_blk = in_g / h;
+        w.m_blk = g * p.group_m + wk.die * h + (in_g - w.n_blk * h);
+        w.batch = 0; w.split = 0; w.kb_begin = 0; w.kb_count = p.k_blocks; w.role = 0; w.flag_tile = 0;
+        return true;
+    }
     if (!p.sk_on) {
-        const uint64_t u = (uint64_t)cluster_id + (uint64_t)i * num_clusters;
+        const uint64_t u = (uint64_t)wk.id + (uint64_t)i * wk.count;
         if (u >= total_units) return false;
         w = decode_unit(p, (uint32_t)u);
         return true;
     }
     if (i < p.sk_full) {
-        w = decode_unit(p, cluster_id + i * num_clusters);
+        w = decode_unit(p, wk.id + i * wk.count);
         return true;
     }
-    return tail_unit(p, cluster_id, num_clusters, i - p.sk_full, w);
+    return tail_unit(p, wk.id, wk.count, i - p.sk_full, w);
 }
 
 // Hand-over flag of a shared tail tile (global memory, gpu scope).
@@ -382,6 +402,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
     const uint32_t abort_off = (bar_base - smem_base) + 8u * (2 * STAGES + 4) + 8u;
     const uint32_t red_bar = bar_base + 8u * (2 * STAGES + 4) + 16u;   // cluster reduction: partial tiles have landed
+    const uint32_t die_slot = bar_base + 8u * (2 * STAGES + 4) + 24u;  // die-aware walk: this pair's (die, rank)
     volatile uint32_t *tmem_slot_gen = (volatile uint32_t *)(smem_gen + (tmem_slot - smem_base));
     volatile uint32_t *abort_flag = (volatile uint32_t *)(smem_gen + abort_off);
 
@@ -423,6 +444,31 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const PassList passes = effective_passes(p);
+    Walk walk = {cluster_id, num_clusters, 0};
+    if (p.die_table) {
+        // Which die is this CTA pair on, and the how-manieth pair of that die is it?  A die with more than half of
+        // the pairs hands its surplus to the ranks the other die leaves unclaimed (exactly as many: the grid is
+        // num_clusters pairs), so every (die, rank) is taken once whatever the placement.
+        volatile uint32_t *slot = (volatile uint32_t *)(smem_gen + (die_slot - smem_base));
+        if (threadIdx.x == 0 && cta_rank == 0) {
+            uint32_t smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            uint32_t d = p.die_table[smid & 255u] & 1u;
+            uint32_t r = atomicAdd(p.die_claim + d, 1u);
+            const uint32_t half = num_clusters >> 1;
+            if (r >= half) { d ^= 1u; r = 2u * half - 1u - r; }
+            const uint32_t word = d | (r << 8);
+            *slot = word;
+            if constexpr (CG == 2) {
+                asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(mapa(die_slot, 1)), "r"(word) : "memory");
+            }
+        }
+        if (CG == 2) cluster_sync_all(); else __syncthreads();
+        const uint32_t word = *slot;
+        walk.die = word & 1u;
+        walk.id = word >> 8;
+        walk.count = num_clusters >> 1;
+    }
     if (PG_DBG(32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 7] = globaltimer_ns();
 
     // Each role loop below is executed by its whole warp with warp-uniform state; the instructions
@@ -437,7 +483,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint64_t pol_a = l2_policy((int)(p.l2_hints & 3u)), pol_b = l2_policy((int)((p.l2_hints >> 2) & 3u));
         for (uint32_t ui = 0; ok; ++ui) {
             WorkUnit w;
-            if (!get_unit(p, cluster_id, num_clusters, total_units, ui, w)) break;
+            if (!get_unit(p, walk, total_units, ui, w)) break;
             const int32_t m0 = (int32_t)(w.m_blk * BM_CTA * CG + cta_rank * BM_CTA);
             const int32_t n0 = (int32_t)(w.n_blk * BN + cta_rank * C_::BN_CTA);
             const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
@@ -527,9 +573,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             };
 
             WorkUnit w, w_next;
-            bool have = get_unit(p, cluster_id, num_clusters, total_units, 0, w);
+            bool have = get_unit(p, walk, total_units, 0, w);
             for (uint32_t ui = 0; have && ok; ++ui, w = w_next) {
-                const bool more_units = get_unit(p, cluster_id, num_clusters, total_units, ui + 1, w_next);
+                const bool more_units = get_unit(p, walk, total_units, ui + 1, w_next);
                 have = more_units;
                 long long c0 = prof ? clock64() : 0;
                 ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_TMEM_EMPTY);
@@ -616,7 +662,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         long long te_wait = 0, te_ld = 0, te_math = 0, te_store = 0, last_e3 = 0;
         for (uint32_t ui = 0; ok; ++ui) {
             WorkUnit w;
-            if (!get_unit(p, cluster_id, num_clusters, total_units, ui, w)) break;
+            if (!get_unit(p, walk, total_units, ui, w)) break;
             // Bias of a chunk: lane l holds bias[col + l], fetched one chunk ahead (the first one before the
             // wait for the accumulator) and handed round by shuffles, so no chunk waits for a load.
             auto bias_fetch = [&](uint32_t c) -> float {
@@ -911,6 +957,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc<CG>(tmem_base, C_::TMEM_COLS);
+    }
+    if (p.die_table && threadIdx.x == 0 && cta_rank == 0) {
+        // the last pair to finish re-arms the claim counters for the next launch
+        __threadfence();
+        if (atomicAdd(p.die_claim + 2, 1u) == num_clusters - 1) {
+            p.die_claim[0] = 0; p.die_claim[1] = 0; p.die_claim[2] = 0;
+            __threadfence();
+        }
     }
     if (PG_DBG(32u) && p.prof && threadIdx.x == 0) p.prof[(size_t)blockIdx.x * 16 + 15] = globaltimer_ns();
 }
@@ -1299,6 +1353,14 @@ int tc_gemm_launch(const TcGemm &g) {
     }
 
     if (p.cluster_k) clusters = (uint32_t)units;      // one unit per CTA; consecutive CTAs = the slices of one tile
+    // die-aware walk: large single products that fill every SM pair for several waves, groups that halve evenly
+    bool die_aware = false;
+    if (g.die_table && g.die_claim && !stream_k && !p.cluster_k && p.batch == 1 && p.splits == 1 &&
+        clusters == (uint32_t)rt.max_clusters && clusters % 2 == 0 && p.group_m % 2 == 0 && p.m_tiles % p.group_m == 0 &&
+        units >= 4ull * clusters && !(kExperiments && (p.debug & 31u))) {
+        p.die_table = g.die_table; p.die_claim = g.die_claim;
+        die_aware = true;
+    }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(clusters * c.cg, 1, 1);
     lc.blockDim = dim3(c.threads, 1, 1);
@@ -1327,7 +1389,7 @@ int tc_gemm_launch(const TcGemm &g) {
     }
     note_launch();
     set_last_path("tc:%s%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
-                  p.cluster_k ? ":cluster" : (p.Cout ? ":fused" : ""), stream_k ? ":balanced_tail" : "");
+                  p.cluster_k ? ":cluster" : (p.Cout ? ":fused" : ""), stream_k ? ":balanced_tail" : (die_aware ? ":die_aware" : ""));
     return ST_OK;
 }
 

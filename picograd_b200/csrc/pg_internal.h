@@ -60,6 +60,8 @@ struct TcGemm {
     uint32_t num_counters;
     int cluster_splitk;        // may run the K-slices of a narrow tile as one cluster, summed through distributed shared memory
     int allow_stream_k;        // may deal the K ranges of a partly filled last wave out to all clusters (two slices per tile)
+    const unsigned char *die_table;   // device table smid -> die (or null: die-oblivious walk); see topology.cu
+    uint32_t *die_claim;              // three zeroed device words (claims per die, pairs finished)
     int pdl;                   // launch with programmatic stream serialisation: the prologue overlaps the previous kernel's tail
     uint32_t splits;           // >1: split-K, slice s goes to C + s*c_stride (batch must be 1)
     int force_cfg;             // -1 = choose; else index into the config table
@@ -81,6 +83,8 @@ bool tc_gemm_supported(const TcGemm &g);
 int wait_timeout_selftest_launch(uint32_t *status, unsigned limit_ms, cudaStream_t stream);
 extern int g_l2_promotion;   // CUtensorMapL2promotion of the operand tensor maps
 int tc_tail_schedule(uint64_t tiles, uint32_t slots, uint32_t k_blocks, uint32_t c, uint32_t j, uint32_t out[6]);
+// topology.cu: measures which SMs share a die; false when the SMs do not fall into two clean groups
+bool measure_die_table(unsigned char table[256], void *scratch, cudaStream_t stream);
 int tc_num_configs();
 const char *tc_config_name(int cfg);
 int tc_config_index(const char *name);   // -1 if unknown

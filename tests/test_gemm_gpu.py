@@ -589,3 +589,44 @@ def test_backward_with_folded_activation_gradient(pg, oracle, act, shape):
     slack = 1.0 if pre is not None else 2.0   # without the f32 form the two sides' g' differ by erf rounding
     assert wl.relerr(to_host(ga), ga_ref) <= slack * wl.tolerance(wl.BF16, n)
     assert wl.relerr(to_host(gb), gb_ref) <= slack * wl.tolerance(wl.BF16, m)
+
+
+def test_die_aware_walk_changes_no_bit(pg, oracle):
+    """Large products are walked die by die (each half of the L2 keeps its own half of a group's A panel).  Only the
+    order of the tiles changes: same bits as the die-oblivious walk, launch after launch (the claim counters re-arm
+    themselves), also when the launches are replayed from a CUDA graph."""
+    m, n, k = 8192, 4096, 512
+    a, b = wl.config2(m, n, k)
+    ad, bd = to_dev(a, wl.BF16), to_dev(b, wl.BF16)
+    pg.set_option("die_aware", 0)
+    ref = torch.empty((m, n), device="cuda")
+    pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, ref, n); pg.pg_dev_sync()
+    assert "die_aware" not in pg.last_path()
+    pg.set_option("die_aware", 1)
+    c = torch.zeros((m, n), device="cuda")
+    pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c, n); pg.pg_dev_sync()
+    if "die_aware" not in pg.last_path():
+        pytest.skip("the SMs of this GPU did not fall into two clean latency groups: " + pg.last_path())
+    assert torch.equal(c, ref)
+    for _ in range(3):
+        c.zero_()
+        pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c, n); pg.pg_dev_sync()
+        assert torch.equal(c, ref)
+    want = oracle.gemm_ex_panel(wl.BF16, a, b, 4000, 4040, 1000, 1064)
+    assert wl.relerr(to_host(c[4000:4040, 1000:1064]), want) <= wl.tolerance(wl.BF16, k)
+    # the same launch replayed from a graph: every replay claims, walks and re-arms again
+    from picograd_b200 import _lib
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        _lib.lib.pg_b200_set_stream(side.cuda_stream)
+        pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c, n); side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c, n)
+            pg.pg_gemm_ex(wl.BF16, m, n, k, ad, k, bd, n, c, n)
+        for _ in range(3):
+            c.zero_()
+            graph.replay(); side.synchronize()
+            assert torch.equal(c, ref)
+    _lib.lib.pg_b200_set_stream(None)
+    pg.pg_dev_sync()
