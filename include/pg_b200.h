@@ -293,6 +293,11 @@ PG_B200_API int pg_b200_debug_counters(uint64_t *out, size_t count);
  * tile, first K block, number of K blocks (0 = no such part), role (1 = first slice: stored, 2 = second slice: added)}. */
 PG_B200_API int pg_b200_debug_tail_schedule(uint64_t tiles, unsigned slots, unsigned k_blocks, unsigned cluster,
                                             unsigned part, unsigned out[6]);
+/* Diagnostic: the table smid -> die (0 / 1) that pg_b200_init measured on this GPU (L2 hit latency from every SM to
+ * one address: the SMs of the die that holds the line answer ~70 cycles sooner) and that the die-aware tile walk of
+ * the tensor-core GEMM uses; up to 256 entries.  PG_ERR_UNSUPPORTED when the SMs did not fall into two clean groups
+ * (the GEMM then walks its tiles without regard to the dies). */
+PG_B200_API int pg_b200_die_table(unsigned char *out, size_t count);
 /* Number of kernels this library has launched since it was loaded. */
 PG_B200_API uint64_t pg_b200_launch_count(void);
 /* Name of the path the last GEMM call took ("tc:2cta_256x256", "simt", ...). */

@@ -60,6 +60,7 @@ SIGNATURES = {
     "pg_b200_tile_config_name": (C.c_char_p, [_i]),
     "pg_b200_launch_count": (C.c_uint64, []),
     "pg_b200_last_path": (C.c_char_p, []),
+    "pg_b200_die_table": (_i, [_vp, _sz]),
     "pg_b200_debug_counters": (_i, [_vp, _sz]),
     "pg_b200_debug_tail_schedule": (_i, [C.c_uint64, C.c_uint, C.c_uint, C.c_uint, C.c_uint, _vp]),
     "pg_b200_selftest_wait_timeout": (_i, [C.c_uint]),

@@ -138,14 +138,14 @@ static int do_init() {
     } else {
         g.counters = nullptr; g.num_counters = 0; cudaGetLastError();
     }
-    // die topology: 8 KB = scratch of the measurement (4 KB), then the table (256 B) and the claim words
-    void *topo = nullptr;
-    if (cudaMalloc(&topo, 8192) == cudaSuccess && cudaMemset(topo, 0, 8192) == cudaSuccess) {
+    // die topology (measured once; see topology.cu): the table (256 B) and the claim words of the die-aware walk
+    {
         unsigned char table[256];
-        if (measure_die_table(table, topo, nullptr) &&
-            cudaMemcpy((char *)topo + 4096, table, 256, cudaMemcpyHostToDevice) == cudaSuccess) {
-            g.die_table = (unsigned char *)topo + 4096;
-            g.die_claim = (uint32_t *)((char *)topo + 4096 + 256);
+        void *topo = nullptr;
+        if (measure_die_table(table, nullptr) && cudaMalloc(&topo, 512) == cudaSuccess && cudaMemset(topo, 0, 512) == cudaSuccess &&
+            cudaMemcpy(topo, table, 256, cudaMemcpyHostToDevice) == cudaSuccess) {
+            g.die_table = (unsigned char *)topo;
+            g.die_claim = (uint32_t *)((char *)topo + 256);
         }
     }
     cudaGetLastError();
@@ -1009,6 +1009,13 @@ int pg_b200_gather_relayout(const float *staging, float *dst, size_t shards, siz
     const int st = gather_relayout_launch(staging, dst, (uint32_t)shards, rows, width, n, ld, g.stream);
     if (st == ST_UNSUPPORTED) set_error("pg_b200_gather_relayout: %zu shards of %zu columns do not cover n = %zu (ld %zu)", shards, width, n, ld);
     return st;
+}
+
+int pg_b200_die_table(unsigned char *out, size_t count) {
+    if (!ready()) return g.init_status;
+    if (!g.die_table) return ST_UNSUPPORTED;
+    if (count > 256) count = 256;
+    return cudaMemcpy(out, g.die_table, count, cudaMemcpyDeviceToHost) == cudaSuccess ? ST_OK : ST_COPY;
 }
 
 int pg_b200_debug_counters(uint64_t *out, size_t count) {

@@ -84,7 +84,7 @@ int wait_timeout_selftest_launch(uint32_t *status, unsigned limit_ms, cudaStream
 extern int g_l2_promotion;   // CUtensorMapL2promotion of the operand tensor maps
 int tc_tail_schedule(uint64_t tiles, uint32_t slots, uint32_t k_blocks, uint32_t c, uint32_t j, uint32_t out[6]);
 // topology.cu: measures which SMs share a die; false when the SMs do not fall into two clean groups
-bool measure_die_table(unsigned char table[256], void *scratch, cudaStream_t stream);
+bool measure_die_table(unsigned char table[256], cudaStream_t stream);
 int tc_num_configs();
 const char *tc_config_name(int cfg);
 int tc_config_index(const char *name);   // -1 if unknown
