@@ -20,7 +20,11 @@
  * Parity pins: the golden vectors of picograd's tests (tests/test_backend.c:
  * 62-96 exact 2x1x2 case and 13x9x7 grid; benchmarks/bench_gemm_cuda.c:16-65
  * dyadic 512^3 data that is exact in f32; tests/test_gemm.c:126-189 shape
- * grid) and the outputs of the unmodified library built into oracle/_ref.
+ * grid) and the outputs of the unmodified library built into oracle/_ref:
+ * products, fused epilogues, conv, addmm, and — for pgo_matmul_backward — the
+ * gradients of picograd's own pg_ag_matmul -> pg_backward on f32, bf16 and f16
+ * leaves (tests/golden/make_golden.py), reproduced bit for bit where
+ * bwd_matmul takes its GEMM route (autograd/autograd.c:635).
  */
 #include "pg_oracle.h"
 

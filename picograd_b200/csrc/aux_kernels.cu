@@ -6,6 +6,7 @@
 // 16-byte accesses where alignment allows.
 
 #include "pg_internal.h"
+#include "fast_math.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -445,7 +446,7 @@ __global__ void act_grad_split_kernel(const float *__restrict__ x, const float *
         const float4 v = *reinterpret_cast<const float4 *>(x + r * cols + c);
         const float4 g = *reinterpret_cast<const float4 *>(gy + r * cols + c);
         float4 y;
-        if (act == 2) y = make_float4(gelu_grad_f(v.x, g.x), gelu_grad_f(v.y, g.y), gelu_grad_f(v.z, g.z), gelu_grad_f(v.w, g.w));
+        if (act == 2) y = make_float4(gelu_grad_fast(v.x, g.x), gelu_grad_fast(v.y, g.y), gelu_grad_fast(v.z, g.z), gelu_grad_fast(v.w, g.w));
         else y = make_float4(v.x > 0.0f ? g.x : 0.0f, v.y > 0.0f ? g.y : 0.0f, v.z > 0.0f ? g.z : 0.0f, v.w > 0.0f ? g.w : 0.0f);
         if (out32) *reinterpret_cast<float4 *>(out32 + r * cols + c) = y;
         unsigned short h[3][4];

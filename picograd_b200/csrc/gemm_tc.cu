@@ -25,6 +25,7 @@
 
 #include "pg_internal.h"
 #include "tc_ptx.cuh"
+#include "fast_math.cuh"
 
 #include <stdio.h>
 #include <string.h>
@@ -262,28 +263,6 @@ __device__ __noinline__ bool flag_wait(uint32_t *flag, volatile uint32_t *abort_
     return true;
 }
 
-// 0.5 x (1 + erf(x / sqrt 2)), picograd's act_apply (backend/cpu/gemm.c:632-636), with
-// erf(a) = sign(a) (1 - 2^(t Q(t))), t = min(|a|, 4): one piece, no branch, 13 instructions, so the
-// epilogue warps take few issue slots from the MMA and producer warps they share schedulers with.
-// Q is a weighted least-squares fit of log2(erfc(t)) / t on [0, 4.05]; tests/test_erf_coefficients.py refits it
-// and checks these numbers (erf to 8e-8 absolute, GELU to 5e-7 at |x| = 6).
-__device__ __forceinline__ float erf_nodiv(float a) {
-    const float t = fminf(fabsf(a), 4.0f);
-    float r = fmaf(-4.477160110e-05f, t, 4.406937805e-04f);
-    r = fmaf(r, t, -1.474020537e-03f);
-    r = fmaf(r, t, -7.993229083e-04f);
-    r = fmaf(r, t, 2.827465348e-02f);
-    r = fmaf(r, t, -1.484908313e-01f);
-    r = fmaf(r, t, -9.184145331e-01f);
-    r = fmaf(r, t, -1.627908707e+00f);
-    float e;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(r * t));     // argument in [-25, 0]: no denormal result
-    return copysignf(1.0f - e, a);
-}
-__device__ __forceinline__ float gelu_erf(float x) {
-    const float h = 0.5f * x;
-    return fmaf(h, erf_nodiv(x * 0.70710678118f), h);
-}
 __device__ __forceinline__ uint32_t pack_bf16(uint32_t lo, uint32_t hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));

@@ -43,8 +43,10 @@ def batch_shards(batch, world):
     return out
 
 
-def gather_columns(c_local, n_total, group=None, align=8, out=None, staging=None):
+def gather_columns(c_local, n_total, group=None, align=8, out=None, staging=None, membership=None, step=0):
     """All ranks receive the full row-major [M, n_total] matrix from the column shards.
+    With a `membership`, the step is announced and every rank's presence is checked on the host first: RankLeft is
+    raised instead of entering a collective that a departed rank would never join.
 
     On the GPU: one NCCL all-gather of the shards into a [world][M][width] staging buffer (a shard narrower than
     the widest one is padded first), then the library's re-layout kernel (pg_b200_gather_relayout) writes the
@@ -52,6 +54,9 @@ def gather_columns(c_local, n_total, group=None, align=8, out=None, staging=None
     On the CPU (gloo, used by the tests of the host logic) the re-layout is a loop of slice copies."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
+    if membership is not None:
+        membership.announce(step)
+        membership.check(step)
     shards = column_shards(n_total, world, align)
     m = c_local.shape[0]
     width = max(c for _, c in shards)
@@ -78,6 +83,57 @@ def gather_columns(c_local, n_total, group=None, align=8, out=None, staging=None
         if count:
             full[:, start:start + count] = recv[r, :, :count]
     return full
+
+
+class RankLeft(RuntimeError):
+    """A rank of the group has left (or has not reached this step in time); `ranks` lists them."""
+
+    def __init__(self, ranks, step):
+        self.ranks, self.step = list(ranks), step
+        super().__init__(f"rank(s) {self.ranks} absent at step {step}")
+
+
+class Membership:
+    """Who is still there?  Host-side failure detection for the one place where ranks depend on each other, the
+    all-gather of `gather_columns` (the products themselves need no exchange: a rank that loses a peer still owns
+    valid shards).  Every rank announces each step in the process group's key-value store before it enters a
+    collective and says so when it leaves; `check` returns normally when all ranks have announced the step and raises
+    RankLeft — before anything is launched on the GPU — when one has left or is late.  Ranks leave between steps
+    only, with none of their kernels or collectives in flight."""
+
+    def __init__(self, store, rank, world, prefix="pg_b200/member"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def announce(self, step):
+        self.store.set(f"{self.prefix}/step/{self.rank}", str(int(step)))
+
+    def leave(self):
+        self.store.set(f"{self.prefix}/left/{self.rank}", "1")
+
+    def _get(self, key):
+        # check() wraps this in its own deadline: a key that is not there yet must not block for the store's timeout
+        return self.store.get(key) if self.store.check([key]) else None
+
+    def check(self, step, timeout_s=1.0, poll_s=0.01):
+        import time
+        deadline = time.monotonic() + timeout_s
+        missing = []
+        while True:
+            missing, left = [], []
+            for r in range(self.world):
+                if self._get(f"{self.prefix}/left/{r}") is not None:
+                    left.append(r)
+                    continue
+                v = self._get(f"{self.prefix}/step/{r}")
+                if v is None or int(v) < int(step):
+                    missing.append(r)
+            if left:
+                raise RankLeft(left, step)
+            if not missing:
+                return
+            if time.monotonic() >= deadline:
+                raise RankLeft(missing, step)
+            time.sleep(poll_s)
 
 
 def row_shards(m, world):

@@ -1,4 +1,4 @@
-"""The branch-free erf of the tensor-core epilogue (erf_nodiv in picograd_b200/csrc/gemm_tc.cu) checked on the CPU.
+"""The branch-free erf of the tensor-core epilogue (erf_nodiv in picograd_b200/csrc/fast_math.cuh) checked on the CPU.
 
     erf(a) = sign(a) * (1 - 2^(t * Q(t))),   t = min(|a|, 4)
 
@@ -14,7 +14,7 @@ import re
 import numpy as np
 from scipy.special import erf, erfc
 
-SRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "picograd_b200", "csrc", "gemm_tc.cu")
+SRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "picograd_b200", "csrc", "fast_math.cuh")
 
 
 def coefficients_in_source():
