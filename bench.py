@@ -473,7 +473,7 @@ def run_other_config(args, rank, world):
         ad, bd = to_dev(a, wl.F32), to_dev(b, wl.F32)
         fn = lambda: pg.pg_matmul(ad, bd)
         flops, byts, name, dt = 2.0 * 512 ** 3, 3 * 512 * 512 * 4, "pg_matmul f32 512^3", "f32"
-        bound, profile = "launch", "simt_gemm_kernel_f32_512.md"
+        bound, profile = "launch", "sgemm_nn_pipe_kernel_f32_512.md"
     elif cfg == "square":
         n = args.size
         a, b = wl.config2(n, n, n)
