@@ -493,6 +493,8 @@ def run_other_config(args, rank, world):
         flops, byts, name = 2.0 * m * n * k, (m * k + k * n) * 2 + m * n * 4, f"pg_gemm_ex {dt} {m}x{n}x{k}"
         if cfg == "3b":
             bound, profile = "hbm", "tc_gemm_kernel_f16_16x4096x4096.md"
+        if cfg == "shard8":
+            profile = "tc_gemm_kernel_bf16_8192x1024x8192.md"
     elif cfg in ("4", "4-fused"):
         q, kt, v = wl.config4()
         b0, bc = sharding.batch_shards(64, world)[rank]
