@@ -367,7 +367,8 @@ def run_ours(args, rank, world):
         e2e_s = float(t.item())
     e2e_tflops = FLOPS / e2e_s / 1e12
     # the host-buffer result against the device-resident one: same bits when both products take the same K order
-    # per element (always at one GPU), else the normwise difference (rounding of a shared tail tile's two slices)
+    # per element (option k_serpentine = 0), else the normwise difference (the strips of the staged product and
+    # the resident product each sum K up or down by their own tile walk: rounding only)
     step()
     torch.cuda.synchronize()
     same = bool(torch.equal(c_dev[:64].cpu(), c_host[:64]))

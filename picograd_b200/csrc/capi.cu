@@ -40,6 +40,7 @@ struct State {
     int opt_splits = 0;
     int opt_f32_parts = 2;   // bf16 pieces an f32 operand is split into when paired with a 16-bit one
     int opt_f32_tc = 0;      // 1: f32 x f32 on the tensor cores as 3 bf16 pieces each (6 passes)
+    int opt_f32_chunk = 512; // that route adds K into C in chunks of this many elements (0: one accumulation)
     int opt_host_pipeline = 1;   // host-pointer pg_gemm_ex: overlap copies and GEMMs block by block
     int opt_fused_splitk = 1;    // split-K slices summed by the GEMM kernel itself (else a second kernel)
     int opt_attn_q_tmem = 1;     // attention kernel: Q copied to tensor memory once per unit and read from there (0: from shared memory)
@@ -53,6 +54,8 @@ struct State {
                                  // of the busiest SM pair by 10 % (8192x1024x8192: 160 k -> 143 k) and the clock under
                                  // the power limit falls by as much (1.52 -> 1.39 GHz): same time to within 1 %
     int opt_pdl = 1;             // programmatic dependent launch of the tensor-core kernels
+    int opt_k_serpentine = 1;    // a CTA's odd-numbered tiles run K downwards
+    int opt_serpentine = 1;      // odd rasterisation groups walk N downwards
     int opt_die_aware = 1;       // large products: each die of the B200 walks its own half of every rasterisation group
     int opt_swap_skinny = 1;     // M <= 32: multiply with swapped operands (C^T = B^T A^T), narrow tiles
     int opt_l2_hints = 0;    // see TcParams::l2_hints
@@ -277,6 +280,8 @@ static int run_tc(const Problem &p) {
     t.allow_stream_k = g.opt_stream_k && !p.no_split_k;
     if (g.opt_die_aware) { t.die_table = g.die_table; t.die_claim = g.die_claim; }
     t.pdl = g.opt_pdl;
+    t.serpentine = g.opt_serpentine;
+    t.k_serpentine = g.opt_k_serpentine;
     t.cluster_splitk = g.opt_cluster_splitk;
     t.counters = g.counters; t.num_counters = g.num_counters;
 
@@ -439,9 +444,16 @@ static int run_tc(const Problem &p) {
             t.accumulate = 0;
         }
     }
-    // Bias and activation ride in the kernel's epilogue when every tile holds finished sums; K-slices
-    // and the swapped route finish C first and one elementwise pass follows.
-    const bool epi_in_kernel = p.has_epilogue() && splits == 1 && !swap;
+    // f32 x f32 in pieces: the tensor cores add into their f32 accumulator without rounding to nearest,
+    // so the error of one long accumulation grows in proportion to K.  K therefore goes in chunks: each
+    // chunk is accumulated in tensor memory from zero and added to C in f32 (round to nearest) by the
+    // store, one launch per chunk in stream order, which keeps the result deterministic.
+    const size_t chunk = (size_t)g.opt_f32_chunk;
+    const bool chunked = p.dtype_a == DT_F32 && p.dtype_b == DT_F32 && npa > 1 && npb > 1 && chunk >= 64 &&
+                         chunk % 64 == 0 && p.k > chunk && splits == 1 && !swap;
+    // Bias and activation ride in the kernel's epilogue when every tile holds finished sums; K-slices,
+    // K-chunks and the swapped route finish C first and one elementwise pass follows.
+    const bool epi_in_kernel = p.has_epilogue() && splits == 1 && !swap && !chunked;
     if (epi_in_kernel) { t.bias = p.bias; t.act = p.act; t.c16 = p.c16; t.ld16 = p.ld16; t.dtype16 = p.dtype16; t.act_copy_only = p.act_copy_only; }
     if (swap) {
         // A' = B (its N runs along the tile rows), B' = A, tile stored transposed into the same C
@@ -453,6 +465,20 @@ static int run_tc(const Problem &p) {
         t.force_cfg = p.m <= 16 ? tc_config_index("1cta_128x16_t") : tc_config_index("1cta_128x32_t");
     }
     if (g.opt_path != 1 && !tc_gemm_supported(t)) return ST_UNSUPPORTED;
+    if (chunked) {
+        const char *a0 = (const char *)t.A.ptr, *b0 = (const char *)t.B.ptr;
+        for (size_t k0 = 0; k0 < p.k; k0 += chunk) {
+            t.K = (uint32_t)(p.k - k0 < chunk ? p.k - k0 : chunk);
+            t.A.ptr = a0 + 2 * (t.A.mn_major ? k0 * t.A.ld : k0);      // pieces are 16-bit
+            t.B.ptr = b0 + 2 * (t.B.mn_major ? k0 * t.B.ld : k0);
+            t.accumulate = k0 ? 1 : p.accumulate;
+            int st = tc_gemm_launch(t);
+            if (st != ST_OK) return st;
+        }
+        if (p.has_epilogue())
+            return bias_act_launch(p.c, p.ldc, p.bias, p.act, p.act_copy_only, p.c16, p.ld16, p.dtype16, p.m, p.n, g.stream);
+        return ST_OK;
+    }
     int st = tc_gemm_launch(t);
     if (st == ST_UNSUPPORTED && fused) {           // more slabs than counters: fall back to the two-kernel form
         fused = false;
@@ -1049,6 +1075,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "k_splits")) { g.opt_splits = value; return ST_OK; }
     if (!strcmp(name, "f32_parts")) { if (value != 2 && value != 3) return ST_UNSUPPORTED; g.opt_f32_parts = value; return ST_OK; }
     if (!strcmp(name, "f32_tensor_cores")) { g.opt_f32_tc = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "f32_chunk")) { if (value < 0 || value % 64) return ST_UNSUPPORTED; g.opt_f32_chunk = value; return ST_OK; }
     if (!strcmp(name, "stages")) { g.opt_stages = value; return ST_OK; }
     if (!strcmp(name, "l2_promotion")) { if (value < 0 || value > 3) return ST_UNSUPPORTED; g_l2_promotion = value; return ST_OK; }
     if (!strcmp(name, "l2_hints")) { g.opt_l2_hints = value; return ST_OK; }
@@ -1062,6 +1089,8 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "small_f32_pipe")) { g_small_f32_pipe = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "k_serpentine")) { g.opt_k_serpentine = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "serpentine")) { g.opt_serpentine = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "die_aware")) { g.opt_die_aware = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "pdl")) { g.opt_pdl = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "debug")) { g.opt_debug = value; return ST_OK; }

@@ -69,6 +69,8 @@ struct TcGemm {
     int stages;                // 0 = all the configuration has; else use this many smem stages
     int l2_hints;              // L2 eviction priorities of the bulk copies (see TcParams::l2_hints)
     int group_m;               // 0 = choose; else M tiles per rasterisation group
+    int serpentine;            // 1: odd rasterisation groups walk N downwards
+    int k_serpentine;          // 1: a CTA's odd-numbered tiles run K downwards
     int debug;                 // timing experiments: 1 = no TMA loads, 2 = no C stores (results are garbage)
     cudaStream_t stream;
     uint32_t *dev_status;      // device status word

@@ -40,7 +40,20 @@ def test_config2_bf16_8192(pg, oracle):
     assert pg.last_path().startswith("tc:2cta")
     _panels(oracle, wl.BF16, a, b, c, 8192)
     assert freivalds(c, ad.double(), bd.double()) < wl.tolerance(wl.BF16, 8192) / 10
-    # every tile configuration must produce the same product (same K order per element)
+    # by default a CTA's odd-numbered tiles sum K downwards (a wave starts on the K blocks the one before ended on):
+    # deterministic, launch after launch
+    assert pg.last_path().endswith(":k_up_down")
+    again = torch.empty_like(c)
+    pg.pg_gemm_ex(wl.BF16, 8192, 8192, 8192, ad, 8192, bd, 8192, again, 8192)
+    pg.pg_dev_sync()
+    assert torch.equal(c, again)
+    # with K ascending everywhere every tile configuration must produce the same product (same K order per element)
+    pg.set_option("k_serpentine", 0)
+    pg.pg_gemm_ex(wl.BF16, 8192, 8192, 8192, ad, 8192, bd, 8192, c, 8192)
+    pg.pg_dev_sync()
+    assert "k_up_down" not in pg.last_path()
+    assert 0 < wl.relerr(again.cpu().numpy(), c.cpu().numpy()) <= wl.tolerance(wl.BF16, 8192) / 10
+    _panels(oracle, wl.BF16, a, b, c, 8192)
     for cfg in (0, 1, 4):
         pg.set_option("tile_config", cfg)
         c2 = torch.empty_like(c)

@@ -93,6 +93,38 @@ def test_f32_on_tensor_cores_within_1e6(pg, oracle):
     assert wl.relerr(got, want) <= 1e-6
 
 
+def test_f32_on_tensor_cores_long_k_goes_in_chunks(pg, oracle):
+    """The tensor cores add into their f32 accumulator without rounding to nearest, so one long accumulation drifts
+    in proportion to K.  The f32 route therefore accumulates K in chunks of 512 and adds each chunk to C in f32: its
+    distance to the exact product stays below 5e-7 at every K — closer than the one-chain f32 result itself, which
+    is why beyond K of a few thousand it cannot also stay within 1e-6 of that chain."""
+    m, n, k = 256, 384, 8192
+    rng = np.random.default_rng(5)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    chain = oracle.gemm_ex(wl.F32, a, b)
+    pg.set_option("f32_tensor_cores", 1)
+    got = gemm_dev(pg, wl.F32, a, b)
+    assert pg.last_path().startswith("tc:")
+    e_tc, e_chain = wl.relerr(got, exact), wl.relerr(chain, exact)
+    assert e_tc <= 5e-7 and e_tc < e_chain, (e_tc, e_chain)
+    assert wl.relerr(got, chain) <= 2.5e-6
+    pg.set_option("f32_chunk", 0)                    # one accumulation over all of K
+    assert wl.relerr(gemm_dev(pg, wl.F32, a, b), exact) > 4 * e_tc
+    pg.set_option("f32_chunk", 512)
+    # bias + activation after the last chunk, ragged K (last chunk shorter)
+    k2 = 1000
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    ad, bd, biasd = to_dev(a[:, :k2].copy(), wl.F32), to_dev(b[:k2].copy(), wl.F32), to_dev(bias, wl.F32)
+    c = torch.empty((m, n), device="cuda")
+    pg.pg_gemm_fused(m, n, k2, ad, k2, bd, n, c, n, bias=biasd, act=pg.PG_ACT_RELU)
+    pg.pg_dev_sync()
+    assert pg.last_path().startswith("tc:")
+    want = oracle.gemm_fused_ex(wl.F32, a[:, :k2].copy(), b[:k2].copy(), bias, pg.PG_ACT_RELU)
+    assert wl.relerr(to_host(c), want) <= 1e-6
+
+
 @pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
 def test_against_reference_outputs(pg, case):
     """The committed outputs of the unmodified picograd CPU library."""
