@@ -275,7 +275,14 @@ PG_B200_API const char *pg_b200_last_error(void);
 /* Tuning / test hooks: kernel path 0 = choose, 1 = tensor-core kernel only
  * (UNSUPPORTED if it cannot take the shape), 2 = FFMA kernel only;
  * tile configuration index (-1 = choose) and its name; epilogue -1 = choose,
- * 0 = direct stores, 1 = TMA stores; K splits 0 = choose. */
+ * 0 = direct stores, 1 = TMA stores; K splits 0 = choose.
+ * Two options change results within the stated tolerance:
+ *   "k_serpentine" (default 1): large products sum K upwards in a CTA's even-numbered tiles and downwards
+ *     in its odd-numbered ones (fewer DRAM reads).  Deterministic for a shape; set 0 when results must be
+ *     bit-identical across shapes, shards or tile configurations (every element then sums K ascending).
+ *   "f32_tensor_cores" (default 0): f32 x f32 as three exact bf16 pieces per operand on the tensor cores,
+ *     K accumulated in chunks of "f32_chunk" (default 512; 0 = one accumulation) that are added to C in f32.
+ *     Closer to the exact product than one f32 chain, hence not bit-identical to picograd's CPU result. */
 PG_B200_API int pg_b200_set_option(const char *name, int value);
 PG_B200_API int pg_b200_num_tile_configs(void);
 PG_B200_API const char *pg_b200_tile_config_name(int index);
