@@ -966,7 +966,8 @@ int pg_b200_conv2d(size_t n, size_t cin, size_t h, size_t w, size_t cout, size_t
         st = bias_rows_launch(out, bias, (uint32_t)cout, n * cout, ncols, g.stream);
         if (st != ST_OK) return st;
     }
-    set_last_path("conv:im2col+simt");
+    // f32 x f32: the one-chain FFMA kernels unless the caller chose the tensor-core route (option f32_tensor_cores)
+    set_last_path(!strncmp(g.last_path, "tc:", 3) ? "conv:im2col+tc" : "conv:im2col+simt");
     return ST_OK;
 }
 

@@ -45,6 +45,22 @@ def test_larger_shapes_bit_exact(pg, oracle, shape):
     assert np.array_equal(y.cpu().numpy(), oracle.conv2d(x, wt, b, s, p))
 
 
+def test_tensor_core_route_by_option(pg, oracle):
+    """With option f32_tensor_cores the convolution's GEMM takes the f32 tensor-core route (three exact bf16 pieces per
+    operand, K in chunks): no longer the CPU's bits, within the f32 tolerance of them."""
+    n, cin, h, w, cout, kh, kw, s, p = 4, 64, 56, 56, 128, 3, 3, 1, 1
+    rng = np.random.default_rng(71)
+    x = rng.uniform(-1, 1, (n, cin, h, w)).astype(np.float32)
+    wt = rng.uniform(-1, 1, (cout, cin, kh, kw)).astype(np.float32)
+    b = rng.uniform(-1, 1, cout).astype(np.float32)
+    pg.set_option("f32_tensor_cores", 1)
+    y = pg.pg_conv2d(dev(x), dev(wt), dev(b), stride=s, padding=p); pg.pg_dev_sync()
+    assert pg.last_path() == "conv:im2col+tc"
+    want = oracle.conv2d(x, wt, b, s, p)
+    got = y.cpu().numpy()
+    assert np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64)) <= 1e-6
+
+
 def test_rejects_what_pg_conv2d_rejects(pg):
     x = torch.zeros(1, 2, 4, 4, device="cuda")
     with pytest.raises(ValueError):
