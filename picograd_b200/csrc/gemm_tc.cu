@@ -474,8 +474,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int32_t n0 = (int32_t)(w.n_blk * BN + cta_rank * C_::BN_CTA);
             const uint32_t rounds = (w.kb_count + SUB - 1) / SUB;
             for (uint32_t pass = 0; pass < passes.n && ok; ++pass) {
-                const int32_t za = (int32_t)(w.batch * p.a_nparts + ((passes.a_sel >> (4 * pass)) & 0xF));
-                const int32_t zb = (int32_t)(w.batch * p.b_nparts + ((passes.b_sel >> (4 * pass)) & 0xF));
+                // a unit that runs K downwards also takes its passes last to first: it begins on the very
+                // blocks (same pieces, same K) the unit before it ended on
+                const uint32_t ps = w.k_down ? passes.n - 1 - pass : pass;
+                const int32_t za = (int32_t)(w.batch * p.a_nparts + ((passes.a_sel >> (4 * ps)) & 0xF));
+                const int32_t zb = (int32_t)(w.batch * p.b_nparts + ((passes.b_sel >> (4 * ps)) & 0xF));
                 for (uint32_t r = 0; r < rounds; ++r) {
                     long long c0 = prof ? clock64() : 0;
                     ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, DEV_ERR_WAIT_EMPTY);
