@@ -300,6 +300,14 @@ PG_B200_API int pg_b200_debug_counters(uint64_t *out, size_t count);
  * tile, first K block, number of K blocks (0 = no such part), role (1 = first slice: stored, 2 = second slice: added)}. */
 PG_B200_API int pg_b200_debug_tail_schedule(uint64_t tiles, unsigned slots, unsigned k_blocks, unsigned cluster,
                                             unsigned part, unsigned out[6]);
+/* Test hook (host arithmetic only, needs no GPU): the i-th output tile that CTA pair `id` of `count` takes in a
+ * product of m_tiles x n_tiles tiles walked in rasterisation groups of `group_m` M tiles, by the function the
+ * kernel's roles call.  die_aware: the pair is number `id` of `count` on die `die` and walks that die's half of every
+ * group; serpentine: odd groups walk N downwards; k_serpentine: a pair's odd-numbered tiles fetch their K blocks last
+ * to first.  out = {1 if there is such a tile, M tile, N tile, 1 if K runs downwards}. */
+PG_B200_API int pg_b200_debug_walk(unsigned m_tiles, unsigned n_tiles, unsigned group_m, unsigned k_blocks,
+                                   unsigned die_aware, unsigned serpentine, unsigned k_serpentine, unsigned die,
+                                   unsigned id, unsigned count, unsigned i, unsigned out[4]);
 /* Diagnostic: the table smid -> die (0 / 1) that pg_b200_init measured on this GPU (L2 hit latency from every SM to
  * one address: the SMs of the die that holds the line answer ~70 cycles sooner) and that the die-aware tile walk of
  * the tensor-core GEMM uses; up to 256 entries.  PG_ERR_UNSUPPORTED when the SMs did not fall into two clean groups

@@ -63,6 +63,7 @@ SIGNATURES = {
     "pg_b200_die_table": (_i, [_vp, _sz]),
     "pg_b200_debug_counters": (_i, [_vp, _sz]),
     "pg_b200_debug_tail_schedule": (_i, [C.c_uint64, C.c_uint, C.c_uint, C.c_uint, C.c_uint, _vp]),
+    "pg_b200_debug_walk": (_i, [C.c_uint] * 11 + [_vp]),
     "pg_b200_selftest_wait_timeout": (_i, [C.c_uint]),
 }
 

@@ -1062,6 +1062,12 @@ int pg_b200_debug_tail_schedule(uint64_t tiles, unsigned slots, unsigned k_block
     return tc_tail_schedule(tiles, slots, k_blocks, cluster, part, out);
 }
 
+int pg_b200_debug_walk(unsigned m_tiles, unsigned n_tiles, unsigned group_m, unsigned k_blocks, unsigned die_aware,
+                       unsigned serpentine, unsigned k_serpentine, unsigned die, unsigned id, unsigned count, unsigned i,
+                       unsigned out[4]) {
+    return tc_walk_unit(m_tiles, n_tiles, group_m, k_blocks, die_aware, serpentine, k_serpentine, die, id, count, i, out);
+}
+
 const char *pg_b200_last_error(void) { return g.err; }
 const char *pg_b200_last_path(void) { return g.last_path; }
 uint64_t pg_b200_launch_count(void) { return g.launches; }

@@ -147,7 +147,7 @@ struct WorkUnit {
     uint32_t k_down;      // the producer fetches this unit's K blocks last to first
 };
 
-__device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
+__host__ __device__ __forceinline__ WorkUnit decode_unit(const TcParams &p, uint32_t u) {
     WorkUnit w;
     uint32_t t = u / p.splits;
     w.split = u - t * p.splits;
@@ -205,7 +205,7 @@ __host__ __device__ inline bool tail_part(uint32_t q, uint32_t r, uint32_t KB, u
     else { kb_begin = split; kb_count = KB - split; role = 2; }
     return true;
 }
-__device__ __noinline__ bool tail_unit(const TcParams &p, uint32_t c, uint32_t S, uint32_t j, WorkUnit &w) {
+__host__ __device__ __noinline__ bool tail_unit(const TcParams &p, uint32_t c, uint32_t S, uint32_t j, WorkUnit &w) {
     uint32_t tile, kb_begin, kb_count, role;
     if (!tail_part(p.sk_q, p.sk_r, p.k_blocks, c, j, tile, kb_begin, kb_count, role)) return false;
     w = decode_unit(p, p.sk_full * S + tile);
@@ -217,7 +217,7 @@ __device__ __noinline__ bool tail_unit(const TcParams &p, uint32_t c, uint32_t S
 // same sequence.
 struct Walk { uint32_t id, count, die; };    // this CTA pair's position: id of count (on its die when die-aware)
 
-__device__ __forceinline__ bool get_unit(const TcParams &p, const Walk &wk, uint32_t total_units, uint32_t i, WorkUnit &w) {
+__host__ __device__ __forceinline__ bool get_unit(const TcParams &p, const Walk &wk, uint32_t total_units, uint32_t i, WorkUnit &w) {
     if (p.die_table) {
         // this die's half of every group: h = group_m / 2 M-tiles x n_tiles, M fastest
         const uint32_t h = p.group_m >> 1, per_g = h * p.n_tiles;
@@ -1209,6 +1209,26 @@ int tc_tail_schedule(uint64_t tiles, uint32_t slots, uint32_t k_blocks, uint32_t
     out[0] = 1; out[1] = full;
     uint32_t tile, b, n, role;
     if (tail_part(q, r, k_blocks, c, j, tile, b, n, role)) { out[2] = tile; out[3] = b; out[4] = n; out[5] = role; }
+    return ST_OK;
+}
+
+// The i-th unit of CTA pair `id` of `count` (on die `die` when the walk is die-aware), by the function the kernel's
+// roles call: out = {1 if there is one, M tile, N tile, 1 if its K blocks are fetched last to first}.
+int tc_walk_unit(uint32_t m_tiles, uint32_t n_tiles, uint32_t group_m, uint32_t k_blocks, uint32_t die_aware, uint32_t serpentine,
+                 uint32_t k_serpentine, uint32_t die, uint32_t id, uint32_t count, uint32_t i, uint32_t out[4]) {
+    for (int j = 0; j < 4; ++j) out[j] = 0;
+    if (!m_tiles || !n_tiles || !group_m || !count || id >= count) return ST_UNSUPPORTED;
+    if (die_aware && (group_m % 2 || m_tiles % group_m || die > 1)) return ST_UNSUPPORTED;
+    TcParams p = {};
+    p.batch = 1; p.splits = 1; p.m_tiles = m_tiles; p.n_tiles = n_tiles; p.group_m = group_m;
+    p.k_blocks = k_blocks; p.kb_per_split = k_blocks;
+    p.serpentine = serpentine ? 1u : 0u; p.k_serpentine = k_serpentine ? 1u : 0u;
+    static const unsigned char some_table[1] = {0};
+    if (die_aware) p.die_table = some_table;          // only its presence selects the walk
+    Walk wk = {id, count, die};
+    WorkUnit w;
+    if (!get_unit(p, wk, m_tiles * n_tiles, i, w)) return ST_OK;
+    out[0] = 1; out[1] = w.m_blk; out[2] = w.n_blk; out[3] = w.k_down;
     return ST_OK;
 }
 

@@ -85,6 +85,8 @@ bool tc_gemm_supported(const TcGemm &g);
 int wait_timeout_selftest_launch(uint32_t *status, unsigned limit_ms, cudaStream_t stream);
 extern int g_l2_promotion;   // CUtensorMapL2promotion of the operand tensor maps
 int tc_tail_schedule(uint64_t tiles, uint32_t slots, uint32_t k_blocks, uint32_t c, uint32_t j, uint32_t out[6]);
+int tc_walk_unit(uint32_t m_tiles, uint32_t n_tiles, uint32_t group_m, uint32_t k_blocks, uint32_t die_aware, uint32_t serpentine,
+                 uint32_t k_serpentine, uint32_t die, uint32_t id, uint32_t count, uint32_t i, uint32_t out[4]);
 // topology.cu: measures which SMs share a die; false when the SMs do not fall into two clean groups
 bool measure_die_table(unsigned char table[256], cudaStream_t stream);
 int tc_num_configs();
