@@ -117,6 +117,26 @@ PG_B200_API int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int 
                          const void *b, size_t ldb, size_t stride_b,
                          float *c, size_t ldc, size_t stride_c, int accumulate);
 
+/* A column shard of C written into the full C of several devices by the GEMM kernel itself (no counterpart in
+ * picograd, which has one device).  The product is pg_b200_gemm_ex's: C_shard (m x n, f32) = A (m x k) * B (k x n);
+ * every tile of it is stored to dst[i] + col0 for i = 0 .. n_dst-1, each dst[i] the base of a row-major m x ldc
+ * f32 matrix: this device's own full C and, typically, the other devices' full C mapped into this process
+ * (pg_b200_ipc_open).  After every rank of an N-column-sharded product has made this call and the ranks have met
+ * (stream synchronisation on each, then a barrier among the processes), every device holds all of C in row-major
+ * order: no all-gather, no re-layout pass, and the transfer over NVLink overlaps the product tile by tile.
+ * f16 / bf16 only; 1 to 8 destinations; col0, n and ldc multiples of 4, destinations 16-byte aligned (the stores
+ * are TMA bulk stores); PG_ERR_UNSUPPORTED otherwise — the caller then gathers with NCCL.  The kernel only
+ * stores to the other devices and waits for none of them. */
+PG_B200_API int pg_b200_gemm_ex_scatter(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda,
+                                        const void *b, size_t ldb, float *const *dst, size_t n_dst, size_t ldc,
+                                        size_t col0);
+/* One process per GPU: handle of a pg_b200_malloc allocation for another process (cudaIpcGetMemHandle, 64
+ * bytes), and the mapping of such a handle into this process with peer access enabled (cudaIpcOpenMemHandle).
+ * pg_b200_ipc_close unmaps; the owner frees its allocation only after every process has closed it. */
+PG_B200_API int pg_b200_ipc_export(const void *dev_ptr, unsigned char handle[64]);
+PG_B200_API int pg_b200_ipc_open(const unsigned char handle[64], void **dev_ptr);
+PG_B200_API int pg_b200_ipc_close(void *dev_ptr);
+
 /* pg_addmm (ops/matmul.c:371-405): c = beta * input + alpha * (a * b).  a [m,k], b [k,n] in `dtype`; c f32 [m,n];
  * input f32 read at input[i * in_row_stride + j * in_col_stride] (strides in elements, 0 = broadcast along that
  * dimension, so [m,n], [n], [m,1] and scalars all fit).  The product is pg_matmul's; the tail is one kernel that

@@ -8,5 +8,5 @@ from .backend import (  # noqa: F401
     PG_ACT_COPY_ONLY, PG_ACT_GELU, PG_ACT_NONE, PG_ACT_RELU, PG_DTYPE_BF16, PG_DTYPE_F16, PG_DTYPE_F32, PG_OK, PgError,
     pg_addmm, pg_attention_bmm, pg_conv2d, pg_gemm_fused, pg_gemm_fused_ex, pg_linear_forward,
     pg_bgemm, pg_bmm, pg_dev_sync, pg_gemm, pg_gemm_ex, pg_gemm_ex_host, pg_hgemm, pg_matmul,
-    pg_gather_relayout, pg_matmul_backward, pg_matmul_backward_act, pg_set_device, pg_tensordot, last_path, launch_count, set_option,
+    pg_gather_relayout, pg_gemm_ex_scatter, pg_matmul_backward, pg_matmul_backward_act, pg_set_device, pg_tensordot, last_path, launch_count, set_option,
 )

@@ -63,6 +63,10 @@ SIGNATURES = {
     "pg_b200_die_table": (_i, [_vp, _sz]),
     "pg_b200_debug_counters": (_i, [_vp, _sz]),
     "pg_b200_debug_tail_schedule": (_i, [C.c_uint64, C.c_uint, C.c_uint, C.c_uint, C.c_uint, _vp]),
+    "pg_b200_gemm_ex_scatter": (_i, [_i, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz]),
+    "pg_b200_ipc_export": (_i, [_vp, _vp]),
+    "pg_b200_ipc_open": (_i, [_vp, _vp]),
+    "pg_b200_ipc_close": (_i, [_vp]),
     "pg_b200_debug_walk": (_i, [C.c_uint] * 11 + [_vp]),
     "pg_b200_selftest_wait_timeout": (_i, [C.c_uint]),
 }

@@ -313,6 +313,17 @@ def pg_gather_relayout(staging, full, shards, rows, width, n):
            "pg_b200_gather_relayout")
 
 
+def pg_gemm_ex_scatter(dtype, m, n, k, a, lda, b, ldb, dst_ptrs, ldc, col0):
+    """The column shard C[:, col0:col0+n] = A * B written by the GEMM kernel itself into every full C in `dst_ptrs`
+    (device addresses of row-major m x ldc f32 matrices: this device's and, mapped with PeerMatrix, the other
+    devices').  No counterpart in picograd.  PgError(UNSUPPORTED) when the shard cannot go through TMA stores."""
+    _ready()
+    import ctypes
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[int(x) for x in dst_ptrs])
+    _check(lib.pg_b200_gemm_ex_scatter(dtype, m, n, k, a.data_ptr(), lda, b.data_ptr(), ldb, arr, len(dst_ptrs), ldc, col0),
+           "pg_b200_gemm_ex_scatter")
+
+
 def _permute_copy(t, perm):
     """permute_copy (ops/matmul.c:21-42) with the library's own kernel: a new contiguous tensor whose dimension d
     is dimension perm[d] of t."""

@@ -230,6 +230,8 @@ struct Problem {
     int dtype16 = DT_BF16;
     int act_copy_only = 0;       // the activation goes into c16 only; C keeps bias + A*B
     int no_split_k = 0;          // every element keeps the K order of the unsplit product (staged pieces of a large one)
+    float *extra_c[7] = {};      // further destinations of C (same ldc), e.g. other devices' full C
+    uint32_t n_extra = 0;
     bool has_epilogue() const { return bias != nullptr || act != 0 || c16 != nullptr; }
 };
 
@@ -273,6 +275,8 @@ static int run_tc(const Problem &p) {
     t.npass = 1; t.a_sel = 0; t.b_sel = 0;
     t.C = p.c; t.ldc = p.ldc; t.c_stride = p.stride_c;
     t.accumulate = p.accumulate;
+    t.n_extra = p.n_extra;
+    for (uint32_t d = 0; d < p.n_extra && d < 7; ++d) t.extra_c[d] = p.extra_c[d];
     t.splits = 1;
     t.force_cfg = g.opt_cfg; t.force_epilogue = g.opt_epilogue;
     t.stages = g.opt_stages; t.debug = g.opt_debug; t.l2_hints = g.opt_l2_hints; t.group_m = g.opt_group_m;
@@ -325,11 +329,11 @@ static int run_tc(const Problem &p) {
     // 128 tensor-memory lanes and M becomes a 16- or 32-wide UMMA N: a stage then holds 16 KB of B and
     // only 2-4 KB of A (12 stages in flight), and the transposed store is coalesced.
     const bool swap = g.opt_swap_skinny && g.opt_cfg < 0 && !mixed && p.batch == 1 && !p.trans_a && p.m <= 32 &&
-                      p.n >= 256;
+                      p.n >= 256 && !p.n_extra;
     // split-K for shapes that would leave most SMs idle
     uint32_t splits = 1;
     const uint32_t k_blocks = (uint32_t)((p.k + 63) / 64);
-    if (p.batch == 1 && npa == 1 && npb == 1 && !p.no_split_k) {
+    if (p.batch == 1 && npa == 1 && npb == 1 && !p.no_split_k && !p.n_extra) {
         if (g.opt_splits > 0) {
             splits = (uint32_t)g.opt_splits;
         } else {
@@ -515,6 +519,10 @@ static int run_problem(const Problem &p) {
         int st = run_tc(p);
         if (st == ST_OK) return ST_OK;
         if (st != ST_UNSUPPORTED || g.opt_path == 1) return st;
+    }
+    if (p.n_extra) {
+        set_error("several destinations of C: only the tensor-core route with a TMA-storable C takes them");
+        return ST_UNSUPPORTED;
     }
     return run_simt(p);
 }
@@ -1060,6 +1068,51 @@ int pg_b200_selftest_wait_timeout(unsigned limit_ms) {
 int pg_b200_debug_tail_schedule(uint64_t tiles, unsigned slots, unsigned k_blocks, unsigned cluster, unsigned part,
                                  unsigned out[6]) {
     return tc_tail_schedule(tiles, slots, k_blocks, cluster, part, out);
+}
+
+int pg_b200_gemm_ex_scatter(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda, const void *b, size_t ldb,
+                            float *const *dst, size_t n_dst, size_t ldc, size_t col0) {
+    if (!ready()) return g.init_status;
+    if (dtype != DT_F16 && dtype != DT_BF16) { set_error("pg_b200_gemm_ex_scatter: f16 or bf16 operands"); return ST_UNSUPPORTED; }
+    if (!dst || n_dst == 0 || n_dst > 8) { set_error("pg_b200_gemm_ex_scatter: 1 to 8 destinations"); return ST_UNSUPPORTED; }
+    if (m == 0 || n == 0) return ST_OK;
+    if (col0 % 4 || ldc % 4 || n % 4 || col0 + n > ldc) {
+        set_error("pg_b200_gemm_ex_scatter: col0, n and ldc must be multiples of 4 and the shard must lie inside a row of C");
+        return ST_UNSUPPORTED;
+    }
+    for (size_t d = 0; d < n_dst; ++d)
+        if (!dst[d]) { set_error("null destination"); return ST_GEMM; }
+    Problem p = {dtype, dtype, 0, 0, 1, m, n, k, a, lda, 0, b, ldb, 0, dst[0] + col0, ldc, 0, 0};
+    p.n_extra = (uint32_t)(n_dst - 1);
+    for (size_t d = 1; d < n_dst; ++d) p.extra_c[d - 1] = dst[d] + col0;
+    return run_problem(p);
+}
+
+int pg_b200_ipc_export(const void *dev_ptr, unsigned char handle[64]) {
+    if (!ready()) return g.init_status;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr));
+    if (e != cudaSuccess) { set_error("cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_UNSUPPORTED; }
+    memcpy(handle, &h, 64);
+    return ST_OK;
+}
+
+int pg_b200_ipc_open(const unsigned char handle[64], void **dev_ptr) {
+    if (!ready()) return g.init_status;
+    if (!dev_ptr) return ST_UNSUPPORTED;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { *dev_ptr = nullptr; set_error("cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_UNSUPPORTED; }
+    return ST_OK;
+}
+
+int pg_b200_ipc_close(void *dev_ptr) {
+    if (!dev_ptr) return ST_OK;
+    cudaError_t e = cudaIpcCloseMemHandle(dev_ptr);
+    if (e != cudaSuccess) { set_error("cudaIpcCloseMemHandle failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return ST_UNSUPPORTED; }
+    return ST_OK;
 }
 
 int pg_b200_debug_walk(unsigned m_tiles, unsigned n_tiles, unsigned group_m, unsigned k_blocks, unsigned die_aware,

@@ -94,6 +94,7 @@ struct TcParams {
     uint32_t a_mn, b_mn;          // operand is MN-major in memory
     uint32_t idesc;               // tcgen05 instruction descriptor
     uint32_t group_m;             // M tiles per rasterisation group
+    uint32_t n_extra;             // further destinations of every C tile (tensor maps in the ExtraMaps argument)
     uint32_t serpentine;          // odd groups walk N downwards: the B panels a group ends on are the next one's first
     uint32_t k_serpentine;        // a CTA's odd-numbered tiles run K downwards: the K blocks a wave ends on are the next one's first
     uint32_t epilogue_tma;        // 1: TMA-store epilogue, 0: direct stores
@@ -363,10 +364,13 @@ __device__ __forceinline__ PassList effective_passes(const TcParams &p) {
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
+// Tensor maps of the further destinations of C (TcParams::n_extra of them are valid).
+struct ExtraMaps { CUtensorMap m[7]; };
+
 template <int CG, int BN, int SUB, bool STAGING, int EW, int EB>
 __global__ void __launch_bounds__(32 * (2 + EW), 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, const TcParams p) {
+               const __grid_constant__ CUtensorMap map_c, const TcParams p, const __grid_constant__ ExtraMaps extra) {
     using C_ = Cfg<CG, BN, SUB, STAGING, EW, EB>;
     constexpr uint32_t EPI_WARPS = EW, EPI_BUFS = EB;
     constexpr uint32_t STAGES = C_::STAGES;     // allocated; p.stages of them are cycled through
@@ -847,6 +851,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         else   // a slab that a second slice will be added to should not leave L2 first
                             tma_store_3d(&map_c, my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc,
                                          w.role == 1 ? pol_keep : pol_c);
+                        // the same chunk to every further destination (other devices' C): one more bulk store each,
+                        // in the same group, so the buffer is reused only when all of them have read it
+                        for (uint32_t d = 0; d < p.n_extra; ++d)
+                            tma_store_3d(&extra.m[d], my_epi + buf * EPI_BUF_BYTES, (int32_t)col, (int32_t)row0, (int32_t)zc, pol_c);
                         tma_store_commit();
                     }
                     if (++buf == EPI_BUFS) buf = 0;
@@ -1345,11 +1353,28 @@ int tc_gemm_launch(const TcGemm &g) {
         mc = ma;  // unused by the kernel
     }
 
+    ExtraMaps extra = {};
+    if (g.n_extra) {
+        if (g.n_extra > 7 || !p.epilogue_tma || p.accumulate || p.splits > 1 || g.batch != 1) {
+            set_error("tc_gemm: further destinations of C need one product, no accumulate and a C that TMA can store "
+                      "(16-byte aligned base, ldc and N multiples of 4)");
+            return ST_UNSUPPORTED;
+        }
+        for (uint32_t d = 0; d < g.n_extra; ++d) {
+            if (!aligned16(g.extra_c[d])) { set_error("tc_gemm: destination %u of C is not 16-byte aligned", d + 1); return ST_UNSUPPORTED; }
+            TcGemm gd = g;
+            gd.C = g.extra_c[d];
+            st = encode_c(&extra.m[d], gd, zc);
+            if (st != ST_OK) return st;
+        }
+        p.n_extra = g.n_extra;
+    }
+
     const uint64_t units = (uint64_t)g.batch * p.m_tiles * p.n_tiles * p.splits;
     if (units > 0xFFFFFFFFull) return ST_UNSUPPORTED;
     uint32_t clusters = (uint32_t)(units < (uint64_t)rt.max_clusters ? units : (uint64_t)rt.max_clusters);
     bool stream_k = false;
-    if (g.allow_stream_k && !g.bias && !g.act && !g.c16 && p.splits == 1 && p.npass == 1 && !p.c_trans && p.epilogue_tma &&
+    if (g.allow_stream_k && !g.n_extra && !g.bias && !g.act && !g.c16 && p.splits == 1 && p.npass == 1 && !p.c_trans && p.epilogue_tma &&
         g.counters && !(kExperiments && (p.debug & 31u))) {
         uint32_t full = 0, q = 0, r = 0;
         const uint32_t slots = (uint32_t)rt.max_clusters;
@@ -1399,7 +1424,7 @@ int tc_gemm_launch(const TcGemm &g) {
         at[1].val.programmaticStreamSerializationAllowed = 1;
         lc.numAttrs = 2;
     }
-    void *args[4] = {(void *)&ma, (void *)&mb, (void *)&mc, (void *)&p};
+    void *args[5] = {(void *)&ma, (void *)&mb, (void *)&mc, (void *)&p, (void *)&extra};
     cudaError_t e = cudaLaunchKernelExC(&lc, c.fn, args);
     if (e != cudaSuccess) {
         set_error("launch %s failed: %s", c.name, cudaGetErrorString(e));
@@ -1407,9 +1432,11 @@ int tc_gemm_launch(const TcGemm &g) {
         return ST_GEMM;
     }
     note_launch();
-    set_last_path("tc:%s%s%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
+    char more[24] = "";
+    if (p.n_extra) snprintf(more, sizeof more, ":to%u", p.n_extra + 1);
+    set_last_path("tc:%s%s%s%s%s%s%s", c.name, p.epilogue_tma ? "" : ":direct", p.splits > 1 ? ":splitk" : "",
                   p.cluster_k ? ":cluster" : (p.Cout ? ":fused" : ""), stream_k ? ":balanced_tail" : (die_aware ? ":die_aware" : ""),
-                  p.k_serpentine ? ":k_up_down" : "");
+                  p.k_serpentine ? ":k_up_down" : "", more);
     return ST_OK;
 }
 

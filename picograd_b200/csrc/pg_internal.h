@@ -49,6 +49,11 @@ struct TcGemm {
     float *C;
     uint64_t ldc, c_stride;    // elements; c_stride between batch elements (or split-K slices)
     int accumulate;            // C += A*B instead of C = A*B
+    // Further destinations of C: every tile is stored to extra_c[i] as well (same M, N, ldc; one product, no
+    // accumulate, TMA-store epilogue only).  The pointers may be another device's memory mapped into this
+    // process: a column shard then lands in every device's full C without a collective afterwards.
+    float *extra_c[7];
+    uint32_t n_extra;
     // fused epilogue: C = act(A*B + bias[col]) and an optional 16-bit copy of C ([batch][M][ld16])
     const float *bias; int act; uint16_t *c16; uint64_t ld16; int dtype16;
     int act_copy_only;         // activation applied to the 16-bit copy only

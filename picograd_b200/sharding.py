@@ -9,9 +9,13 @@ no data-path collective:
     no reduction is needed.
   * pg_bmm: batch shards.
 
-Only when a caller wants the whole C on every rank is there an exchange: `gather_columns`, an
-all-gather of the column shards (NCCL over NVLink on GPUs, gloo on CPU in the tests) followed by a
-local re-layout, because column shards are not contiguous in a row-major matrix.
+Only when a caller wants the whole C on every rank is there an exchange, in one of two forms:
+
+  * `gather_columns`: an all-gather of the column shards (NCCL over NVLink on GPUs, gloo on CPU in the
+    tests) followed by a local re-layout, because column shards are not contiguous in a row-major matrix;
+  * `PeerMatrix` + `scatter_gemm`: every rank maps the other ranks' full C into its own address space once
+    (CUDA IPC) and the GEMM kernel stores each finished tile of its shard into every rank's C over NVLink
+    while it computes the next ones: no collective and no re-layout pass afterwards, only a barrier.
 """
 import torch
 import torch.distributed as dist
@@ -186,3 +190,74 @@ class HostShardedGemm:
                            self.c_dev, self.n_loc)
         c_shard_host.copy_(self.c_dev, non_blocking=True)
         cur.synchronize()
+
+
+class _DeviceArray:
+    """A raw device allocation as the CUDA array interface, so that torch can view it as a tensor."""
+
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False), "version": 3,
+                                         "strides": None}
+
+
+class PeerMatrix:
+    """A row-major [rows, cols] f32 matrix per rank, each mapped into every other rank's address space (CUDA IPC
+    over pg_b200_ipc_export / pg_b200_ipc_open; one process per GPU on one node).  `ptrs[r]` is rank r's matrix as
+    this process addresses it (`ptrs[rank]` the local one, also available as the tensor `local`)."""
+
+    def __init__(self, rows, cols, group=None):
+        import ctypes
+        from . import _lib
+        from .backend import _check, _ready
+        _ready()
+        self._lib, self._check = _lib.lib, _check
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.rows, self.cols = rows, cols
+        # an allocation of its own (cudaMalloc through the library), so that the handle names exactly this matrix
+        self._base = self._lib.pg_b200_malloc(rows * cols * 4)
+        if not self._base:
+            raise MemoryError("pg_b200_malloc failed for the shared matrix")
+        self.local = torch.as_tensor(_DeviceArray(self._base, (rows, cols)), device="cuda")
+        handle = (ctypes.c_ubyte * 64)()
+        _check(self._lib.pg_b200_ipc_export(self._base, handle), "pg_b200_ipc_export")
+        mine = (bytes(handle), 0, torch.cuda.current_device())
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.ptrs, self._opened = [], []
+        for r, (h, offset, _dev) in enumerate(everyone):
+            if r == self.rank:
+                self.ptrs.append(self.local.data_ptr())
+                continue
+            p = ctypes.c_void_p()
+            _check(self._lib.pg_b200_ipc_open((ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(p)), "pg_b200_ipc_open")
+            self._opened.append(p.value)
+            self.ptrs.append(p.value + offset)
+
+    def close(self):
+        """Unmap the peers' matrices; collective (every rank must have stopped writing first)."""
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        for p in self._opened:
+            self._check(self._lib.pg_b200_ipc_close(p), "pg_b200_ipc_close")
+        self._opened = []
+        dist.barrier(self.group)
+        if self._base:
+            self.local = None
+            self._lib.pg_b200_free(self._base)
+            self._base = None
+
+
+def scatter_gemm(dtype, a, b_shard, peers, col0):
+    """This rank's column shard C[:, col0:col0+n_loc] = a @ b_shard, stored by the GEMM kernel into the full C of every
+    rank (`peers`: a PeerMatrix).  Returns without synchronising: the full C is complete on every rank after each
+    rank has synchronised its stream and the ranks have met (`finish_scatter`)."""
+    from .backend import pg_gemm_ex_scatter
+    m, k = a.shape
+    n_loc = b_shard.shape[1]
+    pg_gemm_ex_scatter(dtype, m, n_loc, k, a, a.stride(0), b_shard, b_shard.stride(0), peers.ptrs, peers.cols, col0)
+
+
+def finish_scatter(peers):
+    torch.cuda.synchronize()
+    dist.barrier(peers.group)

@@ -32,6 +32,48 @@ def test_relayout_kernel(pg, shape):
     assert np.all(got[:, n:] == 7.0)
 
 
+@pytest.mark.parametrize("shape", [(384, 1000, 512, 4), (1024, 2048, 1024, 8), (256, 256, 128, 1)])
+def test_shard_stored_into_several_full_matrices(pg, oracle, shape):
+    """pg_b200_gemm_ex_scatter on one GPU: the destinations stand in for the ranks' full C.  Every "rank" stores its
+    column shard into all of them; afterwards each holds the whole product, the same bits everywhere and the same
+    bits as the plain shard product, with the padding columns of a wider leading dimension untouched."""
+    from picograd_b200 import sharding
+    from gpu_util import to_dev
+    m, n, k, world = shape
+    a, b = wl.config2(m, n, k)
+    ld = n + 8
+    fulls = [torch.full((m, ld), 7.0, device="cuda") for _ in range(world)]
+    ad = to_dev(a, wl.BF16)
+    pg.set_option("k_splits", 1)          # the plain product it is compared with must not cut K either
+    for rank, (c0, cnt) in enumerate(sharding.column_shards(n, world)):
+        bd = to_dev(np.ascontiguousarray(b[:, c0:c0 + cnt]), wl.BF16)
+        pg.pg_gemm_ex_scatter(wl.BF16, m, cnt, k, ad, k, bd, cnt, [f.data_ptr() for f in fulls], ld, c0)
+        assert pg.last_path().startswith("tc:") and (world == 1 or pg.last_path().endswith(f":to{world}"))
+        own = torch.empty((m, cnt), device="cuda")
+        pg.pg_gemm_ex(wl.BF16, m, cnt, k, ad, k, bd, cnt, own, cnt)
+        pg.pg_dev_sync()
+        assert torch.equal(fulls[rank][:, c0:c0 + cnt], own)
+    want = oracle.gemm_ex(wl.BF16, a, b)
+    for f in fulls:
+        assert torch.equal(f, fulls[0])
+        got = f.cpu().numpy()
+        assert wl.relerr(got[:, :n], want) <= wl.tolerance(wl.BF16, k)
+        assert np.all(got[:, n:] == 7.0)
+
+
+def test_scatter_refuses_what_tma_cannot_store(pg):
+    a = torch.zeros((64, 64), device="cuda", dtype=torch.bfloat16)
+    c = torch.zeros((64, 72), device="cuda")
+    with pytest.raises(pg.PgError):                      # shard width not a multiple of 4
+        pg.pg_gemm_ex_scatter(wl.BF16, 64, 62, 64, a, 64, a, 64, [c.data_ptr()], 72, 0)
+    with pytest.raises(pg.PgError):                      # shard beyond the row
+        pg.pg_gemm_ex_scatter(wl.BF16, 64, 64, 64, a, 64, a, 64, [c.data_ptr()], 72, 16)
+    with pytest.raises(pg.PgError):                      # f32 operands
+        pg.pg_gemm_ex_scatter(wl.F32, 64, 64, 64, c, 72, c, 72, [c.data_ptr()], 72, 0)
+    with pytest.raises(pg.PgError):                      # nine destinations
+        pg.pg_gemm_ex_scatter(wl.BF16, 64, 64, 64, a, 64, a, 64, [c.data_ptr()] * 9, 72, 0)
+
+
 def test_relayout_refuses_shards_that_do_not_cover(pg):
     st = torch.zeros((2, 4, 8), device="cuda")
     full = torch.zeros((4, 32), device="cuda")
@@ -72,6 +114,28 @@ hs = sharding.HostShardedGemm(wl.BF16, m2, n2, k)
 a_rows = torch.from_numpy(np.ascontiguousarray(a2[hs.r0:hs.r0 + hs.m_loc]).view(np.int16)).pin_memory()
 b_sh = torch.from_numpy(np.ascontiguousarray(b2[:, hs.c0:hs.c0 + hs.n_loc]).view(np.int16)).pin_memory()
 c_sh = torch.empty((m2, hs.n_loc), dtype=torch.float32).pin_memory()
+# the shard stored by the GEMM kernel itself into every rank's full C (peer memory mapped over CUDA IPC)
+n3 = 1024
+a3, b3 = wl.config2(m, n3, k)
+c0, cnt = sharding.column_shards(n3, world)[rank]
+peers = sharding.PeerMatrix(m, n3)
+peers.local.fill_(-1.0)
+torch.cuda.synchronize(); dist.barrier()
+ad3, bd3 = to_dev(a3, wl.BF16), to_dev(np.ascontiguousarray(b3[:, c0:c0 + cnt]), wl.BF16)
+sharding.scatter_gemm(wl.BF16, ad3, bd3, peers, c0)
+path3 = pg.last_path()
+sharding.finish_scatter(peers)
+want3 = o.gemm_ex(wl.BF16, a3, b3)
+ok = ok and path3.endswith(":to%d" % world)
+ok = ok and wl.relerr(peers.local.cpu().numpy(), want3) <= wl.tolerance(wl.BF16, k)
+c_own = torch.empty((m, cnt), device="cuda")
+pg.set_option("k_splits", 1)
+pg.pg_gemm_ex(wl.BF16, m, cnt, k, ad3, k, bd3, cnt, c_own, cnt)
+pg.set_option("k_splits", 0)
+ok = ok and bool(torch.equal(peers.local[:, c0:c0 + cnt], c_own))
+ref3 = peers.local.clone(); dist.broadcast(ref3, 0)
+ok = ok and bool(torch.equal(ref3, peers.local))
+peers.close()
 for _ in range(2):
     hs(a_rows, b_sh, c_sh)
 want2 = o.gemm_ex(wl.BF16, a2, np.ascontiguousarray(b2[:, hs.c0:hs.c0 + hs.n_loc]))
