@@ -230,9 +230,18 @@ class PeerMatrix:
                 self.ptrs.append(self.local.data_ptr())
                 continue
             p = ctypes.c_void_p()
-            _check(self._lib.pg_b200_ipc_open((ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(p)), "pg_b200_ipc_open")
+            if self._lib.pg_b200_ipc_open((ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(p)) != 0:
+                self.ptrs.append(None)
+                continue
             self._opened.append(p.value)
             self.ptrs.append(p.value + offset)
+        # every rank learns whether every mapping succeeded, so that all of them give up together
+        good = torch.tensor([0 if None in self.ptrs else 1], device="cuda")
+        dist.all_reduce(good, op=dist.ReduceOp.MIN, group=group)
+        if int(good.item()) == 0:
+            why = self._lib.pg_b200_last_error().decode()
+            self.close()
+            raise RuntimeError("a rank could not map a peer's matrix (no peer access between these GPUs?): " + why)
 
     def close(self):
         """Unmap the peers' matrices; collective (every rank must have stopped writing first)."""
