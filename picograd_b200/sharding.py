@@ -264,7 +264,10 @@ def scatter_gemm(dtype, a, b_shard, peers, col0):
     from .backend import pg_gemm_ex_scatter
     m, k = a.shape
     n_loc = b_shard.shape[1]
-    pg_gemm_ex_scatter(dtype, m, n_loc, k, a, a.stride(0), b_shard, b_shard.stride(0), peers.ptrs, peers.cols, col0)
+    # a chunk goes to the destinations in list order: the local matrix first, then the peers starting behind this
+    # rank, so that at any moment the ranks are sending to different peers and not all to rank 0
+    order = [peers.ptrs[(peers.rank + i) % peers.world] for i in range(peers.world)]
+    pg_gemm_ex_scatter(dtype, m, n_loc, k, a, a.stride(0), b_shard, b_shard.stride(0), order, peers.cols, col0)
 
 
 def finish_scatter(peers):
