@@ -266,6 +266,41 @@ int main(int argc, char **argv) {
         dfree(da); dfree(db); dfree(dw); dfree(dv); dfree(dtb); dfree(dg); dfree(dga); dfree(dgw);
     }
 
+    /* ---- a column shard stored into two full matrices by the GEMM kernel (pg_b200_gemm_ex_scatter) ---- */
+    {
+        typedef int (*scatter_fn)(int, size_t, size_t, size_t, const void *, size_t, const void *, size_t, float *const *, size_t,
+                                  size_t, size_t);
+        typedef int (*gemm_ex_fn)(int, size_t, size_t, size_t, const void *, size_t, const void *, size_t, float *, size_t);
+        scatter_fn scatter = (scatter_fn)dlsym(h, "pg_b200_gemm_ex_scatter");
+        gemm_ex_fn gemm_ex = (gemm_ex_fn)dlsym(h, "pg_b200_gemm_ex");
+        if (!scatter || !gemm_ex) { printf("missing symbol (scatter)\n"); return 2; }
+        enum { SM = 256, SN = 128, SK = 128, LD = 384, COL0 = 128 };
+        static uint16_t a[SM * SK], b[SK * SN];
+        static float full[2][SM * LD], own[SM * SN];
+        for (int i = 0; i < SM * SK; i++) a[i] = to_bf16(urand());
+        for (int i = 0; i < SK * SN; i++) b[i] = to_bf16(urand());
+        void *da = dmalloc(sizeof a), *db = dmalloc(sizeof b), *d0 = dmalloc(sizeof full[0]), *d1 = dmalloc(sizeof full[0]),
+             *down = dmalloc(sizeof own);
+        CHECK(da && db && d0 && d1 && down);
+        for (int i = 0; i < SM * LD; i++) full[0][i] = -3.0f;
+        CHECK(h2d(da, a, sizeof a) == 0 && h2d(db, b, sizeof b) == 0 && h2d(d0, full[0], sizeof full[0]) == 0 &&
+              h2d(d1, full[0], sizeof full[0]) == 0);
+        float *dst[2] = {(float *)d0, (float *)d1};
+        CHECK(scatter(2, SM, SN, SK, da, SK, db, SN, dst, 2, LD, COL0) == 0);
+        CHECK(gemm_ex(2, SM, SN, SK, da, SK, db, SN, (float *)down, SN) == 0);
+        CHECK(dsync() == 0 && d2h(full[0], d0, sizeof full[0]) == 0 && d2h(full[1], d1, sizeof full[1]) == 0 &&
+              d2h(own, down, sizeof own) == 0);
+        CHECK(memcmp(full[0], full[1], sizeof full[0]) == 0);
+        for (int i = 0; i < SM; i++)
+            for (int j = 0; j < LD; j++) {
+                float want = (j >= COL0 && j < COL0 + SN) ? own[i * SN + j - COL0] : -3.0f;
+                if (full[0][i * LD + j] != want) { CHECK(!"scatter: element differs"); i = SM; break; }
+            }
+        CHECK(scatter(2, SM, SN - 2, SK, da, SK, db, SN, dst, 2, LD, COL0) == -1);     /* width not a multiple of 4 */
+        printf("gemm_ex_scatter bf16 256x128x128 into two 256x384 matrices: same bits as gemm_ex, rest untouched\n");
+        dfree(da); dfree(db); dfree(d0); dfree(d1); dfree(down);
+    }
+
     if (fails) { printf("%d check(s) failed: %s\n", fails, last_error()); return 1; }
     printf("all passed\n");
     return 0;
