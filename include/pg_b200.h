@@ -124,9 +124,10 @@ PG_B200_API int pg_b200_gemm_batched(int dtype_a, int dtype_b, int trans_a, int 
  * (pg_b200_ipc_open).  After every rank of an N-column-sharded product has made this call and the ranks have met
  * (stream synchronisation on each, then a barrier among the processes), every device holds all of C in row-major
  * order: no all-gather, no re-layout pass, and the transfer over NVLink overlaps the product tile by tile.
- * f16 / bf16 only; 1 to 8 destinations; col0, n and ldc multiples of 4, destinations 16-byte aligned (the stores
- * are TMA bulk stores); PG_ERR_UNSUPPORTED otherwise — the caller then gathers with NCCL.  The kernel only
- * stores to the other devices and waits for none of them. */
+ * f16 / bf16 only; 1 to 8 destinations; col0, n and ldc multiples of 4, destinations 16-byte aligned (dst[0] is
+ * written with TMA bulk stores, the others with 16-byte stores from the same staged chunks: put the local matrix
+ * first); PG_ERR_UNSUPPORTED otherwise — the caller then gathers with NCCL.  The kernel only stores to the other
+ * devices and waits for none of them. */
 PG_B200_API int pg_b200_gemm_ex_scatter(int dtype, size_t m, size_t n, size_t k, const void *a, size_t lda,
                                         const void *b, size_t ldb, float *const *dst, size_t n_dst, size_t ldc,
                                         size_t col0);
