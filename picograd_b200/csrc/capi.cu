@@ -248,6 +248,7 @@ static int run_simt(const Problem &p) {
     s.bias = p.bias; s.act = p.act; s.c16 = p.c16; s.ld16 = (int64_t)p.ld16; s.dtype16 = p.dtype16;
     s.act_copy_only = p.act_copy_only;
     s.stream = g.stream;
+    s.pdl = g.opt_pdl;
     int st = simt_gemm_launch(s);
     if (st == ST_OK) set_last_path("simt");
     return st;

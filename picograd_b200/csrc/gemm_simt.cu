@@ -330,18 +330,22 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-constexpr int PM = 32, PN = 64, PSTAGES = 4;
+constexpr int PM = 32, PN = 64, PK = 32, PSTAGES = 3;
 int g_small_f32_pipe = 1;      // small f32 products take the cp.async kernel (0: the register-staged 64 x 64 one)
 __global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) {
-    constexpr int LDA = SK + 4, LDB = PN + 4;
+    constexpr int LDA = PK + 4, LDB = PN + 4;
     __shared__ __align__(16) float As[PSTAGES][PM][LDA];
-    __shared__ __align__(16) float Bs[PSTAGES][SK][LDB];
+    __shared__ __align__(16) float Bs[PSTAGES][PK][LDB];
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;                 // 16 x 8 threads, each 4 columns x 4 rows
     const uint32_t bz = blockIdx.z;
     const long long m0 = (long long)blockIdx.y * PM, n0 = (long long)blockIdx.x * PN;
     const float *A = reinterpret_cast<const float *>(p.A) + (long long)bz * p.a_bs;
     const float *B = reinterpret_cast<const float *>(p.B) + (long long)bz * p.b_bs;
+    // Launched with programmatic stream serialisation: this CTA may have been started while the kernel before it in
+    // the stream was still draining.  Nothing of global memory is touched before that kernel has finished.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     float acc[4][4];
 #pragma unroll
@@ -352,55 +356,68 @@ __global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) 
         for (int i = 0; i < 4; ++i) acc[i][j] = b0;
     }
 
-    // copy roles: A 32 rows x 4 vectors = one per thread; B 16 k-rows x 16 vectors = two per thread
-    const int a_r = tid >> 2, a_kq = (tid & 3) * 4;
+    // copy roles: A 32 rows x 8 vectors = two per thread; B 32 k-rows x 16 vectors = four per thread
+    const int a_r = tid >> 3, a_kq = (tid & 7) * 4;
     const int b_k = tid >> 4, b_nq = (tid & 15) * 4;
     auto issue = [&](int stage, uint32_t k0) {
-        {
-            const long long gm = m0 + a_r, gk = (long long)k0 + a_kq;
-            int bytes = 0;
-            if (gm < p.M && gk < p.K) bytes = (int)((p.K - gk) < 4 ? (p.K - gk) : 4) * 4;
-            cp_async_16(&As[stage][a_r][a_kq], bytes ? A + gm * p.a_rs + gk : A, bytes);
-        }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
+            const long long gm = m0 + a_r + 16 * h, gk = (long long)k0 + a_kq;
+            int bytes = 0;
+            if (gm < p.M && gk < p.K) bytes = (int)((p.K - gk) < 4 ? (p.K - gk) : 4) * 4;
+            cp_async_16(&As[stage][a_r + 16 * h][a_kq], bytes ? A + gm * p.a_rs + gk : A, bytes);
+        }
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
             const long long gk = (long long)k0 + b_k + 8 * h, gn = n0 + b_nq;
             int bytes = 0;
             if (gk < p.K && gn < p.N) bytes = (int)((p.N - gn) < 4 ? (p.N - gn) : 4) * 4;
             cp_async_16(&Bs[stage][b_k + 8 * h][b_nq], bytes ? B + gk * p.b_rs + gn : B, bytes);
         }
     };
+    // the operands of four k steps in registers; the next four are fetched while these are multiplied, so that the
+    // one warp a scheduler has does not wait for shared memory between its multiply-adds
+    struct Frag { float4 a[4], b[4]; };
+    auto fetch = [&](Frag &f, int st, int kq) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f.a[i] = *reinterpret_cast<const float4 *>(&As[st][ty * 4 + i][kq]);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) f.b[kk] = *reinterpret_cast<const float4 *>(&Bs[st][kq + kk][tx * 4]);
+    };
+    auto multiply = [&](const Frag &f) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float a = kk == 0 ? f.a[i].x : (kk == 1 ? f.a[i].y : (kk == 2 ? f.a[i].z : f.a[i].w));
+                acc[i][0] = __fmaf_rn(a, f.b[kk].x, acc[i][0]);
+                acc[i][1] = __fmaf_rn(a, f.b[kk].y, acc[i][1]);
+                acc[i][2] = __fmaf_rn(a, f.b[kk].z, acc[i][2]);
+                acc[i][3] = __fmaf_rn(a, f.b[kk].w, acc[i][3]);
+            }
+        }
+    };
 
-    const uint32_t slabs = (p.K + SK - 1) / SK;
+    const uint32_t slabs = (p.K + PK - 1) / PK;
 #pragma unroll
     for (int s = 0; s < PSTAGES - 1; ++s) {
-        if ((uint32_t)s < slabs) issue(s, s * SK);
+        if ((uint32_t)s < slabs) issue(s, s * PK);
         cp_async_commit();
     }
     for (uint32_t s = 0; s < slabs; ++s) {
         cp_async_wait<PSTAGES - 2>();          // slab s has landed (this thread's copies) ...
         __syncthreads();                       // ... and everyone's; the stage read in iteration s - 1 is free again
-        if (s + PSTAGES - 1 < slabs) issue((s + PSTAGES - 1) % PSTAGES, (s + PSTAGES - 1) * SK);
+        if (s + PSTAGES - 1 < slabs) issue((s + PSTAGES - 1) % PSTAGES, (s + PSTAGES - 1) * PK);
         cp_async_commit();
         const int st = s % PSTAGES;
+        Frag f0, f1;
+        fetch(f0, st, 0);
 #pragma unroll
-        for (int kq = 0; kq < SK; kq += 4) {
-            float4 a4[4], b4[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) a4[i] = *reinterpret_cast<const float4 *>(&As[st][ty * 4 + i][kq]);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) b4[kk] = *reinterpret_cast<const float4 *>(&Bs[st][kq + kk][tx * 4]);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float a = kk == 0 ? a4[i].x : (kk == 1 ? a4[i].y : (kk == 2 ? a4[i].z : a4[i].w));
-                    acc[i][0] = __fmaf_rn(a, b4[kk].x, acc[i][0]);
-                    acc[i][1] = __fmaf_rn(a, b4[kk].y, acc[i][1]);
-                    acc[i][2] = __fmaf_rn(a, b4[kk].z, acc[i][2]);
-                    acc[i][3] = __fmaf_rn(a, b4[kk].w, acc[i][3]);
-                }
-            }
+        for (int kq = 0; kq < PK; kq += 8) {
+            fetch(f1, st, kq + 4);
+            multiply(f0);
+            if (kq + 8 < PK) fetch(f0, st, kq + 8);
+            multiply(f1);
         }
     }
 
@@ -464,7 +481,14 @@ int simt_gemm_launch(const SimtGemm &g) {
         if (nn_f32 && big) sgemm_nn_kernel<128><<<grid, 256, 0, g.stream>>>(q);
         else if (nn_f32 && g_small_f32_pipe) {
             dim3 pgrid((g.N + PN - 1) / PN, (g.M + PM - 1) / PM, nb);
-            sgemm_nn_pipe_kernel<<<pgrid, 128, 0, g.stream>>>(q);
+            cudaLaunchConfig_t lc = {};
+            lc.gridDim = pgrid; lc.blockDim = dim3(128, 1, 1); lc.stream = g.stream;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            lc.attrs = at; lc.numAttrs = g.pdl ? 1 : 0;
+            void *args[1] = {(void *)&q};
+            cudaLaunchKernelExC(&lc, (const void *)sgemm_nn_pipe_kernel, args);
         } else if (nn_f32) sgemm_nn_kernel<64><<<grid, 256, 0, g.stream>>>(q);
         else if (big) simt_gemm_kernel<128><<<grid, 256, 0, g.stream>>>(q);
         else simt_gemm_kernel<64><<<grid, 256, 0, g.stream>>>(q);

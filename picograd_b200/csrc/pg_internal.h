@@ -127,6 +127,7 @@ struct SimtGemm {
     const float *bias; int act;   // fused epilogue: the chain of column j starts at bias[j]; act applied at the store
     uint16_t *c16; int64_t ld16; int dtype16;
     int act_copy_only;         // activation applied to the 16-bit copy only
+    int pdl;                   // small f32 kernel: launch with programmatic stream serialisation
     cudaStream_t stream;
 };
 int simt_gemm_launch(const SimtGemm &g);
