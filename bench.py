@@ -507,6 +507,12 @@ def run_other_config(args, rank, world):
         a, b = wl.config1(512)
         ad, bd = to_dev(a, wl.F32), to_dev(b, wl.F32)
         fn = lambda: pg.pg_matmul(ad, bd)
+        # the same call as a C caller makes it: descriptors built once, the output allocated once
+        from picograd_b200 import _lib, backend as _be
+        import ctypes as _C
+        c1 = torch.empty((512, 512), dtype=torch.float32, device="cuda")
+        _da, _db, _do = _be._desc(ad), _be._desc(bd), _be._desc(c1)
+        c_fn = lambda: _lib.lib.pg_b200_matmul(_C.byref(_da), _C.byref(_db), _C.byref(_do))
         flops, byts, name, dt = 2.0 * 512 ** 3, 3 * 512 * 512 * 4, "pg_matmul f32 512^3", "f32"
         bound, profile = "launch", "sgemm_nn_pipe_kernel_f32_512.md"
     elif cfg == "square":
@@ -524,6 +530,9 @@ def run_other_config(args, rank, world):
         ad, bd = to_dev(a, code), to_dev(b, code)
         c = torch.empty((m, n), dtype=torch.float32, device="cuda")
         fn = lambda: pg.pg_gemm_ex(code, m, n, k, ad, k, bd, n, c, n)
+        from picograd_b200 import _lib
+        _pa, _pb, _pc = ad.data_ptr(), bd.data_ptr(), c.data_ptr()
+        c_fn = lambda: _lib.lib.pg_b200_gemm_ex(code, m, n, k, _pa, k, _pb, n, _pc, n)
         dt = "f16" if code == wl.F16 else "bf16"
         flops, byts, name = 2.0 * m * n * k, (m * k + k * n) * 2 + m * n * 4, f"pg_gemm_ex {dt} {m}x{n}x{k}"
         if cfg == "3b":
@@ -631,6 +640,17 @@ def run_other_config(args, rank, world):
             for _ in range(50):
                 graph.replay()
             g1.record(side); side.synchronize()
+            # the bare C-ABI call in a loop (no Python wrapper around it): what a C caller's eager loop costs
+            for _ in range(200):
+                c_fn()
+            side.synchronize()
+            n_c = 5000
+            c0e, c1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0e.record(side)
+            for _ in range(n_c):
+                c_fn()
+            c1e.record(side); side.synchronize()
+            line["c_abi_eager_ms_per_step"] = c0e.elapsed_time(c1e) / n_c
         _lib.lib.pg_b200_set_stream(None)
         gms = g0.elapsed_time(g1) / 1000
         line["graph_replay_ms_per_step"] = gms
