@@ -1149,6 +1149,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "cluster_splitk")) { g.opt_cluster_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "big_f32_pipe")) { g_big_f32_pipe = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "small_f32_pipe")) { g_small_f32_pipe = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "k_serpentine")) { g.opt_k_serpentine = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "serpentine")) { g.opt_serpentine = value ? 1 : 0; return ST_OK; }

@@ -52,14 +52,17 @@ def test_f32_dyadic_exact_like_bench_gemm_cuda(pg):
     assert np.array_equal(got.astype(np.float64), d.astype(np.float64) @ d.astype(np.float64))
 
 
+@pytest.mark.parametrize("pipe", [1, 0], ids=["cp.async-packed-fma", "register-staged"])
 @pytest.mark.parametrize("lds", [(336, 1200, 1200), (333, 1203, 1201)], ids=["aligned", "odd-ld"])
-def test_f32_large_bit_exact(pg, oracle, lds):
-    """Large f32 products (the 128x128 FFMA kernels, vectorised when rows are 16-byte aligned) keep the
-    one-chain-per-element arithmetic: equal to the CPU result bit for bit, ragged edges included."""
+def test_f32_large_bit_exact(pg, oracle, lds, pipe):
+    """Large f32 products (the 128x128 FFMA kernels: cp.async slabs and two columns per fma.rn.f32x2 when rows are
+    16-byte aligned, the generic kernel otherwise) keep the one-chain-per-element arithmetic: equal to the CPU result
+    bit for bit, ragged edges in M, N and K included."""
     m, n, k = 1100, 1200, 333
     rng = np.random.default_rng(20)
     a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
     b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    pg.set_option("big_f32_pipe", pipe)
     got = gemm_dev(pg, wl.F32, a, b, lda=lds[0], ldb=lds[1], ldc=lds[2])
     assert pg.last_path() == "simt"
     assert np.array_equal(got, oracle.gemm_ex(wl.F32, a, b))
