@@ -347,13 +347,14 @@ __global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    float acc[4][4];
+    float2 acc2[4][2];                   // columns in pairs: what fma.rn.f32x2 reads and writes
+#define ACC(i, j) (((j) & 1) ? acc2[i][(j) >> 1].y : acc2[i][(j) >> 1].x)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const long long gn = n0 + tx * 4 + j;
         const float b0 = (p.bias && gn < p.N) ? p.bias[gn] : 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[i][j] = b0;
+        for (int i = 0; i < 4; ++i) ACC(i, j) = b0;
     }
 
     // copy roles: A 32 rows x 8 vectors = two per thread; B 32 k-rows x 16 vectors = four per thread
@@ -390,10 +391,9 @@ __global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) 
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float a = kk == 0 ? f.a[i].x : (kk == 1 ? f.a[i].y : (kk == 2 ? f.a[i].z : f.a[i].w));
-                acc[i][0] = __fmaf_rn(a, f.b[kk].x, acc[i][0]);
-                acc[i][1] = __fmaf_rn(a, f.b[kk].y, acc[i][1]);
-                acc[i][2] = __fmaf_rn(a, f.b[kk].z, acc[i][2]);
-                acc[i][3] = __fmaf_rn(a, f.b[kk].w, acc[i][3]);
+                const float2 aa = make_float2(a, a);      // fma.rn.f32x2: two columns per instruction, same arithmetic per lane
+                acc2[i][0] = __ffma2_rn(aa, make_float2(f.b[kk].x, f.b[kk].y), acc2[i][0]);
+                acc2[i][1] = __ffma2_rn(aa, make_float2(f.b[kk].z, f.b[kk].w), acc2[i][1]);
             }
         }
     };
@@ -431,8 +431,8 @@ __global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) 
         float y[4], c[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            y[j] = simt_act(acc[i][j], p.act);
-            c[j] = p.act_copy_only ? acc[i][j] : y[j];
+            y[j] = simt_act(ACC(i, j), p.act);
+            c[j] = p.act_copy_only ? ACC(i, j) : y[j];
         }
         if (p.c16) {
 #pragma unroll
@@ -451,6 +451,8 @@ __global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) 
 }
 
 // ---------------------------------------------------------------------------------------------
+#undef ACC
+
 // The same product for LARGE f32 shapes: 128 x 128 tile, 256 threads, 8 x 8 outputs per thread (rows ty*4.. and
 // 64 + ty*4.., columns tx*4.. and 64 + tx*4..), K slabs of 16 brought in by 16-byte cp.async copies with three slabs
 // in flight (56 KB of dynamic shared memory, two CTAs per SM: 16 warps hide each other's shared-memory latency).
