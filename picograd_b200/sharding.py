@@ -214,18 +214,24 @@ class PeerMatrix:
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.rows, self.cols = rows, cols
-        # an allocation of its own (cudaMalloc through the library), so that the handle names exactly this matrix
+        # an allocation of its own (cudaMalloc through the library), so that the handle names exactly this matrix.
+        # A rank that cannot allocate or export still takes part in the exchange below (with no handle), so that the
+        # ranks fail together instead of leaving the others waiting in a collective.
+        self._opened, self.ptrs, self.local = [], [], None
         self._base = self._lib.pg_b200_malloc(rows * cols * 4)
-        if not self._base:
-            raise MemoryError("pg_b200_malloc failed for the shared matrix")
-        self.local = torch.as_tensor(_DeviceArray(self._base, (rows, cols)), device="cuda")
-        handle = (ctypes.c_ubyte * 64)()
-        _check(self._lib.pg_b200_ipc_export(self._base, handle), "pg_b200_ipc_export")
-        mine = (bytes(handle), 0, torch.cuda.current_device())
+        mine = None
+        if self._base:
+            self.local = torch.as_tensor(_DeviceArray(self._base, (rows, cols)), device="cuda")
+            handle = (ctypes.c_ubyte * 64)()
+            if self._lib.pg_b200_ipc_export(self._base, handle) == 0:
+                mine = (bytes(handle), 0, torch.cuda.current_device())
         everyone = [None] * self.world
         dist.all_gather_object(everyone, mine, group=group)
-        self.ptrs, self._opened = [], []
-        for r, (h, offset, _dev) in enumerate(everyone):
+        for r, entry in enumerate(everyone):
+            if entry is None or mine is None:
+                self.ptrs.append(None)
+                continue
+            h, offset, _dev = entry
             if r == self.rank:
                 self.ptrs.append(self.local.data_ptr())
                 continue
@@ -241,7 +247,8 @@ class PeerMatrix:
         if int(good.item()) == 0:
             why = self._lib.pg_b200_last_error().decode()
             self.close()
-            raise RuntimeError("a rank could not map a peer's matrix (no peer access between these GPUs?): " + why)
+            raise RuntimeError("a rank could not allocate, export or map a shared matrix (no peer access between these "
+                               "GPUs?): " + why)
 
     def close(self):
         """Unmap the peers' matrices; collective (every rank must have stopped writing first)."""
