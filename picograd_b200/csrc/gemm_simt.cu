@@ -454,15 +454,16 @@ __global__ void __launch_bounds__(128) sgemm_nn_pipe_kernel(const SimtParams p) 
 #undef ACC
 
 // The same product for LARGE f32 shapes: 128 x 128 tile, 256 threads, 8 x 8 outputs per thread (rows ty*4.. and
-// 64 + ty*4.., columns tx*4.. and 64 + tx*4..), K slabs of 16 brought in by 16-byte cp.async copies with three slabs
-// in flight (56 KB of dynamic shared memory, two CTAs per SM: 16 warps hide each other's shared-memory latency).
+// 64 + ty*4.., columns tx*4.. and 64 + tx*4..), K slabs of 32 brought in by 16-byte cp.async copies with three slabs
+// in flight (106 KB of dynamic shared memory, two CTAs per SM: 16 warps hide each other's shared-memory latency).
 // A stays [m][k] in shared memory; a thread reads two k steps of its eight rows as 8-byte vectors and two k rows of
 // B as 16-byte vectors, then issues the 128 multiply-adds of those two steps as 64 fma.rn.f32x2 (sm_100: two
 // columns per instruction, each lane the same fused multiply-add as the scalar form; measured 48.1 against 43.5
-// TFLOP/s at 4096^3 for scalar fmaf in the same kernel, 38.6 for the register-staged kernel).  One fmaf chain per
+// TFLOP/s at 4096^3 for scalar fmaf in the same kernel with 16-deep slabs, 50.7 with 32-deep ones, 38.6 for the
+// register-staged kernel).  One fmaf chain per
 // element, k ascending, tails zero-filled by the copies: the bits of picograd's CPU kernels.
 // ---------------------------------------------------------------------------------------------
-constexpr int GM = 128, GN = 128, GK = 16, GSTAGES = 3;
+constexpr int GM = 128, GN = 128, GK = 32, GSTAGES = 3;
 constexpr int G_LDA = GK + 4, G_LDB = GN + 4;
 constexpr int G_SMEM = GSTAGES * (GM * G_LDA + GK * G_LDB) * 4;
 int g_big_f32_pipe = 1;        // large f32 products take this kernel (0: the register-staged 128 x 128 one)
@@ -487,19 +488,20 @@ __global__ void __launch_bounds__(256, 2) sgemm_nn_big_kernel(const SimtParams p
         for (int i = 0; i < 8; ++i) ACC(i, j) = b0;
     }
 
-    // copy roles per slab: A 128 rows x 4 vectors and B 16 k-rows x 32 vectors = two of each per thread
+    // copy roles per slab: A 128 rows x GK/4 vectors and B GK k-rows x 32 vectors, GK/8 of each per thread
+    constexpr int AV = GK / 4;                       // 16-byte vectors per row of A in a slab
     auto issue = [&](int stage, uint32_t k0) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < GK / 8; ++h) {
             const int idx = tid + 256 * h;
-            const int r = idx >> 2, kq = (idx & 3) * 4;
+            const int r = idx / AV, kq = (idx % AV) * 4;
             const long long gm = m0 + r, gk = (long long)k0 + kq;
             int bytes = 0;
             if (gm < p.M && gk < p.K) bytes = (int)((p.K - gk) < 4 ? (p.K - gk) : 4) * 4;
             cp_async_16(&As[stage][r][kq], bytes ? A + gm * p.a_rs + gk : A, bytes);
         }
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < GK / 8; ++h) {
             const int idx = tid + 256 * h;
             const int k = idx >> 5, nq = (idx & 31) * 4;
             const long long gk = (long long)k0 + k, gn = n0 + nq;
