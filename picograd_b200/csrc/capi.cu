@@ -47,6 +47,8 @@ struct State {
     int opt_fused_attention = 1; // 0: pg_b200_attention_bmm always runs the three-kernel chain
     DeviceBuf attn_ws;           // S and P of the chain form of pg_b200_attention_bmm
     DeviceBuf caller_ws[2];      // permuted operand copies of pg_b200_tensordot
+    DeviceBuf simt_ws[2];        // row-major copies of transposed f32 operands (large products on the FFMA route)
+    int opt_f32_retranspose = 1; // large f32 products with a transposed operand: transpose it once, then the row-major kernel
     int opt_cluster_splitk = 1;  // K-slices of a skinny product as one cluster (reduction through distributed shared memory)
     int opt_host_blk = 0;        // slab size of the staged host-pointer pipeline (0 = 2048)
     int opt_stream_k = 0;        // balanced last wave: the K ranges of the tiles of a partly filled last wave are dealt
@@ -235,7 +237,42 @@ struct Problem {
     bool has_epilogue() const { return bias != nullptr || act != 0 || c16 != nullptr; }
 };
 
+static int run_simt(const Problem &p);
+
+// Large f32 products with a transposed operand — the two products of bwd_matmul on f32 leaves (autograd.c:659-691) —
+// would take the generic strided kernel (27 TFLOP/s at 4096^3).  The transposed operand is instead copied once into
+// scratch in row-major order (bandwidth-bound: 134 MB at 4096^2, ~1 % of the product's time) and the product takes
+// the row-major kernel (51 TFLOP/s).  Same chain per element, same bits.
+static int run_simt_retransposed(const Problem &p, bool &taken) {
+    taken = false;
+    if (!g.opt_f32_retranspose || p.dtype_a != DT_F32 || p.dtype_b != DT_F32 || p.batch != 1) return ST_OK;
+    if (!(p.trans_a || p.trans_b) || (uint64_t)p.m * p.n < (uint64_t)512 * 512 * 4 || p.k < 64) return ST_OK;
+    if ((p.trans_a && p.k % 4) || (p.trans_b && p.n % 4)) return ST_OK;          // the row-major kernel wants 16-byte rows
+    Problem q = p;
+    for (int which = 0; which < 2; ++which) {
+        if (!(which == 0 ? p.trans_a : p.trans_b)) continue;
+        // stored [rows_src][cols_src] with leading dimension ld; wanted [cols_src][rows_src], contiguous
+        const uint64_t rows_src = which == 0 ? p.k : p.n, cols_src = which == 0 ? p.m : p.k;
+        const uint64_t ld = which == 0 ? p.lda : p.ldb;
+        int st = grow(g.simt_ws[which], rows_src * cols_src * 4);
+        if (st != ST_OK) return st;
+        const uint64_t shape[2] = {rows_src, cols_src}, stride[2] = {ld, 1};
+        const uint32_t perm[2] = {1, 0};
+        st = permute_copy_launch(which == 0 ? p.a : p.b, g.simt_ws[which].ptr, 4, 2, shape, perm, g.stream, stride);
+        if (st != ST_OK) return st;
+        if (which == 0) { q.a = g.simt_ws[0].ptr; q.lda = rows_src; q.trans_a = 0; }
+        else { q.b = g.simt_ws[1].ptr; q.ldb = rows_src; q.trans_b = 0; }
+    }
+    taken = true;
+    return run_simt(q);
+}
+
 static int run_simt(const Problem &p) {
+    {
+        bool taken = false;
+        const int st = run_simt_retransposed(p, taken);
+        if (taken || st != ST_OK) return st;
+    }
     SimtGemm s;
     s.dtype_a = p.dtype_a; s.dtype_b = p.dtype_b;
     s.M = (uint32_t)p.m; s.N = (uint32_t)p.n; s.K = (uint32_t)p.k; s.batch = (uint32_t)p.batch;
@@ -1149,6 +1186,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "cluster_splitk")) { g.opt_cluster_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "f32_retranspose")) { g.opt_f32_retranspose = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "big_f32_pipe")) { g_big_f32_pipe = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "small_f32_pipe")) { g_small_f32_pipe = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "k_serpentine")) { g.opt_k_serpentine = value ? 1 : 0; return ST_OK; }

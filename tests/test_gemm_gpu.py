@@ -569,6 +569,25 @@ def test_backward_accumulates_into_existing_grads(pg, oracle):
     assert wl.relerr(to_host(gb) - gb0, gb_ref) <= wl.tolerance(wl.BF16, m)
 
 
+@pytest.mark.parametrize("retranspose", [1, 0], ids=["transposed-once", "strided-kernel"])
+def test_backward_large_f32_leaves_bit_exact(pg, oracle, retranspose):
+    """bwd_matmul on f32 leaves (autograd.c:659-691: f32 GEMMs with a transposed operand).  Large products copy the
+    transposed operand into row-major order once and take the row-major FFMA kernel; either way every gradient element
+    is one fused multiply-add chain in picograd's order: the CPU result bit for bit."""
+    rng = np.random.default_rng(15)
+    m, n, k = 1100, 1200, 1000
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    g = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    pg.set_option("f32_retranspose", retranspose)
+    ga, gb = pg.pg_matmul_backward(to_dev(a, wl.F32), to_dev(b, wl.F32), to_dev(g, wl.F32))
+    pg.pg_dev_sync()
+    assert pg.last_path() == "simt"
+    ga_ref, gb_ref = oracle.matmul_backward(wl.F32, a, b, g)
+    assert np.array_equal(to_host(ga), ga_ref)
+    assert np.array_equal(to_host(gb), gb_ref)
+
+
 def test_backward_f16_operands(pg, oracle):
     """f16 A and B with the f32 gradient: both sides meet the tensor cores as exact bf16 pieces."""
     rng = np.random.default_rng(16)
