@@ -1186,6 +1186,7 @@ int pg_b200_set_option(const char *name, int value) {
     if (!strcmp(name, "cluster_splitk")) { g.opt_cluster_splitk = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "host_blk")) { g.opt_host_blk = value; return ST_OK; }
     if (!strcmp(name, "stream_k")) { g.opt_stream_k = value ? 1 : 0; return ST_OK; }
+    if (!strcmp(name, "big_f32_min_ctas")) { g_big_f32_min_ctas = value; return ST_OK; }
     if (!strcmp(name, "f32_retranspose")) { g.opt_f32_retranspose = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "big_f32_pipe")) { g_big_f32_pipe = value ? 1 : 0; return ST_OK; }
     if (!strcmp(name, "small_f32_pipe")) { g_small_f32_pipe = value ? 1 : 0; return ST_OK; }

@@ -467,6 +467,7 @@ constexpr int GM = 128, GN = 128, GK = 32, GSTAGES = 3;
 constexpr int G_LDA = GK + 4, G_LDB = GN + 4;
 constexpr int G_SMEM = GSTAGES * (GM * G_LDA + GK * G_LDB) * 4;
 int g_big_f32_pipe = 1;        // large f32 products take this kernel (0: the register-staged 128 x 128 one)
+int g_big_f32_min_ctas = 140;  // ... when its grid has at least this many CTAs (measured: 144 CTAs 44.1 vs 40.2 TFLOP/s for the small kernel, 128 CTAs 38.7 vs 40.0, 64 CTAs 19.3 vs 27.5)
 __global__ void __launch_bounds__(256, 2) sgemm_nn_big_kernel(const SimtParams p) {
     extern __shared__ __align__(16) float g_smem[];
     float (*As)[GM][G_LDA] = reinterpret_cast<float (*)[GM][G_LDA]>(g_smem);
@@ -616,7 +617,9 @@ int simt_gemm_launch(const SimtGemm &g) {
         const bool nn_f32 = g.dtype_a == DT_F32 && g.dtype_b == DT_F32 && g.a_cs == 1 && g.b_cs == 1 &&
                             g.a_rs % 4 == 0 && g.b_rs % 4 == 0 && g.a_bs % 4 == 0 && g.b_bs % 4 == 0 &&
                             (((uintptr_t)g.A | (uintptr_t)g.B) & 15) == 0;
-        if (nn_f32 && big && g_big_f32_pipe) {
+        // the 128 x 128 kernel needs a grid that fills the SMs; below that the 32 x 64 tiles of the small kernel do better
+        const bool big_grid = (uint64_t)grid.x * grid.y * grid.z >= (uint64_t)g_big_f32_min_ctas;
+        if (nn_f32 && big && g_big_f32_pipe && big_grid) {
             static bool attr_set[8] = {};
             int dev = 0;
             cudaGetDevice(&dev);
@@ -625,7 +628,7 @@ int simt_gemm_launch(const SimtGemm &g) {
                 attr_set[dev] = true;
             }
             sgemm_nn_big_kernel<<<grid, 256, G_SMEM, g.stream>>>(q);
-        } else if (nn_f32 && big) sgemm_nn_kernel<128><<<grid, 256, 0, g.stream>>>(q);
+        } else if (nn_f32 && big && !g_big_f32_pipe) sgemm_nn_kernel<128><<<grid, 256, 0, g.stream>>>(q);
         else if (nn_f32 && g_small_f32_pipe) {
             dim3 pgrid((g.N + PN - 1) / PN, (g.M + PM - 1) / PM, nb);
             cudaLaunchConfig_t lc = {};
@@ -636,7 +639,11 @@ int simt_gemm_launch(const SimtGemm &g) {
             lc.attrs = at; lc.numAttrs = g.pdl ? 1 : 0;
             void *args[1] = {(void *)&q};
             cudaLaunchKernelExC(&lc, (const void *)sgemm_nn_pipe_kernel, args);
-        } else if (nn_f32) sgemm_nn_kernel<64><<<grid, 256, 0, g.stream>>>(q);
+        } else if (nn_f32) {
+            dim3 grid64((g.N + 63) / 64, (g.M + 63) / 64, nb);
+            if (grid64.y > 65535u) { set_error("simt gemm: M too large for one launch"); return ST_UNSUPPORTED; }
+            sgemm_nn_kernel<64><<<grid64, 256, 0, g.stream>>>(q);
+        }
         else if (big) simt_gemm_kernel<128><<<grid, 256, 0, g.stream>>>(q);
         else simt_gemm_kernel<64><<<grid, 256, 0, g.stream>>>(q);
         cudaError_t e = cudaGetLastError();

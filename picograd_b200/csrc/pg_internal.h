@@ -131,6 +131,7 @@ struct SimtGemm {
     cudaStream_t stream;
 };
 int simt_gemm_launch(const SimtGemm &g);
+extern int g_big_f32_min_ctas; // the 128 x 128 f32 kernel is used from this many CTAs on
 extern int g_big_f32_pipe;     // large f32 x f32 products: cp.async-pipelined 128 x 128 kernel (1) or the register-staged one (0)
 extern int g_small_f32_pipe;   // small f32 x f32 products: cp.async-pipelined 32 x 64 kernel (1) or the 64 x 64 one (0)
 

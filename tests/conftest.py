@@ -45,5 +45,5 @@ def _reset_options(request):
     if "gpu" in request.keywords:
         import picograd_b200 as pg
         for name, val in (("path", 0), ("tile_config", -1), ("epilogue", -1), ("k_splits", 0),
-                          ("f32_parts", 2), ("f32_tensor_cores", 0), ("host_pipeline", 1), ("stages", 0), ("debug", 0), ("fused_splitk", 1), ("swap_skinny", 1), ("stream_k", 0), ("pdl", 1), ("small_f32_pipe", 1), ("big_f32_pipe", 1), ("f32_retranspose", 1), ("die_aware", 1), ("serpentine", 1), ("k_serpentine", 1), ("f32_chunk", 512), ("fused_attention", 1), ("attn_q_tmem", 1)):
+                          ("f32_parts", 2), ("f32_tensor_cores", 0), ("host_pipeline", 1), ("stages", 0), ("debug", 0), ("fused_splitk", 1), ("swap_skinny", 1), ("stream_k", 0), ("pdl", 1), ("small_f32_pipe", 1), ("big_f32_pipe", 1), ("f32_retranspose", 1), ("big_f32_min_ctas", 140), ("die_aware", 1), ("serpentine", 1), ("k_serpentine", 1), ("f32_chunk", 512), ("fused_attention", 1), ("attn_q_tmem", 1)):
             pg.set_option(name, val)
