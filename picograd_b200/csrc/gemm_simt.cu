@@ -71,13 +71,14 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
 
     // the chain of column gn starts at bias[gn], as in picograd, where the micro-kernel accumulates onto
     // a C row that was initialised with the bias
-    float acc[T][T];
+    float2 acc2[T][T / 2];                    // columns in pairs: what fma.rn.f32x2 (sm_100) reads and writes
+#define ACC(i, j) (((j) & 1) ? acc2[i][(j) >> 1].y : acc2[i][(j) >> 1].x)
 #pragma unroll
     for (int j = 0; j < T; ++j) {
         const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
         const float b0 = (p.bias && gn < p.N) ? p.bias[gn] : 0.0f;
 #pragma unroll
-        for (int i = 0; i < T; ++i) acc[i][j] = b0;
+        for (int i = 0; i < T; ++i) ACC(i, j) = b0;
     }
 
     // walk the contiguous dimension of each operand with consecutive threads
@@ -134,10 +135,13 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
                     const float4 vb = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4 + i * 16]);
                     b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
                 }
+                // two columns per instruction; each lane is the same fused multiply-add as the scalar form
 #pragma unroll
-                for (int i = 0; i < T; ++i)
+                for (int i = 0; i < T; ++i) {
+                    const float2 aa = make_float2(a[i], a[i]);
 #pragma unroll
-                    for (int j = 0; j < T; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+                    for (int j = 0; j < T; j += 2) acc2[i][j >> 1] = __ffma2_rn(aa, make_float2(b[j], b[j + 1]), acc2[i][j >> 1]);
+                }
             }
             __syncthreads();
         }
@@ -153,12 +157,13 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
             const long long gn = n0 + tx * 4 + (j / 4) * 64 + (j % 4);
             if (gn >= p.N) continue;
             float *dst = Cb + gm * p.ldc + gn;
-            const float r = simt_act(acc[i][j], p.act), rc = p.act_copy_only ? acc[i][j] : r;
+            const float r = simt_act(ACC(i, j), p.act), rc = p.act_copy_only ? ACC(i, j) : r;
             *dst = p.accumulate ? (*dst + rc) : rc;
             if (p.c16) p.c16[(long long)bz * p.c16_bs + gm * p.ld16 + gn] = simt_to16(r, p.dtype16);
         }
     }
 }
+#undef ACC
 
 // ---------------------------------------------------------------------------------------------
 // f32 x f32, both operands row-major with unit column stride and 16-byte aligned rows (the shape of
