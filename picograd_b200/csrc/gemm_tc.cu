@@ -10,7 +10,14 @@
 //     warps 2..5 = epilogue (tcgen05.ld -> swizzled smem -> TMA store, or direct
 //     predicated stores when C does not satisfy the TMA alignment rules).
 //   * Persistent: each CTA (pair) walks a strided list of work units
-//     (batch x M-tile x N-tile x K-split) in an L2-friendly grouped order.
+//     (batch x M-tile x N-tile x K-split) in an L2-friendly grouped order:
+//     rasterisation groups of M tiles, each die of the GPU on its own half of a
+//     group, odd groups walking N downwards and a CTA's odd-numbered tiles
+//     fetching K last to first, so that a wave starts on what the one before it
+//     has just read.
+//   * A tile of C can be stored to several matrices at once (other devices' C
+//     mapped into this process): a column shard then lands in every device's full
+//     C while the next tiles are multiplied, with no collective afterwards.
 //   * Either operand may be K-major or MN-major in memory (that is how the
 //     row-major NN product and the two transposed products of the backward pass
 //     are served without materialising a transpose), and the K loop may run
