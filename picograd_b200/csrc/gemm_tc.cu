@@ -1342,13 +1342,11 @@ int tc_gemm_launch(const TcGemm &g) {
     } else if (g.l2_hints < 0) {
         p.l2_hints = 0;
     } else {
-        // C is written once: let it leave L2 first.  The A panel of one rasterisation group is re-read by
-        // every wave of the group: keep it, when it is small enough to stay (measured +0.8 % at 8192^3).
-        const uint64_t a_panel = (uint64_t)p.group_m * BM_CTA * c.cg * g.K * 2;
-        // ... and B at evict-last as well, so that what leaves the L2 first is C and nothing of the operands
-        // (measured interleaved with B at normal priority: 1271.0 -> 1294.6 and 1312.8 -> 1334.0 TFLOP/s at 8192^3 on two
-        // GPUs, 1295.0 -> 1312.7 at 8192 x 4096 x 8192, 1293.8 -> 1308.9 at 8192 x 16384 x 4096, 1150.6 -> 1159.0 at 4096^3)
-        p.l2_hints = (1u << 4) | (2u << 2) | (a_panel <= (48ull << 20) ? 2u : 0u);
+        // C is written once: let it leave the L2 first, and nothing of the operands (both evict-last).  Measured
+        // interleaved against B at normal priority: 1271.0 -> 1294.6 and 1312.8 -> 1334.0 TFLOP/s at 8192^3 on two GPUs,
+        // 1295.0 -> 1312.7 at 8192 x 4096 x 8192, 1293.8 -> 1308.9 at 8192 x 16384 x 4096, 1150.6 -> 1159.0 at 4096^3;
+        // against A at normal priority where a group's A panel is larger than the L2 keeps (K = 16384): 1292.9 -> 1307.6.
+        p.l2_hints = (1u << 4) | (2u << 2) | 2u;
         // A narrow product (all of its N tiles inside one wave: the N-column shard of a multi-GPU run) turns the
         // roles round: every wave multiplies new rows of A by ALL of B, so B is what should stay and A is read once
         // (measured at 8192 x 1024 x 8192, interleaved: 1092.9 -> 1130.3 and 1111.8 -> 1154.1 TFLOP/s, +3.4-3.8 %; with
