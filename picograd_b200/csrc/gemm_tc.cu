@@ -1350,12 +1350,11 @@ int tc_gemm_launch(const TcGemm &g) {
         // A narrow product (all of its N tiles inside one wave: the N-column shard of a multi-GPU run) turns the
         // roles round: every wave multiplies new rows of A by ALL of B, so B is what should stay and A is read once
         // (measured at 8192 x 1024 x 8192, interleaved: 1092.9 -> 1130.3 and 1111.8 -> 1154.1 TFLOP/s, +3.4-3.8 %; with
-        // a B of 33.5 MB, 8192 x 2048 x 8192, the same hints lose 1.6 %, so the rule stops at 24 MB).
+        // a B of 33.5 MB, 8192 x 2048 x 8192, the same hints lose 1.6 % and the general rule above is the best
+        // of those tried: 1212.9 against 1201.3 with A at normal priority; so the rule stops at 24 MB).
         const uint32_t wave_n = (uint32_t)rt.max_clusters / (p.group_m ? p.group_m : 1);
         const uint64_t b_all = (uint64_t)g.N * g.K * 2;
         if (g.batch == 1 && p.n_tiles <= wave_n && b_all <= (24ull << 20)) p.l2_hints = (1u << 4) | (2u << 2) | 1u;
-        // in between (the 4-GPU shard, B 33.5 MB): keep B, leave A at normal priority (1193.0 -> 1205.0, +1.0 %)
-        else if (g.batch == 1 && p.n_tiles <= wave_n && b_all <= (48ull << 20)) p.l2_hints = (1u << 4) | (2u << 2);
     }
     if (g.group_m > 0) p.group_m = (uint32_t)g.group_m;
     p.serpentine = g.serpentine ? 1u : 0u;
