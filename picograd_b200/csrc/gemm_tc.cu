@@ -1347,6 +1347,7 @@ int tc_gemm_launch(const TcGemm &g) {
         // 1295.0 -> 1312.7 at 8192 x 4096 x 8192, 1293.8 -> 1308.9 at 8192 x 16384 x 4096, 1150.6 -> 1159.0 at 4096^3;
         // against A at normal priority where a group's A panel is larger than the L2 keeps (K = 16384): 1292.9 -> 1307.6.
         p.l2_hints = (1u << 4) | (2u << 2) | 2u;
+        if (g.c_trans) p.l2_hints = (1u << 4) | 2u;          // swapped skinny route (one stream through B): as before
         // A narrow product (all of its N tiles inside one wave: the N-column shard of a multi-GPU run) turns the
         // roles round: every wave multiplies new rows of A by ALL of B, so B is what should stay and A is read once
         // (measured at 8192 x 1024 x 8192, interleaved: 1092.9 -> 1130.3 and 1111.8 -> 1154.1 TFLOP/s, +3.4-3.8 %; with
